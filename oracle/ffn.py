@@ -1,0 +1,34 @@
+"""Oracle for the SwiGLU FFN (test infrastructure, not product code).
+
+Restates
+  examples/models/01_ffn.py:174-176  fp32: (gate * sigmoid(gate) * up) @ W_down
+  tests/st/runtime/framework_and_models/test_qwen3_decode_scope3_mixed.py:282-285
+      bf16 variant: operands bf16, fp32 accumulate, activation rounded to bf16
+      before the down projection.
+"""
+
+from __future__ import annotations
+
+import torch
+
+
+def ffn_swiglu(x, w_gate, w_up, w_down):
+    """fp32 SwiGLU FFN, the expression of 01_ffn.py:174-176."""
+    gate = x @ w_gate
+    up = x @ w_up
+    return (gate * torch.sigmoid(gate) * up) @ w_down
+
+
+def ffn_swiglu_bf16(x_bf16, w_gate, w_up, w_down):
+    """bf16-operand FFN with the reference's rounding points
+    (test_qwen3_decode_scope3_mixed.py:282-285): fp32 accumulate, activation
+    rounded to bf16, fp32 result returned (the caller adds the residual)."""
+    xf = x_bf16.float()
+    gate = torch.matmul(xf, w_gate.float())
+    up = torch.matmul(xf, w_up.float())
+    act = (gate * torch.sigmoid(gate) * up).bfloat16()
+    return torch.matmul(act.float(), w_down.float())
+
+
+def ffn_flops(m, k, inter):
+    return 3 * 2 * m * k * inter
