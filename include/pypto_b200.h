@@ -1,0 +1,146 @@
+/* C ABI of the B200 (sm_100a) backend for pypto's fused model operators.
+ *
+ * Two groups of entry points:
+ *   1. the runtime object the reference obtains from its external device runtime
+ *      (`simpler.Worker`: init / malloc / free / copy_to / copy_from / register /
+ *      run / close, used at python/pypto/runtime/device_runner.py:821-842 and
+ *      python/pypto/runtime/worker.py:222-423), and
+ *   2. one direct launcher per fused operator, taking plain device pointers and
+ *      sizes, for callers that manage memory themselves.
+ *
+ * Conventions: every function returns 0 on success or a pto_status code; no C++
+ * exception crosses this boundary; `pto_last_error()` gives the message of the
+ * last failure on the calling thread.  All `*_dev` / device pointers are CUDA
+ * device addresses on the worker's (or the current) device.  `stream` is a
+ * `cudaStream_t` passed as `void*` (NULL = the legacy default stream).  Kernels
+ * are asynchronous; `pto_synchronize` / `pto_device_status` wait for them.
+ */
+#ifndef PYPTO_B200_H_
+#define PYPTO_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define PTO_API __attribute__((visibility("default")))
+#else
+#define PTO_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum pto_status {
+  PTO_OK = 0,
+  PTO_INVALID_ARGUMENT = 1,
+  PTO_CUDA_ERROR = 2,
+  PTO_UNSUPPORTED = 3,
+  PTO_DEVICE_TIMEOUT = 4, /* a bounded device-side wait ran out; see pto_device_status */
+  PTO_OUT_OF_MEMORY = 5,
+  PTO_NOT_FOUND = 6
+} pto_status;
+
+/* Element types, numbered like the subset of pypto's DataType that the fused
+ * operators use (python/pypto/__init__.py:53-56 lists the fp8 members). */
+typedef enum pto_dtype {
+  PTO_FP32 = 0,
+  PTO_BF16 = 1,
+  PTO_FP16 = 2,
+  PTO_INT32 = 3,
+  PTO_INT64 = 4,
+  PTO_FP8E4M3 = 5,
+  PTO_UINT8 = 6
+} pto_dtype;
+
+/* Tensor descriptor handed to a registered callable.  Mirrors the fields of the
+ * reference's ChipTensor that generated kernels read (buffer.addr, start_offset
+ * in elements, shapes[], ndims: python/pypto/runtime/builtins/collectives/
+ * all_to_all_v/templates/kernel.cpp.in:45-94). */
+typedef struct pto_chip_tensor {
+  uint64_t addr;
+  uint64_t start_offset;
+  uint32_t shapes[5];
+  uint32_t ndims;
+  uint32_t dtype; /* pto_dtype */
+  uint32_t reserved;
+} pto_chip_tensor;
+
+/* Arguments of one launch: tensors first, then scalars bit-cast to uint64, the
+ * order of the reference's `kernel_entry(int64_t* args)` convention
+ * (python/pypto/backend/pto_backend.py:541-629, 898-915). */
+typedef struct pto_task_args {
+  const pto_chip_tensor* tensors;
+  uint32_t n_tensors;
+  const uint64_t* scalars;
+  uint32_t n_scalars;
+} pto_task_args;
+
+typedef struct pto_worker pto_worker;
+
+PTO_API const char* pto_last_error(void);
+PTO_API const char* pto_version(void);
+
+/* ---- runtime object (replaces simpler.Worker: device_runner.py:821-842) ---- */
+PTO_API int pto_worker_create(int device_id, pto_worker** out);
+PTO_API int pto_worker_destroy(pto_worker* w); /* idempotent on NULL; frees what the worker still owns */
+PTO_API int pto_malloc(pto_worker* w, size_t nbytes, uint64_t* dev_ptr);      /* worker.py:349-366 */
+PTO_API int pto_free(pto_worker* w, uint64_t dev_ptr);                        /* worker.py:368-379; unknown or already freed pointers are an error */
+PTO_API int pto_copy_to(pto_worker* w, uint64_t dst_dev, const void* src_host, size_t nbytes);   /* worker.py:381-400 */
+PTO_API int pto_copy_from(pto_worker* w, void* dst_host, uint64_t src_dev, size_t nbytes);       /* worker.py:402-423 */
+PTO_API int pto_synchronize(pto_worker* w);
+PTO_API void* pto_worker_stream(pto_worker* w);
+/* Reads and clears the device error word of the worker's scratch arena:
+ * out[0] code (0 none, 1 barrier timeout, 2 block id outside the pool), out[1] site,
+ * out[2] CTA, out[3] detail.  Synchronises the worker's stream. */
+PTO_API int pto_device_status(pto_worker* w, int32_t out[4]);
+/* The worker's scratch arena (grown on demand, never shrunk). */
+PTO_API int pto_worker_scratch(pto_worker* w, size_t min_bytes, uint64_t* dev_ptr, size_t* nbytes);
+
+/* Registered callables (replaces Worker.register / Worker.run with a ChipCallable:
+ * device_runner.py:651-656, worker.py:532-626).  `op_name` names a fused operator:
+ * "paged_attention", "paged_gather", "rms_norm", "rope_kv_append", "linear",
+ * "ffn_swiglu", "moe_gate_topk", ...  (pto_op_list). */
+PTO_API int pto_register_callable(pto_worker* w, const char* op_name, int32_t* cid);
+PTO_API int pto_unregister_callable(pto_worker* w, int32_t cid);
+PTO_API int pto_run(pto_worker* w, int32_t cid, const pto_task_args* args);
+/* NUL-separated, double-NUL-terminated list of operator names. */
+PTO_API const char* pto_op_list(void);
+
+/* ---- direct launchers ---- */
+
+/* Paged-attention decode.  Replaces the orchestration `paged_attention` and its four
+ * kernels (examples/models/04_paged_attention.py:62-227, 272-367) and the SPMD variant
+ * (examples/models/09_paged_attention_spmd.py:503-572).
+ *   q            bf16 [batch * q_len * num_heads, head_dim], row = (sequence, draft, head)
+ *   k_cache, v_cache  bf16 [pool_blocks * kv_heads * block_size, head_dim],
+ *                row = (block, kv head, token)
+ *   block_table  int32 [batch, max_blocks]; context_lens int32 [batch]
+ *   out          bf16 (out_dtype PTO_BF16) or fp32 (PTO_FP32), same rows as q
+ *   q_len > 1    draft token j of a sequence sees its first ctx - q_len + j + 1 keys
+ *   scratch      device buffer of at least pto_paged_attention_scratch_bytes() bytes whose
+ *                first 64 bytes were zeroed once (error word); reused across calls on
+ *                one stream, not shared between concurrent launches. */
+PTO_API size_t pto_paged_attention_scratch_bytes(int batch, int num_heads, int kv_heads, int q_len);
+PTO_API int pto_paged_attention(const void* q, const void* k_cache, const void* v_cache,
+                        const int32_t* block_table, const int32_t* context_lens, void* out,
+                        int out_dtype, int batch, int num_heads, int kv_heads, int head_dim,
+                        int block_size, int max_blocks, int64_t pool_blocks, int q_len, float scale,
+                        void* scratch, size_t scratch_bytes, void* stream);
+
+/* Block-table row gather.  Replaces `pl.paged_gather`
+ * (src/ir/op/tensor_ops/paged_gather.cpp:63-169; semantics
+ * tests/st/runtime/ops/test_paged_gather.py:14-17):
+ *   phys = block_table[idx / block_size] * block_size + idx % block_size
+ *   out[i, 0:size] = src[phys, col_off : col_off + size]
+ * `elem_bytes` is the element size; rows are copied bit-exactly.  `err` (may be NULL)
+ * points at a zeroed int32[4] that receives code 2 if a row falls outside `src_rows`. */
+PTO_API int pto_paged_gather(const void* src, int64_t src_rows, int64_t src_cols, int elem_bytes,
+                     const int32_t* indices, int64_t n_indices, const int32_t* block_table,
+                     int64_t table_len, int block_size, int64_t col_off, int64_t size, void* out,
+                     int32_t* err, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PYPTO_B200_H_ */

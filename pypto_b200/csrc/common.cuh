@@ -1,0 +1,194 @@
+// Shared device/host helpers for the sm_100a kernels: bounded mbarrier waits,
+// TMA (cp.async.bulk.tensor) loads, ldmatrix / mma.sync wrappers, tcgen05 wrappers
+// and the host-side tensor-map encoder.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+namespace pto {
+
+// ---------------------------------------------------------------------------
+// Host: error plumbing.  No C++ exception crosses the C ABI; every entry point
+// returns a status and leaves a message here.
+// ---------------------------------------------------------------------------
+enum Status : int {
+  kOk = 0,
+  kInvalidArgument = 1,
+  kCudaError = 2,
+  kUnsupported = 3,
+  kDeviceTimeout = 4,
+  kOutOfMemory = 5,
+  kNotFound = 6,
+};
+
+void set_last_error(const std::string& msg);
+int fail(int status, const std::string& msg);
+int check_cuda(cudaError_t e, const char* what);
+
+#define PTO_CUDA(expr)                                  \
+  do {                                                  \
+    int _s = ::pto::check_cuda((expr), #expr);          \
+    if (_s != ::pto::kOk) return _s;                    \
+  } while (0)
+
+#define PTO_REQUIRE(cond, msg)                                            \
+  do {                                                                    \
+    if (!(cond)) return ::pto::fail(::pto::kInvalidArgument, (msg));      \
+  } while (0)
+
+// Encode a 2-D row-major tensor map [rows, cols] of `elem_bytes` elements with a
+// {box_cols, box_rows} box and the given swizzle.  Returns a Status.
+int make_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype,
+                       int elem_bytes, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
+                       uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swizzle);
+
+int sm_count();
+
+// Device error word layout (first 16 ints of every scratch buffer).
+//   [0] error code (0 = none), [1] where (site id), [2] blockIdx.x, [3] extra
+constexpr int kErrWords = 16;
+constexpr int kErrBarrierTimeout = 1;
+constexpr int kErrBadBlockId = 2;
+
+#ifdef __CUDACC__
+// ---------------------------------------------------------------------------
+// Device helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void report_error(int* err, int code, int site, int extra) {
+  if (err != nullptr && atomicCAS(err, 0, code) == 0) {
+    err[1] = site;
+    err[2] = static_cast<int>(blockIdx.x);
+    err[3] = extra;
+  }
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait: every spin in these kernels gives up after a fixed number of
+// polls so that a protocol bug ends the kernel with an error word instead of
+// hanging the device.  Returns false on timeout.
+constexpr uint32_t kMaxPolls = 1u << 22;
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kMaxPolls; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  return false;
+}
+
+// 2-D tiled TMA load into this CTA's shared memory; completion is signalled on
+// `bar` as transaction bytes.  No cluster multicast is used anywhere.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+// D(16x8, fp32) += A(16x16, bf16 row) * B(16x8, bf16 col)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Round two floats to bf16 (round-to-nearest-even), pack (lo in bits 0..15).
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+__device__ __forceinline__ float bf16_lo_to_float(uint32_t packed) {
+  return __uint_as_float(packed << 16);
+}
+__device__ __forceinline__ float bf16_hi_to_float(uint32_t packed) {
+  return __uint_as_float(packed & 0xffff0000u);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+#endif  // __CUDACC__
+
+}  // namespace pto

@@ -1,0 +1,161 @@
+// Operator registry (name -> adapter from the tensors-first task-argument list to a
+// kernel launcher) and the direct C launchers.  The adapters take what a
+// registered callable receives through pto_run: device tensors in the order of
+// the reference program's orchestration signature, then scalars as uint64.
+#include <cstring>
+#include <string>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "pypto_b200.h"
+#include "runtime.h"
+
+namespace pto {
+namespace {
+
+inline void* tptr(const pto_chip_tensor& t, size_t elem_bytes) {
+  return reinterpret_cast<void*>(t.addr + t.start_offset * elem_bytes);
+}
+
+inline size_t dtype_bytes(uint32_t d) {
+  switch (d) {
+    case PTO_FP32: case PTO_INT32: return 4;
+    case PTO_BF16: case PTO_FP16: return 2;
+    case PTO_INT64: return 8;
+    default: return 1;
+  }
+}
+
+inline float f32_from_bits(uint64_t v) {
+  uint32_t b = static_cast<uint32_t>(v & 0xffffffffu);
+  float f;
+  memcpy(&f, &b, 4);
+  return f;
+}
+
+inline int64_t numel(const pto_chip_tensor& t) {
+  int64_t n = 1;
+  for (uint32_t i = 0; i < t.ndims && i < 5; ++i) n *= t.shapes[i];
+  return n;
+}
+
+// tensors: query, key_cache, value_cache, block_table, context_lens, out
+// scalars: batch, num_heads, kv_heads, head_dim, block_size, max_blocks, q_len, scale (fp32 bits)
+// (the order of the reference's config tensor, examples/models/04_paged_attention.py:287)
+int op_paged_attention(Worker* w, const pto_task_args* a) {
+  if (a->n_tensors != 6 || a->n_scalars != 8)
+    return fail(kInvalidArgument, "paged_attention: expects 6 tensors and 8 scalars");
+  const pto_chip_tensor* t = a->tensors;
+  const uint64_t* s = a->scalars;
+  const int batch = (int)s[0], heads = (int)s[1], kvh = (int)s[2], hd = (int)s[3], bs = (int)s[4];
+  const int max_blocks = (int)s[5], q_len = (int)s[6];
+  if (t[0].dtype != PTO_BF16 || t[1].dtype != PTO_BF16 || t[2].dtype != PTO_BF16)
+    return fail(kInvalidArgument, "paged_attention: query and caches must be bf16");
+  if (t[3].dtype != PTO_INT32 || t[4].dtype != PTO_INT32)
+    return fail(kInvalidArgument, "paged_attention: block_table and context_lens must be int32");
+  if (t[5].dtype != PTO_BF16 && t[5].dtype != PTO_FP32)
+    return fail(kInvalidArgument, "paged_attention: out must be bf16 or fp32");
+  if (batch < 0 || heads <= 0 || kvh <= 0 || hd <= 0 || bs <= 0 || max_blocks <= 0 || q_len <= 0)
+    return fail(kInvalidArgument, "paged_attention: bad geometry scalars");
+  if (numel(t[0]) != (int64_t)batch * q_len * heads * hd || numel(t[5]) != numel(t[0]))
+    return fail(kInvalidArgument, "paged_attention: query/out size does not match batch*q_len*heads*head_dim");
+  if (numel(t[3]) < (int64_t)batch * max_blocks || numel(t[4]) < batch)
+    return fail(kInvalidArgument, "paged_attention: block_table/context_lens too small");
+  const int64_t rows = numel(t[1]) / hd;
+  if (numel(t[2]) != numel(t[1]) || rows % ((int64_t)kvh * bs) != 0)
+    return fail(kInvalidArgument, "paged_attention: cache rows must be a multiple of kv_heads*block_size");
+  const int64_t pool_blocks = rows / ((int64_t)kvh * bs);
+  const size_t need = pa_scratch_bytes(batch, heads, kvh, q_len);
+  int st = w->ensure_scratch(need);
+  if (st != kOk) return st;
+  return pa_launch(tptr(t[0], 2), tptr(t[1], 2), tptr(t[2], 2), static_cast<const int32_t*>(tptr(t[3], 4)),
+                   static_cast<const int32_t*>(tptr(t[4], 4)), tptr(t[5], dtype_bytes(t[5].dtype)),
+                   t[5].dtype == PTO_FP32, batch, heads, kvh, hd, bs, max_blocks, pool_blocks, q_len,
+                   f32_from_bits(s[7]), w->scratch, w->scratch_bytes, w->stream);
+}
+
+// tensors: src [rows, cols], indices int32 [n], block_table int32 [m], out [n, size]
+// scalars: block_size, col_off, size
+int op_paged_gather(Worker* w, const pto_task_args* a) {
+  if (a->n_tensors != 4 || a->n_scalars != 3)
+    return fail(kInvalidArgument, "paged_gather: expects 4 tensors and 3 scalars");
+  const pto_chip_tensor* t = a->tensors;
+  if (t[0].ndims != 2) return fail(kInvalidArgument, "paged_gather: src must be 2-D");
+  if (t[1].dtype != PTO_INT32 || t[2].dtype != PTO_INT32)
+    return fail(kInvalidArgument, "paged_gather: indices and block_table must be int32");
+  const size_t eb = dtype_bytes(t[0].dtype);
+  if (dtype_bytes(t[3].dtype) != eb) return fail(kInvalidArgument, "paged_gather: out dtype differs from src");
+  const int64_t n = numel(t[1]), size = (int64_t)a->scalars[2];
+  if (numel(t[3]) != n * size) return fail(kInvalidArgument, "paged_gather: out must hold n_indices*size elements");
+  int st = w->ensure_scratch(256);
+  if (st != kOk) return st;
+  return paged_gather_launch(tptr(t[0], eb), t[0].shapes[0], t[0].shapes[1], (int)eb,
+                             static_cast<const int32_t*>(tptr(t[1], 4)), n,
+                             static_cast<const int32_t*>(tptr(t[2], 4)), numel(t[2]), (int)a->scalars[0],
+                             (int64_t)a->scalars[1], size, tptr(t[3], eb), static_cast<int32_t*>(w->scratch),
+                             w->stream);
+}
+
+struct OpEntry {
+  const char* name;
+  OpFn fn;
+};
+
+const OpEntry kOps[] = {
+    {"paged_attention", op_paged_attention},
+    {"paged_gather", op_paged_gather},
+};
+
+}  // namespace
+
+OpFn find_op(const char* name) {
+  for (const OpEntry& e : kOps)
+    if (strcmp(e.name, name) == 0) return e.fn;
+  return nullptr;
+}
+
+}  // namespace pto
+
+extern "C" {
+
+const char* pto_op_list(void) {
+  static std::string names;
+  if (names.empty()) {
+    for (const pto::OpEntry& e : pto::kOps) {
+      names += e.name;
+      names.push_back('\0');
+    }
+    names.push_back('\0');
+  }
+  return names.c_str();
+}
+
+size_t pto_paged_attention_scratch_bytes(int batch, int num_heads, int kv_heads, int q_len) {
+  if (batch < 0 || num_heads <= 0 || kv_heads <= 0 || q_len <= 0) return 0;
+  return pto::pa_scratch_bytes(batch, num_heads, kv_heads, q_len);
+}
+
+int pto_paged_attention(const void* q, const void* k_cache, const void* v_cache, const int32_t* block_table,
+                        const int32_t* context_lens, void* out, int out_dtype, int batch, int num_heads,
+                        int kv_heads, int head_dim, int block_size, int max_blocks, int64_t pool_blocks,
+                        int q_len, float scale, void* scratch, size_t scratch_bytes, void* stream) {
+  if (out_dtype != PTO_BF16 && out_dtype != PTO_FP32)
+    return pto::fail(pto::kInvalidArgument, "paged_attention: out_dtype must be PTO_BF16 or PTO_FP32");
+  if (!q || !k_cache || !v_cache || !block_table || !context_lens || !out)
+    return pto::fail(pto::kInvalidArgument, "paged_attention: NULL tensor");
+  return pto::pa_launch(q, k_cache, v_cache, block_table, context_lens, out, out_dtype == PTO_FP32, batch,
+                        num_heads, kv_heads, head_dim, block_size, max_blocks, pool_blocks, q_len, scale,
+                        scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int pto_paged_gather(const void* src, int64_t src_rows, int64_t src_cols, int elem_bytes, const int32_t* indices,
+                     int64_t n_indices, const int32_t* block_table, int64_t table_len, int block_size,
+                     int64_t col_off, int64_t size, void* out, int32_t* err, void* stream) {
+  if (n_indices > 0 && (!src || !indices || !block_table || !out))
+    return pto::fail(pto::kInvalidArgument, "paged_gather: NULL tensor");
+  return pto::paged_gather_launch(src, src_rows, src_cols, elem_bytes, indices, n_indices, block_table,
+                                  table_len, block_size, col_off, size, out, err,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

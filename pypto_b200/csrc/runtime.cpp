@@ -1,0 +1,271 @@
+// Host runtime behind the C ABI: worker object (device, stream, allocations,
+// scratch arena), registered callables, error plumbing, tensor-map encoding.
+// It stands where the reference loads its external device runtime
+// (python/pypto/runtime/device_runner.py:821-842).
+#include "runtime.h"
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+#include "pypto_b200.h"
+
+namespace pto {
+
+namespace {
+thread_local std::string g_last_error;
+}
+
+void set_last_error(const std::string& msg) { g_last_error = msg; }
+
+int fail(int status, const std::string& msg) {
+  g_last_error = msg;
+  return status;
+}
+
+int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return kOk;
+  g_last_error = std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
+  return e == cudaErrorMemoryAllocation ? kOutOfMemory : kCudaError;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+static EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+  });
+  return fn;
+}
+
+int make_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes,
+                       uint64_t rows, uint64_t cols, uint64_t row_stride_bytes, uint32_t box_cols,
+                       uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return fail(kCudaError, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_stride_bytes & 15) != 0)
+    return fail(kInvalidArgument, "tensor map: base and row stride must be multiples of 16 bytes");
+  if (box_cols * static_cast<uint64_t>(elem_bytes) % 16 != 0 || box_rows == 0 || box_rows > 256 || box_cols > 256)
+    return fail(kInvalidArgument, "tensor map: bad box");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[160];
+    snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%llu cols=%llu box=%ux%u)",
+             static_cast<int>(r), (unsigned long long)rows, (unsigned long long)cols, box_cols, box_rows);
+    return fail(kCudaError, buf);
+  }
+  return kOk;
+}
+
+// ------------------------------- Worker -----------------------------------
+
+Worker::~Worker() {
+  cudaSetDevice(device);
+  for (auto& kv : allocs) cudaFree(reinterpret_cast<void*>(kv.first));
+  allocs.clear();
+  if (scratch) cudaFree(scratch);
+  if (stream) cudaStreamDestroy(stream);
+}
+
+int Worker::ensure_scratch(size_t nbytes) {
+  if (nbytes <= scratch_bytes) return kOk;
+  PTO_CUDA(cudaSetDevice(device));
+  PTO_CUDA(cudaStreamSynchronize(stream));
+  size_t want = nbytes < (size_t(1) << 20) ? (size_t(1) << 20) : nbytes;
+  void* p = nullptr;
+  PTO_CUDA(cudaMalloc(&p, want));
+  cudaError_t e = cudaMemsetAsync(p, 0, 256, stream);
+  if (e != cudaSuccess) { cudaFree(p); return check_cuda(e, "cudaMemsetAsync(scratch)"); }
+  if (scratch) cudaFree(scratch);
+  scratch = p;
+  scratch_bytes = want;
+  return kOk;
+}
+
+}  // namespace pto
+
+using pto::Worker;
+
+extern "C" {
+
+const char* pto_last_error(void) { return pto::g_last_error.c_str(); }
+const char* pto_version(void) { return "pypto-b200 0.1 (sm_100a)"; }
+
+int pto_worker_create(int device_id, pto_worker** out) {
+  if (out == nullptr) return pto::fail(pto::kInvalidArgument, "worker_create: out is NULL");
+  *out = nullptr;
+  int n = 0;
+  PTO_CUDA(cudaGetDeviceCount(&n));
+  if (device_id < 0 || device_id >= n) return pto::fail(pto::kInvalidArgument, "worker_create: no such device");
+  PTO_CUDA(cudaSetDevice(device_id));
+  Worker* w = new (std::nothrow) Worker();
+  if (w == nullptr) return pto::fail(pto::kOutOfMemory, "worker_create: host allocation failed");
+  w->device = device_id;
+  cudaError_t e = cudaStreamCreateWithFlags(&w->stream, cudaStreamNonBlocking);
+  if (e != cudaSuccess) { delete w; return pto::check_cuda(e, "cudaStreamCreate"); }
+  *out = reinterpret_cast<pto_worker*>(w);
+  return pto::kOk;
+}
+
+int pto_worker_destroy(pto_worker* h) {
+  if (h == nullptr) return pto::kOk;
+  Worker* w = reinterpret_cast<Worker*>(h);
+  cudaSetDevice(w->device);
+  cudaStreamSynchronize(w->stream);
+  delete w;
+  return pto::kOk;
+}
+
+#define PTO_WORKER(h)                                                              \
+  Worker* w = reinterpret_cast<Worker*>(h);                                        \
+  if (w == nullptr) return pto::fail(pto::kInvalidArgument, "worker handle is NULL"); \
+  PTO_CUDA(cudaSetDevice(w->device))
+
+int pto_malloc(pto_worker* h, size_t nbytes, uint64_t* dev_ptr) {
+  PTO_WORKER(h);
+  if (dev_ptr == nullptr) return pto::fail(pto::kInvalidArgument, "malloc: dev_ptr is NULL");
+  void* p = nullptr;
+  PTO_CUDA(cudaMalloc(&p, nbytes == 0 ? 1 : nbytes));
+  std::lock_guard<std::mutex> g(w->mu);
+  w->allocs[reinterpret_cast<uint64_t>(p)] = nbytes;
+  *dev_ptr = reinterpret_cast<uint64_t>(p);
+  return pto::kOk;
+}
+
+int pto_free(pto_worker* h, uint64_t dev_ptr) {
+  PTO_WORKER(h);
+  {
+    std::lock_guard<std::mutex> g(w->mu);
+    auto it = w->allocs.find(dev_ptr);
+    if (it == w->allocs.end()) return pto::fail(pto::kNotFound, "free: pointer is not owned by this worker (double free?)");
+    w->allocs.erase(it);
+  }
+  PTO_CUDA(cudaStreamSynchronize(w->stream));
+  PTO_CUDA(cudaFree(reinterpret_cast<void*>(dev_ptr)));
+  return pto::kOk;
+}
+
+int pto_copy_to(pto_worker* h, uint64_t dst_dev, const void* src_host, size_t nbytes) {
+  PTO_WORKER(h);
+  if (nbytes == 0) return pto::kOk;
+  if (src_host == nullptr || dst_dev == 0) return pto::fail(pto::kInvalidArgument, "copy_to: NULL pointer");
+  PTO_CUDA(cudaMemcpyAsync(reinterpret_cast<void*>(dst_dev), src_host, nbytes, cudaMemcpyHostToDevice, w->stream));
+  PTO_CUDA(cudaStreamSynchronize(w->stream));
+  return pto::kOk;
+}
+
+int pto_copy_from(pto_worker* h, void* dst_host, uint64_t src_dev, size_t nbytes) {
+  PTO_WORKER(h);
+  if (nbytes == 0) return pto::kOk;
+  if (dst_host == nullptr || src_dev == 0) return pto::fail(pto::kInvalidArgument, "copy_from: NULL pointer");
+  PTO_CUDA(cudaMemcpyAsync(dst_host, reinterpret_cast<const void*>(src_dev), nbytes, cudaMemcpyDeviceToHost, w->stream));
+  PTO_CUDA(cudaStreamSynchronize(w->stream));
+  return pto::kOk;
+}
+
+int pto_synchronize(pto_worker* h) {
+  PTO_WORKER(h);
+  PTO_CUDA(cudaStreamSynchronize(w->stream));
+  return pto::kOk;
+}
+
+void* pto_worker_stream(pto_worker* h) {
+  return h ? reinterpret_cast<Worker*>(h)->stream : nullptr;
+}
+
+int pto_worker_scratch(pto_worker* h, size_t min_bytes, uint64_t* dev_ptr, size_t* nbytes) {
+  PTO_WORKER(h);
+  int st = w->ensure_scratch(min_bytes < 256 ? 256 : min_bytes);
+  if (st != pto::kOk) return st;
+  if (dev_ptr) *dev_ptr = reinterpret_cast<uint64_t>(w->scratch);
+  if (nbytes) *nbytes = w->scratch_bytes;
+  return pto::kOk;
+}
+
+int pto_device_status(pto_worker* h, int32_t out[4]) {
+  PTO_WORKER(h);
+  int32_t words[4] = {0, 0, 0, 0};
+  PTO_CUDA(cudaStreamSynchronize(w->stream));
+  if (w->scratch) {
+    PTO_CUDA(cudaMemcpyAsync(words, w->scratch, sizeof words, cudaMemcpyDeviceToHost, w->stream));
+    PTO_CUDA(cudaStreamSynchronize(w->stream));
+    if (words[0] != 0) {
+      PTO_CUDA(cudaMemsetAsync(w->scratch, 0, 64, w->stream));
+      PTO_CUDA(cudaStreamSynchronize(w->stream));
+    }
+  }
+  if (out) memcpy(out, words, sizeof words);
+  if (words[0] == pto::kErrBarrierTimeout) {
+    char buf[128];
+    snprintf(buf, sizeof buf, "device wait timed out (site %d, CTA %d, detail %d)", words[1], words[2], words[3]);
+    return pto::fail(pto::kDeviceTimeout, buf);
+  }
+  if (words[0] == pto::kErrBadBlockId) {
+    char buf[128];
+    snprintf(buf, sizeof buf, "block id or row outside the pool (site %d, CTA %d, value %d)", words[1], words[2], words[3]);
+    return pto::fail(pto::kInvalidArgument, buf);
+  }
+  return pto::kOk;
+}
+
+int pto_register_callable(pto_worker* h, const char* op_name, int32_t* cid) {
+  PTO_WORKER(h);
+  if (op_name == nullptr || cid == nullptr) return pto::fail(pto::kInvalidArgument, "register: NULL argument");
+  pto::OpFn fn = pto::find_op(op_name);
+  if (fn == nullptr) return pto::fail(pto::kNotFound, std::string("no fused kernel registered for '") + op_name + "'");
+  std::lock_guard<std::mutex> g(w->mu);
+  int32_t id = w->next_cid++;
+  w->callables[id] = fn;
+  *cid = id;
+  return pto::kOk;
+}
+
+int pto_unregister_callable(pto_worker* h, int32_t cid) {
+  PTO_WORKER(h);
+  std::lock_guard<std::mutex> g(w->mu);
+  if (w->callables.erase(cid) == 0) return pto::fail(pto::kNotFound, "unregister: unknown callable id");
+  return pto::kOk;
+}
+
+int pto_run(pto_worker* h, int32_t cid, const pto_task_args* args) {
+  PTO_WORKER(h);
+  if (args == nullptr) return pto::fail(pto::kInvalidArgument, "run: args is NULL");
+  pto::OpFn fn = nullptr;
+  {
+    std::lock_guard<std::mutex> g(w->mu);
+    auto it = w->callables.find(cid);
+    if (it == w->callables.end()) return pto::fail(pto::kNotFound, "run: unknown callable id");
+    fn = it->second;
+  }
+  return fn(w, args);
+}
+
+}  // extern "C"

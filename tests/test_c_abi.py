@@ -1,0 +1,40 @@
+"""The shared library loads without a GPU and exports every symbol the header declares."""
+
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "pypto_b200.h")).read()
+    return sorted(set(re.findall(r"PTO_API\s+[\w\s\*]+?\b(pto_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    import __graft_entry__ as entry
+    entry.build()
+    from pypto_b200 import _lib
+    lib = _lib.load()
+    names = _declared()
+    assert len(names) >= 19
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in the header but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert set(_lib.SIGNATURES) == set(names)
+
+
+def test_op_list_and_version():
+    from pypto_b200 import _lib
+    assert {"paged_attention", "paged_gather"} <= set(_lib.op_names())
+    assert b"sm_100a" in _lib.load().pto_version()
+
+
+def test_cpu_tensors_are_refused_not_computed():
+    import torch
+    from pypto_b200 import BackendUnavailable, ops
+    with pytest.raises(BackendUnavailable):
+        ops.paged_gather(torch.zeros(4, 4), torch.zeros(1, dtype=torch.int32),
+                         torch.zeros(1, dtype=torch.int32), 4)
