@@ -36,7 +36,7 @@ WORKLOAD = dict(batch=64, num_heads=32, kv_heads=8, head_dim=128, block_size=128
 METRIC, UNIT = "paged_attn_decode_GBps", "GB/s"
 # dram bytes (read + write) of one pa_decode_kernel launch on this workload, from the ncu
 # capture summarised in profiles/ (None until captured)
-NCU_TRAFFIC_BYTES = None
+NCU_TRAFFIC_BYTES = 1406460304  # 1.398522e9 read + 7.938304e6 write, profiles/pa_decode_kernel_*.md
 
 
 def peaks():
@@ -150,7 +150,7 @@ def run_reference(args):
     if rank != 0:
         return
     d = make_inputs(0)
-    n_seq = 16
+    n_seq = WORKLOAD["batch"]
     times = []
     for i in range(args.warmup + args.steps):
         dt, nbytes = cpu_oracle_time(d, n_seq)
@@ -183,7 +183,6 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     from pypto_b200 import ops
-    from pypto_b200.runtime import RunConfig, fused_programs
 
     d = make_inputs(rank)  # every rank decodes its own sequences
     g = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
@@ -230,23 +229,39 @@ def run_ours(args):
     sec_per_step = ms_max / 1e3 / args.steps
     value = total_bytes / sec_per_step / 1e9
 
-    # ---- end to end through the launch surface with HOST tensors ----
-    prog = fused_programs.paged_attention_program(batch=d["batch"], num_heads=d["num_heads"],
-                                                  kv_heads=d["kv_heads"], head_dim=d["head_dim"],
-                                                  block_size=d["block_size"], max_blocks=d["max_blocks"],
-                                                  q_len=d["q_len"], out_dtype=torch.bfloat16)
+    e2e_value = e2e_res = None
+    h2d = d2h = 0
+    if not args.kernel_only:
+        e2e_value, e2e_res, h2d, d2h = end_to_end(args, d, dev, local, world, total_bytes, barrier)
+
+    if rank == 0:
+        emit(args, d, ms, my_bytes, value, sec_per_step, total_seq, world, clocks, e2e_value, e2e_res, h2d, d2h)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def end_to_end(args, d, dev, local, world, total_bytes, barrier):
+    """The same metric through the launch surface with HOST tensors."""
+    import torch.distributed as dist
+
+    from pypto_b200.runtime import RunConfig, fused_programs
+    prog = fused_programs.paged_attention_program(d["batch"], d["num_heads"], d["head_dim"], d["block_size"],
+                                                  d["max_blocks"], kv_heads=d["kv_heads"], q_len=d["q_len"],
+                                                  out_dtype=torch.bfloat16)
     host = {k: d[k].pin_memory() for k in ("query", "key_cache", "value_cache", "block_table", "context_lens")}
     host_out = torch.empty(d["query"].shape, dtype=torch.bfloat16).pin_memory()
     cfg_t = fused_programs.pack_config(d)
-    compiled = prog.compile(RunConfig(platform="b200", device_id=local))
+    from pypto_b200 import ir
+    compiled = ir.compile(prog, platform="b200")
+    run_cfg = RunConfig(platform="b200", device_id=local)
     e2e_steps = max(2, min(args.steps, 5))
     compiled(host["query"], host["key_cache"], host["value_cache"], host["block_table"].flatten(),
-             host["context_lens"], host_out, cfg_t)
+             host["context_lens"], host_out, cfg_t, config=run_cfg)
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         compiled(host["query"], host["key_cache"], host["value_cache"], host["block_table"].flatten(),
-                 host["context_lens"], host_out, cfg_t)
+                 host["context_lens"], host_out, cfg_t, config=run_cfg)
     torch.cuda.synchronize()
     e2e_sec = (time.perf_counter() - t0) / e2e_steps
     e2e_stats = torch.tensor([e2e_sec], dtype=torch.float64, device=dev)
@@ -265,45 +280,50 @@ def run_ours(args):
         e2e_res = total_bytes / res_stats[0].item() / 1e9
     except Exception as e:  # reported, never hidden
         e2e_res = f"failed: {e}"
+    return e2e_value, e2e_res, h2d, d2h
 
-    if rank == 0:
-        peak, which = peaks()
-        kernel_bytes = my_bytes  # one launch of the dominant kernel processes one rank's batch
-        achieved = kernel_bytes / (ms / 1e3 / args.steps) / 1e9
-        n_seq = 16
-        cpu_dt, cpu_bytes = cpu_oracle_time(d, n_seq)
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": sec_per_step * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "paged_attention_decode batch64/GPU hq32 hkv8 d128 block128 "
-                                   "ctx U[1024,8192] q_len1", "l2": "inputs (1.2 GB/GPU) larger than L2",
-                       "kv_bytes_per_step_per_gpu": kv_bytes_of(d)},
-            "tokens_per_s": total_seq / sec_per_step,
-            "gpu_launches": 2 * args.steps,
-            "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES, "peak_source": which,
-                         "note": "achieved = algorithmic bytes of one step / CUDA-event time of the step "
-                                 "(pa_decode_kernel + pa_merge_kernel), rank 0"},
-            "cpu_baseline": {"value": cpu_bytes / cpu_dt / 1e9, "unit": UNIT, "cores": torch.get_num_threads(),
-                             "kind": "port", "sample": f"{n_seq} of 64 sequences, one pass, torch CPU oracle",
-                             "host_cpus": os.cpu_count()},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "note": "run()-style call with every tensor on the host, KV pools included",
-                    "resident_kv_cache_value": e2e_res},
-        }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+
+def emit(args, d, ms, my_bytes, value, sec_per_step, total_seq, world, clocks, e2e_value, e2e_res, h2d, d2h):
+    peak, which = peaks()
+    kernel_bytes = my_bytes  # one launch of the dominant kernel processes one rank's batch
+    achieved = kernel_bytes / (ms / 1e3 / args.steps) / 1e9
+    n_seq = WORKLOAD["batch"]
+    cpu = None
+    if not args.kernel_only:
+        cpu_dt, cpu_bytes = cpu_oracle_time(d, n_seq, repeats=5)
+        cpu = {"value": cpu_bytes / cpu_dt / 1e9, "unit": UNIT, "cores": torch.get_num_threads(),
+               "kind": "port", "sample": f"{n_seq} of 64 sequences, mean of 5 passes, torch CPU oracle",
+               "host_cpus": os.cpu_count()}
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": sec_per_step * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "paged_attention_decode batch64/GPU hq32 hkv8 d128 block128 "
+                               "ctx U[1024,8192] q_len1", "l2": "inputs (1.2 GB/GPU) larger than L2",
+                   "kv_bytes_per_step_per_gpu": kv_bytes_of(d)},
+        "tokens_per_s": total_seq / sec_per_step,
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES, "peak_source": which,
+                     "note": "achieved = algorithmic bytes of one step / CUDA-event time of the step "
+                             "(pa_decode_kernel + pa_merge_kernel), rank 0"},
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "note": "run()-style call with every tensor on the host, KV pools included",
+                "resident_kv_cache_value": e2e_res},
+    }
+    print(json.dumps(line), flush=True)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU legs (used for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 5:

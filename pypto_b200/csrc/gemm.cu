@@ -1,0 +1,299 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM,
+// operands staged by TMA), with the epilogues the fused operators need.
+//
+//   D[a_row, b_row] = sum_k A[a_row, k] * B[b_row, k]        (both operands K-major bf16)
+//
+// It stands where the reference runs `matmul_kernel` / `pl.matmul` tiles with every
+// intermediate written back to global memory (examples/models/01_ffn.py:37-45, 112-131;
+// examples/models/qwen3_jit/kernels/projection.py:36-177, kernels/mlp.py:23-61): fp32
+// accumulation of bf16 operands, the rule of python/pypto/debug/torch_codegen.py:1078-1086.
+//
+// Orientation.  TMEM lanes hold A rows (128 per tile), TMEM columns hold B rows (bn per
+// tile).  For a prefill-sized activation matrix A = activations, B = weights [N, K].
+// For decode (a few dozen tokens) the operands are swapped: A = weights, so that the 128
+// lanes are filled by output features and the token count becomes the small N of the
+// MMA; the output is then written transposed (`swap`).
+//
+// Work units.  unit = (A tile, B tile, K chunk); CTAs are persistent and take units
+// round-robin.  With more than one K chunk the partial sums are added to the output
+// with red.global.add.f32 (the output then has to be initialised by the caller: zeros,
+// or the residual that the reference adds after the projection).
+//
+// CTA = 6 warps: warp 0 TMA producer, warp 1 MMA issuer (owns the TMEM allocation),
+// warps 2-5 epilogue (TMEM -> registers -> global).  smem ring of (A, B[, B2]) stages with
+// full/empty mbarriers; two TMEM accumulator buffers so that the epilogue of unit i
+// overlaps the main loop of unit i+1.  All waits are bounded.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace pto {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;  // bf16 elements per stage row = 128 bytes = one swizzle atom
+constexpr int kGemmThreads = 192;
+constexpr int kMaxStages = 12;
+
+struct GemmParams {
+  int a_rows, b_rows, k;
+  int a_tiles, b_tiles, k_chunks, kblocks_per_chunk, kblocks_total;
+  int units;
+  int bn;
+  int dual, dual_off;  // SwiGLU: second B tile (up weights) at row offset dual_off
+  int swap;            // out[b_row * ldo + a_row] instead of out[a_row * ldo + b_row]
+  int epi;             // GemmEpi
+  int out_bf16;
+  int stages;
+  void* out;
+  long long ldo;
+  int* err;
+};
+
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  // sigmoid as recip(1 + exp(-g)), the form of examples/models/01_ffn.py:66-77
+  return g * (1.f / (1.f + __expf(-g))) * u;
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const int nacc = p.dual ? 2 : 1;
+  const uint32_t a_bytes = kBM * 128;
+  const uint32_t b_bytes = p.bn * 128;
+  const uint32_t stage_bytes = a_bytes + nacc * b_bytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
+  uint64_t* empty = full + kMaxStages;
+  uint64_t* tmem_full = empty + kMaxStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t acc_cols = nacc * p.bn;
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < 2 * acc_cols) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < p.stages; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+        const int kc = u % p.k_chunks;
+        const int bt = (u / p.k_chunks) % p.b_tiles;
+        const int at = u / (p.k_chunks * p.b_tiles);
+        const int kb0 = kc * p.kblocks_per_chunk;
+        const int kb1 = min(p.kblocks_total, kb0 + p.kblocks_per_chunk);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const uint32_t s = it % p.stages, round = it / p.stages;
+          if (!mbar_wait(&empty[s], (round & 1u) ^ 1u)) {
+            report_error(p.err, kErrBarrierTimeout, 40, static_cast<int>(it));
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
+          mbar_arrive_expect_tx(&full[s], stage_bytes);
+          tma_load_2d(st, &tm_a, kb * kBK, at * kBM, &full[s]);
+          tma_load_2d(st + a_bytes, &tm_b, kb * kBK, bt * p.bn, &full[s]);
+          if (p.dual) tma_load_2d(st + a_bytes + b_bytes, &tm_b, kb * kBK, p.dual_off + bt * p.bn, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(kBM, p.bn, 1, 1);
+      uint32_t it = 0, ui = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x, ++ui) {
+        const int kc = u % p.k_chunks;
+        const int kb0 = kc * p.kblocks_per_chunk;
+        const int kb1 = min(p.kblocks_total, kb0 + p.kblocks_per_chunk);
+        const uint32_t ab = ui & 1u;
+        if (!mbar_wait(&tmem_empty[ab], ((ui >> 1) & 1u) ^ 1u)) {
+          report_error(p.err, kErrBarrierTimeout, 41, static_cast<int>(ui));
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d0 = tmem_base + ab * acc_cols;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const uint32_t s = it % p.stages, round = it / p.stages;
+          if (!mbar_wait(&full[s], round & 1u)) {
+            report_error(p.err, kErrBarrierTimeout, 42, static_cast<int>(it));
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
+          const uint32_t b_addr = a_addr + a_bytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint32_t acc = (kb > kb0 || k > 0) ? 1u : 0u;
+            const uint64_t ad = umma_desc_sw128(a_addr + k * 32);
+            umma_bf16(d0, ad, umma_desc_sw128(b_addr + k * 32), idesc, acc);
+            if (p.dual) umma_bf16(d0 + p.bn, ad, umma_desc_sw128(b_addr + b_bytes + k * 32), idesc, acc);
+          }
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&tmem_full[ab]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t ui = 0;
+    for (int u = blockIdx.x; u < p.units; u += gridDim.x, ++ui) {
+      const int bt = (u / p.k_chunks) % p.b_tiles;
+      const int at = u / (p.k_chunks * p.b_tiles);
+      const uint32_t ab = ui & 1u;
+      if (!mbar_wait(&tmem_full[ab], (ui >> 1) & 1u)) {
+        report_error(p.err, kErrBarrierTimeout, 43, static_cast<int>(ui));
+        break;
+      }
+      tc_fence_after_sync();
+      const int a_row = at * kBM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * acc_cols;
+      for (int c0 = 0; c0 < p.bn; c0 += 32) {
+        uint32_t v[32], w[32];
+        tmem_ld_32x32(taddr + c0, v);
+        if (p.dual) tmem_ld_32x32(taddr + p.bn + c0, w);
+        tmem_ld_wait();
+        const int b_row0 = bt * p.bn + c0;
+        if (p.epi == kGemmEpiSwiglu) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(silu_mul(__uint_as_float(v[j]), __uint_as_float(w[j])));
+        }
+        if (a_row < p.a_rows) {
+          if (p.swap) {
+            // out[(b_row0 + j) * ldo + a_row]: the warp's lanes are consecutive a_row
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (b_row0 + j >= p.b_rows) break;
+              const long long o = static_cast<long long>(b_row0 + j) * p.ldo + a_row;
+              const float x = __uint_as_float(v[j]);
+              if (p.epi == kGemmEpiAtomic) red_add_f32(static_cast<float*>(p.out) + o, x);
+              else if (p.out_bf16) static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(x);
+              else static_cast<float*>(p.out)[o] = x;
+            }
+          } else {
+            const long long o = static_cast<long long>(a_row) * p.ldo + b_row0;
+            const bool full_row = b_row0 + 32 <= p.b_rows;
+            if (p.epi == kGemmEpiAtomic) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (b_row0 + j < p.b_rows) red_add_f32(static_cast<float*>(p.out) + o + j, __uint_as_float(v[j]));
+            } else if (p.out_bf16) {
+              __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + o;
+              if (full_row && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 pk;
+                  pk.x = pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                  pk.y = pack_bf16x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                  pk.z = pack_bf16x2(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                  pk.w = pack_bf16x2(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                  *reinterpret_cast<uint4*>(dst + j) = pk;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (b_row0 + j < p.b_rows) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+              }
+            } else {
+              float* dst = static_cast<float*>(p.out) + o;
+              if (full_row && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  *reinterpret_cast<uint4*>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (b_row0 + j < p.b_rows) dst[j] = __uint_as_float(v[j]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[ab]);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+}  // namespace
+
+int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total, int b_rows, int k, void* out,
+                     long long ldo, int out_bf16, int swap, int epi, int dual_off, int bn, int k_chunks,
+                     int* err, cudaStream_t stream) {
+  PTO_REQUIRE(a && b && out, "gemm: NULL operand");
+  PTO_REQUIRE(a_rows > 0 && b_rows > 0 && k > 0, "gemm: empty problem");
+  PTO_REQUIRE(k % 8 == 0, "gemm: K must be a multiple of 8 (16-byte rows)");
+  PTO_REQUIRE(bn == 32 || bn == 64 || bn == 128 || bn == 256, "gemm: bn must be 32, 64, 128 or 256");
+  const int dual = epi == kGemmEpiSwiglu ? 1 : 0;
+  PTO_REQUIRE(!dual || (bn <= 128 && !swap), "gemm: SwiGLU epilogue needs bn <= 128 and the normal orientation");
+  PTO_REQUIRE(k_chunks >= 1 && (k_chunks == 1 || epi == kGemmEpiAtomic), "gemm: split-K needs the atomic epilogue");
+  PTO_REQUIRE(epi != kGemmEpiAtomic || !out_bf16, "gemm: atomic epilogue accumulates in fp32");
+
+  GemmParams p;
+  p.a_rows = a_rows; p.b_rows = b_rows; p.k = k;
+  p.a_tiles = (a_rows + kBM - 1) / kBM;
+  p.b_tiles = (b_rows + bn - 1) / bn;
+  p.kblocks_total = (k + kBK - 1) / kBK;
+  if (k_chunks > p.kblocks_total) k_chunks = p.kblocks_total;
+  p.kblocks_per_chunk = (p.kblocks_total + k_chunks - 1) / k_chunks;
+  p.k_chunks = (p.kblocks_total + p.kblocks_per_chunk - 1) / p.kblocks_per_chunk;
+  p.units = p.a_tiles * p.b_tiles * p.k_chunks;
+  p.bn = bn; p.dual = dual; p.dual_off = dual_off; p.swap = swap; p.epi = epi; p.out_bf16 = out_bf16;
+  p.out = out; p.ldo = ldo; p.err = err;
+  const int stage_bytes = kBM * 128 + (dual ? 2 : 1) * bn * 128;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) stages = 2;
+  p.stages = stages;
+  const size_t smem = 1024 + static_cast<size_t>(stages) * stage_bytes + (2 * kMaxStages + 4) * 8 + 16;
+
+  CUtensorMap tm_a, tm_b;
+  int st = make_tensor_map_2d(&tm_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_rows, k, static_cast<uint64_t>(k) * 2,
+                              kBK, kBM, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (st != kOk) return st;
+  st = make_tensor_map_2d(&tm_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_rows_total, k,
+                          static_cast<uint64_t>(k) * 2, kBK, bn, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (st != kOk) return st;
+  static bool attr_set = false;
+  if (!attr_set) {
+    PTO_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    attr_set = true;
+  }
+  int grid = sm_count();
+  if (grid > p.units) grid = p.units;
+  gemm_bf16_kernel<<<grid, kGemmThreads, smem, stream>>>(tm_a, tm_b, p);
+  return check_cuda(cudaGetLastError(), "gemm_bf16_kernel launch");
+}
+
+}  // namespace pto

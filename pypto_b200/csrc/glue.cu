@@ -1,0 +1,221 @@
+// Decoder-layer glue kernels: RMSNorm, RoPE + paged KV-cache append, SwiGLU activation,
+// casts, and the one-time weight packing ([K, N] row-major -> [N, K] bf16, the K-major
+// operand layout of the tensor-core GEMM).  All are bandwidth-bound elementwise / row
+// kernels with 16-byte accesses where the shapes allow.
+//
+// Reference semantics:
+//   RMSNorm   x * rsqrt(mean(x^2) + eps) * gamma, fp32 statistics, bf16 round at the end
+//             (examples/models/qwen3_jit/kernels/rmsnorm.py:27-89;
+//              tests/st/runtime/framework_and_models/test_qwen3_decode_scope3_mixed.py:278-280)
+//   RoPE      rotate-half with cos/sin table rows at pos = seq_len - 1, rotated K and the V row
+//             written to the cache as bf16, rotated Q as bf16
+//             (examples/models/qwen3_jit/kernels/attention.py:40-111)
+//   SwiGLU    bf16(gate * sigmoid(gate) * up) (examples/models/qwen3_jit/kernels/mlp.py:23-61)
+#include "common.cuh"
+#include "kernels.h"
+
+namespace pto {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) r += red[i];
+  return r;
+}
+
+// One CTA (256 threads) per row.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+rms_norm_kernel(const TI* __restrict__ x, const float* __restrict__ gamma, TO* __restrict__ out, int hidden,
+                float eps) {
+  __shared__ float red[8];
+  const TI* xr = x + static_cast<size_t>(blockIdx.x) * hidden;
+  TO* orow = out + static_cast<size_t>(blockIdx.x) * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += 256) {
+    const float v = to_f32(xr[i]);
+    ss += v * v;
+  }
+  const float mean = block_sum_256(ss, red) / static_cast<float>(hidden);
+  const float inv = rsqrtf(mean + eps);
+  for (int i = threadIdx.x; i < hidden; i += 256) {
+    const float g = gamma ? gamma[i] : 1.f;
+    orow[i] = from_f32<TO>(to_f32(xr[i]) * inv * g);
+  }
+}
+
+// grid = (batch, num_heads + kv_heads); block = head_dim / 2 threads.
+// qkv fp32 [batch, (num_heads + 2 kv_heads) * D]: q heads, then k heads, then v heads.
+__global__ void rope_kv_append_kernel(const float* __restrict__ qkv, const int* __restrict__ seq_lens,
+                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                      int table_rows, const int* __restrict__ block_table, int max_blocks,
+                                      __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                      __nv_bfloat16* __restrict__ q_out, int num_heads, int kv_heads, int head_dim,
+                                      int block_size, int pool_blocks, int* err) {
+  const int b = blockIdx.x, h = blockIdx.y, i = threadIdx.x, half = head_dim / 2;
+  const int len = seq_lens[b];
+  int pos = len - 1;
+  if (pos < 0 || pos >= table_rows || pos / block_size >= max_blocks) {
+    if (i == 0) report_error(err, kErrBadBlockId, 4, pos);
+    return;
+  }
+  const size_t row_w = static_cast<size_t>(num_heads + 2 * kv_heads) * head_dim;
+  const float* src = qkv + b * row_w + static_cast<size_t>(h) * head_dim;
+  const float c_lo = cos_t[static_cast<size_t>(pos) * head_dim + i];
+  const float c_hi = cos_t[static_cast<size_t>(pos) * head_dim + half + i];
+  const float s_lo = sin_t[static_cast<size_t>(pos) * head_dim + i];
+  const float s_hi = sin_t[static_cast<size_t>(pos) * head_dim + half + i];
+  const float lo = src[i], hi = src[half + i];
+  const float r_lo = lo * c_lo - hi * s_lo;
+  const float r_hi = hi * c_hi + lo * s_hi;
+  if (h < num_heads) {
+    __nv_bfloat16* dst = q_out + (static_cast<size_t>(b) * num_heads + h) * head_dim;
+    dst[i] = __float2bfloat16_rn(r_lo);
+    dst[half + i] = __float2bfloat16_rn(r_hi);
+    return;
+  }
+  const int ki = h - num_heads;
+  const int blk = block_table[static_cast<size_t>(b) * max_blocks + pos / block_size];
+  if (blk < 0 || blk >= pool_blocks) {
+    if (i == 0) report_error(err, kErrBadBlockId, 5, blk);
+    return;
+  }
+  const size_t row = (static_cast<size_t>(blk) * kv_heads + ki) * block_size + pos % block_size;
+  k_cache[row * head_dim + i] = __float2bfloat16_rn(r_lo);
+  k_cache[row * head_dim + half + i] = __float2bfloat16_rn(r_hi);
+  const float* vsrc = qkv + b * row_w + static_cast<size_t>(num_heads + kv_heads + ki) * head_dim;
+  v_cache[row * head_dim + i] = __float2bfloat16_rn(vsrc[i]);
+  v_cache[row * head_dim + half + i] = __float2bfloat16_rn(vsrc[half + i]);
+}
+
+// gate_up fp32 [rows, 2 * inter] (gate columns first) -> act bf16 [rows, inter]
+__global__ void swiglu_act_kernel(const float* __restrict__ gate_up, __nv_bfloat16* __restrict__ act, long long rows,
+                                  int inter) {
+  const long long n = rows * inter;
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < n;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = idx / inter;
+    const int c = static_cast<int>(idx - r * inter);
+    const float g = gate_up[r * 2 * inter + c], u = gate_up[r * 2 * inter + inter + c];
+    act[idx] = __float2bfloat16_rn(g * (1.f / (1.f + __expf(-g))) * u);
+  }
+}
+
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, long long n) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    out[i] = from_f32<TO>(to_f32(in[i]));
+}
+
+// src [K, N] row-major -> dst [N, K] bf16; 32x32 tiles through shared memory.
+template <typename TI>
+__global__ void __launch_bounds__(256) pack_weight_kernel(const TI* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                                          int k, int n) {
+  __shared__ float tile[32][33];
+  const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int r = ty; r < 32; r += 8) {
+    const int kk = k0 + r, nn = n0 + tx;
+    tile[r][tx] = (kk < k && nn < n) ? to_f32(src[static_cast<size_t>(kk) * n + nn]) : 0.f;
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    const int nn = n0 + r, kk = k0 + tx;
+    if (nn < n && kk < k) dst[static_cast<size_t>(nn) * k + kk] = __float2bfloat16_rn(tile[tx][r]);
+  }
+}
+
+int grid_for(long long n, int block) {
+  long long g = (n + block - 1) / block;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace
+
+int rms_norm_launch(const void* x, int x_dtype, const float* gamma, void* out, int out_dtype, long long rows,
+                    int hidden, float eps, cudaStream_t stream) {
+  PTO_REQUIRE(x && out && rows >= 0 && hidden > 0, "rms_norm: bad arguments");
+  if (rows == 0) return kOk;
+  const unsigned g = static_cast<unsigned>(rows);
+  if (x_dtype == PTO_BF16 && out_dtype == PTO_BF16)
+    rms_norm_kernel<__nv_bfloat16, __nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), gamma, static_cast<__nv_bfloat16*>(out), hidden, eps);
+  else if (x_dtype == PTO_FP32 && out_dtype == PTO_BF16)
+    rms_norm_kernel<float, __nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const float*>(x), gamma, static_cast<__nv_bfloat16*>(out), hidden, eps);
+  else if (x_dtype == PTO_FP32 && out_dtype == PTO_FP32)
+    rms_norm_kernel<float, float><<<g, 256, 0, stream>>>(static_cast<const float*>(x), gamma, static_cast<float*>(out), hidden, eps);
+  else if (x_dtype == PTO_BF16 && out_dtype == PTO_FP32)
+    rms_norm_kernel<__nv_bfloat16, float><<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), gamma, static_cast<float*>(out), hidden, eps);
+  else
+    return fail(kInvalidArgument, "rms_norm: dtypes must be fp32 or bf16");
+  return check_cuda(cudaGetLastError(), "rms_norm_kernel launch");
+}
+
+int rope_kv_append_launch(const float* qkv, const int32_t* seq_lens, const float* cos_t, const float* sin_t,
+                          int table_rows, const int32_t* block_table, int max_blocks, void* k_cache, void* v_cache,
+                          void* q_out, int batch, int num_heads, int kv_heads, int head_dim, int block_size,
+                          long long pool_blocks, int* err, cudaStream_t stream) {
+  PTO_REQUIRE(qkv && seq_lens && cos_t && sin_t && block_table && k_cache && v_cache && q_out, "rope: NULL tensor");
+  PTO_REQUIRE(head_dim % 2 == 0 && head_dim <= 2048 && num_heads > 0 && kv_heads > 0, "rope: bad head geometry");
+  if (batch == 0) return kOk;
+  dim3 grid(batch, num_heads + kv_heads);
+  rope_kv_append_kernel<<<grid, head_dim / 2, 0, stream>>>(
+      qkv, seq_lens, cos_t, sin_t, table_rows, block_table, max_blocks, static_cast<__nv_bfloat16*>(k_cache),
+      static_cast<__nv_bfloat16*>(v_cache), static_cast<__nv_bfloat16*>(q_out), num_heads, kv_heads, head_dim,
+      block_size, static_cast<int>(pool_blocks), err);
+  return check_cuda(cudaGetLastError(), "rope_kv_append_kernel launch");
+}
+
+int swiglu_act_launch(const float* gate_up, void* act, long long rows, int inter, cudaStream_t stream) {
+  PTO_REQUIRE(gate_up && act && rows >= 0 && inter > 0, "swiglu_act: bad arguments");
+  if (rows == 0) return kOk;
+  swiglu_act_kernel<<<grid_for(rows * inter, 256), 256, 0, stream>>>(gate_up, static_cast<__nv_bfloat16*>(act), rows, inter);
+  return check_cuda(cudaGetLastError(), "swiglu_act_kernel launch");
+}
+
+int cast_launch(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream) {
+  PTO_REQUIRE(in && out && n >= 0, "cast: bad arguments");
+  if (n == 0) return kOk;
+  const int g = grid_for(n, 256);
+  if (in_dtype == PTO_FP32 && out_dtype == PTO_BF16)
+    cast_kernel<float, __nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const float*>(in), static_cast<__nv_bfloat16*>(out), n);
+  else if (in_dtype == PTO_BF16 && out_dtype == PTO_FP32)
+    cast_kernel<__nv_bfloat16, float><<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), static_cast<float*>(out), n);
+  else
+    return fail(kInvalidArgument, "cast: only fp32 <-> bf16");
+  return check_cuda(cudaGetLastError(), "cast_kernel launch");
+}
+
+int pack_weight_launch(const void* src, int src_dtype, void* dst, int k, int n, cudaStream_t stream) {
+  PTO_REQUIRE(src && dst && k > 0 && n > 0, "pack_weight: bad arguments");
+  dim3 grid((n + 31) / 32, (k + 31) / 32);
+  if (src_dtype == PTO_FP32)
+    pack_weight_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(src), static_cast<__nv_bfloat16*>(dst), k, n);
+  else if (src_dtype == PTO_BF16)
+    pack_weight_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), k, n);
+  else
+    return fail(kInvalidArgument, "pack_weight: source must be fp32 or bf16");
+  return check_cuda(cudaGetLastError(), "pack_weight_kernel launch");
+}
+
+}  // namespace pto

@@ -1,0 +1,39 @@
+"""Handle to a buffer resident on a worker (python/pypto/runtime/device_tensor.py:43-112)."""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+
+class DeviceTensor:
+    __slots__ = ("data_ptr", "shape", "dtype", "buffer")
+
+    def __init__(self, data_ptr: int, shape: Sequence[int], dtype: torch.dtype, *, buffer=None):
+        if isinstance(data_ptr, bool) or not isinstance(data_ptr, int) or data_ptr <= 0:
+            raise ValueError(f"DeviceTensor.data_ptr must be a positive int, got {data_ptr!r}")
+        shape = tuple(shape)
+        for d in shape:
+            if isinstance(d, bool) or not isinstance(d, int):
+                raise TypeError(f"DeviceTensor.shape must contain ints, got {shape!r}")
+        if not shape:
+            raise ValueError("DeviceTensor.shape must be non-empty")
+        if any(d <= 0 for d in shape):
+            raise ValueError(f"DeviceTensor.shape must be all positive, got {shape}")
+        if not isinstance(dtype, torch.dtype):
+            raise TypeError(f"DeviceTensor.dtype must be torch.dtype, got {type(dtype).__name__}")
+        self.data_ptr, self.shape, self.dtype, self.buffer = data_ptr, shape, dtype, buffer
+
+    @property
+    def nbytes(self) -> int:
+        n = 1
+        for d in self.shape:
+            n *= d
+        return n * torch.empty(0, dtype=self.dtype).element_size()
+
+    def numel(self) -> int:
+        return self.nbytes // torch.empty(0, dtype=self.dtype).element_size()
+
+    def __repr__(self):
+        return f"DeviceTensor(data_ptr=0x{self.data_ptr:x}, shape={self.shape}, dtype={self.dtype})"

@@ -1,0 +1,177 @@
+"""Fused-operator table: orchestration entry -> CUDA kernel launcher.
+
+Each entry knows the parameter list of one reference program (names, order, directions)
+and how to turn a call into ``ChipWorker.launch(op, tensors, scalars)``.  A program whose
+entry is not in the table has no kernel here and ``lookup`` raises.
+
+(Annotations in this file must be evaluated eagerly -- the program builders below put
+shapes from local variables into them -- so postponed evaluation is not enabled here.)
+"""
+
+import struct
+
+import torch
+
+from .. import language as pl
+from ..language import Direction
+
+
+class FusedOp:
+    op_names: tuple[str, ...] = ()
+
+    def matches(self, entry) -> bool:
+        raise NotImplementedError
+
+    def plan(self, compiled, host: dict, worker) -> dict:
+        return {}
+
+    def launch(self, worker, dev: dict, host: dict, plan: dict) -> None:
+        raise NotImplementedError
+
+
+def _host_values(t, worker) -> list[int]:
+    """Integer contents of a small tensor argument, wherever it lives."""
+    from .device_tensor import DeviceTensor
+    if isinstance(t, DeviceTensor):
+        t = worker.read_tensor(t)
+    return [int(v) for v in t.flatten().tolist()]
+
+
+class PagedAttentionOp(FusedOp):
+    """``paged_attention(query, key_cache, value_cache, block_table, context_lens, out, config)``
+    (examples/models/04_paged_attention.py:272-283).  ``config`` is the int64 tensor
+    [batch, num_heads, kv_head_num, head_dim, block_size, block_num, scale_bits] (:287); an
+    optional eighth entry carries q_len (an extension, 1 when absent).  The scale is taken
+    from config[6] as the golden does (:489-491)."""
+
+    op_names = ("paged_attention",)
+    names = ("query", "key_cache", "value_cache", "block_table", "context_lens", "out", "config")
+
+    def matches(self, entry) -> bool:
+        return entry.name in ("paged_attention", "paged_attention_unaligned") and \
+            tuple(p.name for p in entry.params) == self.names
+
+    def plan(self, compiled, host, worker):
+        cfg = _host_values(host["config"], worker)
+        if len(cfg) < 7:
+            raise ValueError("config must hold at least 7 int64 entries")
+        batch, heads, kvh, hd, bs, nblk, bits = cfg[:7]
+        q_len = cfg[7] if len(cfg) > 7 else 1
+        kvh = max(kvh, 1)
+        q, out = host["query"], host["out"]
+        if q.dtype != torch.bfloat16:
+            raise TypeError("query must be bfloat16")
+        numel = batch * q_len * heads * hd
+        if _numel(q) != numel or _numel(out) != numel:
+            raise ValueError(f"query/out hold {_numel(q)}/{_numel(out)} elements; config implies {numel}")
+        if _numel(host["block_table"]) != batch * nblk:
+            raise ValueError("block_table size does not match batch * block_num from config")
+        if _numel(host["context_lens"]) != batch:
+            raise ValueError("context_lens size does not match batch from config")
+        return dict(scalars=[batch, heads, kvh, hd, bs, nblk, q_len, bits & 0xFFFFFFFF], host_only=("config",))
+
+    def launch(self, worker, dev, host, plan):
+        worker.launch("paged_attention", [dev[n] for n in self.names[:6]], plan["scalars"])
+
+
+def _numel(t) -> int:
+    n = 1
+    for s in t.shape:
+        n *= s
+    return n
+
+
+class PagedGatherOp(FusedOp):
+    """``paged_gather(src, indices, block_table, out)`` with block size / column window taken
+    from the shapes: out[i, :] = src[block_table[idx // bs] * bs + idx % bs, :size]
+    (tests/st/runtime/ops/test_paged_gather.py:14-17).  bs = src rows / block_table length."""
+
+    op_names = ("paged_gather",)
+    names = ("src", "indices", "block_table", "out")
+
+    def matches(self, entry) -> bool:
+        return entry.name == "paged_gather" and tuple(p.name for p in entry.params) == self.names
+
+    def plan(self, compiled, host, worker):
+        src, bt, out = host["src"], host["block_table"], host["out"]
+        rows, nb = src.shape[0], _numel(bt)
+        if nb == 0 or rows % nb:
+            raise ValueError("src rows must be a multiple of the block table length")
+        return dict(scalars=[rows // nb, 0, out.shape[-1]])
+
+    def launch(self, worker, dev, host, plan):
+        worker.launch("paged_gather", [dev[n] for n in self.names], plan["scalars"])
+
+
+REGISTRY: list[FusedOp] = [PagedAttentionOp(), PagedGatherOp()]
+
+
+def lookup(entry) -> FusedOp:
+    for op in REGISTRY:
+        if op.matches(entry):
+            return op
+    sig = ", ".join(p.name for p in entry.params)
+    raise NotImplementedError(f"no fused kernel registered for program entry '{entry.name}({sig})'; "
+                              "this backend runs fused operators only and has no CPU fallback")
+
+
+# ---------------------------------------------------------------------------
+# Programs written against the compatibility surface (same style as the reference
+# examples: typed signature, DSL body never executed here).
+# ---------------------------------------------------------------------------
+
+def paged_attention_program(batch, num_heads, head_dim, block_size, max_blocks, kv_heads=1, q_len=1,
+                            out_dtype=torch.float32, pool_rows=None):
+    q_rows = batch * q_len * num_heads
+    table = batch * max_blocks
+    out_t = pl.dtype_of(out_dtype)
+    cfg_len = 8 if q_len != 1 else 7
+    kv_shape = [pool_rows, head_dim] if pool_rows else None
+    kv_type = pl.Tensor[kv_shape, pl.BF16] if kv_shape else pl.Tensor[pl.BF16]
+
+    @pl.program
+    class PagedAttention:
+        @pl.function(type=pl.FunctionType.Orchestration)
+        def paged_attention(self,
+                            query: pl.Tensor[[q_rows, head_dim], pl.BF16],
+                            key_cache: kv_type,
+                            value_cache: kv_type,
+                            block_table: pl.Tensor[[table], pl.INT32],
+                            context_lens: pl.Tensor[[batch], pl.INT32],
+                            out: pl.Out[pl.Tensor[[q_rows, head_dim], out_t]],
+                            config: pl.Tensor[[cfg_len], pl.INT64]):
+            ...
+
+    return PagedAttention
+
+
+def pack_config(d: dict) -> torch.Tensor:
+    """int64 config tensor for ``paged_attention_program`` from an input dict
+    (batch, num_heads, kv_heads, head_dim, block_size, max_blocks, scale[, q_len])."""
+    bits = struct.unpack("I", struct.pack("f", float(d["scale"])))[0]
+    vals = [d["batch"], d["num_heads"], d["kv_heads"], d["head_dim"], d["block_size"], d["max_blocks"], bits]
+    if d.get("q_len", 1) != 1:
+        vals.append(d["q_len"])
+    return torch.tensor(vals, dtype=torch.int64)
+
+
+def time_resident(compiled, d, host, host_out, cfg_t, steps, dev) -> float:
+    """Seconds per step with the KV pools resident on the worker as DeviceTensors (the
+    reference's own benchmarking recipe: allocate once, register once, loop the handle:
+    python/pypto/runtime/bench.py:1267-1340); per step the query, tables and lengths go
+    host->device and the output comes back."""
+    import time
+
+    from .run_config import RunConfig
+    from .worker import ChipWorker
+    with ChipWorker(RunConfig(platform="b200", device_id=dev.index or 0)) as w:
+        kc = w.alloc_tensor(d["key_cache"].shape, d["key_cache"].dtype, init=d["key_cache"])
+        vc = w.alloc_tensor(d["value_cache"].shape, d["value_cache"].dtype, init=d["value_cache"])
+        handle = w.register(compiled)
+        args = (host["query"], kc, vc, host["block_table"].flatten(), host["context_lens"], host_out, cfg_t)
+        handle(*args)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            handle(*args)
+        dt = (time.perf_counter() - t0) / steps
+    return dt

@@ -1,0 +1,160 @@
+"""Host-side behaviour of the launch surface (no GPU): the specs follow the reference's own
+unit tests -- tests/ut/runtime/test_run_config.py, tests/ut/runtime/test_device_tensor.py,
+tests/ut/ir/test_compiled_program.py, tests/ut/backend/test_backend_handler.py."""
+
+import os
+
+import pytest
+import torch
+
+import pypto_b200.language as pl
+from pypto_b200 import BackendUnavailable, backend, ir
+from pypto_b200.backend import BackendType
+from pypto_b200.runtime import DeviceTensor, RunConfig, TensorSpec, fused_programs, validate_golden
+
+
+def test_run_config_platform_drives_backend():
+    assert RunConfig().platform == "b200" and RunConfig().backend_type is BackendType.CudaSM100
+    c = RunConfig(platform="a5sim", backend_type=BackendType.Ascend910B)
+    assert c.backend_type is BackendType.Ascend950  # platform wins (test_run_config.py:35)
+    with pytest.raises(ValueError):
+        RunConfig(platform="h100")
+
+
+def test_run_config_dfx_flags_force_save_kernels():
+    assert RunConfig(enable_pmu=1).save_kernels is True   # test_run_config.py:72
+    assert RunConfig(enable_chip_swimlane=True).enable_chip_swimlane == 4
+    assert RunConfig().save_kernels is False
+    with pytest.raises(ValueError):
+        RunConfig(enable_chip_swimlane=9)
+
+
+def test_run_config_ring_overrides_validated():
+    assert RunConfig(ring_heap=(1, 2, 3, 4)).ring_heap == [1, 2, 3, 4]   # test_run_config.py:297-326
+    for bad in ([1, 2, 3], -1, [1, 2, 3, -4], "8", True):
+        with pytest.raises(ValueError):
+            RunConfig(ring_task_window=bad)
+
+
+def test_backend_registry_and_handler():
+    backend.reset_for_testing()
+    b = backend.get_backend_instance(BackendType.CudaSM100)
+    assert b is backend.get_backend_instance(BackendType.CudaSM100)
+    assert b.get_type_name() == "CudaSM100"
+    h = b.get_handler()
+    assert h.get_pto_target_arch() == "b200" and h.get_cuda_arch() == "sm_100a" and h.can_execute()
+    assert not backend.get_backend_instance(BackendType.Ascend910B).get_handler().can_execute()
+    assert "paged_attention" in b.get_op_names()
+    backend.set_backend_type(BackendType.CudaSM100)
+    backend.set_backend_type(BackendType.CudaSM100)
+    with pytest.raises(RuntimeError):
+        backend.set_backend_type(BackendType.Ascend950)
+    backend.reset_for_testing()
+    with pytest.raises(RuntimeError):
+        backend.get_backend_type()
+
+
+def test_device_tensor_validation():
+    t = DeviceTensor(4096, (2, 3), torch.bfloat16)
+    assert t.nbytes == 12 and "0x1000" in repr(t)
+    for args in [(0, (1,), torch.float32), (True, (1,), torch.float32), (8, (), torch.float32),
+                 (8, (0,), torch.float32)]:
+        with pytest.raises(ValueError):
+            DeviceTensor(*args)
+    with pytest.raises(TypeError):
+        DeviceTensor(8, (1.5,), torch.float32)
+    with pytest.raises(TypeError):
+        DeviceTensor(8, (1,), "float32")
+
+
+def test_tensor_spec_create():
+    assert TensorSpec("a", [2, 2], torch.float32, init_value=3).create_tensor().sum() == 12
+    assert TensorSpec("b", [4], torch.int32).create_tensor().dtype == torch.int32
+    assert TensorSpec("c", [3], torch.float32, init_value=torch.ones).create_tensor().sum() == 3
+    assert TensorSpec("d", [2], torch.float32, init_value=lambda: [1, 2]).create_tensor().tolist() == [1, 2]
+
+
+def test_program_signature_capture_and_lookup():
+    prog = fused_programs.paged_attention_program(2, 16, 128, 128, 4)
+    e = prog.entry
+    assert e.name == "paged_attention" and [p.name for p in e.params][-2:] == ["out", "config"]
+    assert e.params[5].direction is pl.Direction.Out and e.params[0].type.shape == (32, 128)
+    c = ir.compile(prog, platform="b200")
+    assert c.op_names == ("paged_attention",)
+    with pytest.raises(RuntimeError):
+        e(1, 2)  # DSL bodies are not executable Python
+
+
+def test_unknown_program_has_no_kernel_and_no_fallback():
+    @pl.program
+    class Mystery:
+        @pl.function(type=pl.FunctionType.Orchestration)
+        def conv3d(self, x: pl.Tensor[[4, 4], pl.FP32], y: pl.Out[pl.Tensor[[4, 4], pl.FP32]]):
+            ...
+    with pytest.raises(NotImplementedError, match="no fused kernel"):
+        ir.compile(Mystery, platform="b200")
+    with pytest.raises(BackendUnavailable):
+        ir.compile(Mystery, platform="a2a3")
+
+
+def test_argument_coercion_errors_raise_in_python():
+    c = ir.compile(fused_programs.paged_attention_program(2, 16, 128, 128, 4), platform="b200")
+    q = torch.zeros(32, 128, dtype=torch.bfloat16)
+    kv = torch.zeros(1024, 128, dtype=torch.bfloat16)
+    bt, cl = torch.zeros(8, dtype=torch.int32), torch.zeros(2, dtype=torch.int32)
+    out, cfg = torch.zeros(32, 128), torch.zeros(7, dtype=torch.int64)
+    with pytest.raises(TypeError, match="takes 7 arguments"):
+        c._coerce_args((q, kv))
+    with pytest.raises(TypeError, match="dtype"):
+        c._coerce_args((q.float(), kv, kv, bt, cl, out, cfg))
+    with pytest.raises(ValueError, match="shape"):
+        c._coerce_args((q[:16], kv, kv, bt, cl, out, cfg))
+    with pytest.raises(ValueError, match="contiguous"):
+        c._coerce_args((q, kv, kv, bt, cl, out.t().contiguous().t(), cfg))
+    with pytest.raises(TypeError, match="torch.Tensor"):
+        c._coerce_args((q, kv, kv, [0] * 8, cl, out, cfg))
+    full, returned = c._coerce_args((q, kv, kv, bt, cl, cfg))   # return style: out allocated
+    assert len(full) == 7 and returned[0].shape == (32, 128) and returned[0].dtype == torch.float32
+
+
+def test_validate_golden_nan_is_dont_care():
+    exp = torch.tensor([1.0, float("nan"), 3.0])
+    validate_golden({"y": torch.tensor([1.0, 99.0, 3.0])}, {"y": exp})
+    with pytest.raises(AssertionError, match="does not match"):
+        validate_golden({"y": torch.tensor([1.0, 2.0, 3.5])}, {"y": exp})
+
+
+def test_jit_cache_key_and_decorators():
+    @pl.jit
+    def paged_gather(src: pl.Tensor, indices: pl.Tensor, block_table: pl.Tensor, out: pl.Out[pl.Tensor]):
+        ...
+
+    @pl.jit.incore
+    def helper(x: pl.Tensor):
+        ...
+    a = (torch.zeros(32, 8), torch.zeros(4, dtype=torch.int32), torch.zeros(2, dtype=torch.int32), torch.zeros(4, 8))
+    c1 = paged_gather.compile(*a)
+    assert paged_gather.compile(*a) is c1 and len(paged_gather._cache) == 1
+    b = (torch.zeros(64, 8),) + a[1:]
+    assert paged_gather.compile(*b) is not c1 and len(paged_gather._cache) == 2
+    paged_gather._cache.clear()   # the reference's tests clear it between cases
+    assert helper.type is pl.FunctionType.InCore
+
+
+def test_reference_examples_import_and_compile_unchanged():
+    """Load the reference's own example files through the compatibility surface."""
+    import importlib.util
+
+    import ref_extract
+    if not ref_extract.available():
+        pytest.skip("reference tree not mounted")
+    from pypto_b200 import compat
+    compat.install()
+    path = os.path.join(ref_extract.REFERENCE_ROOT, "examples/models/04_paged_attention.py")
+    spec = importlib.util.spec_from_file_location("ref_example_04", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    prog = mod.build_paged_attention_program(batch=2, num_heads=16, head_dim=128, block_size=128,
+                                             max_num_blocks_per_req=4)
+    c = ir.compile(prog, platform="b200")
+    assert c.entry.name == "paged_attention" and len(c.params) == 7
