@@ -5,6 +5,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include "pypto_b200.h"
+
 namespace pto {
 
 // paged_attention.cu
@@ -20,5 +22,33 @@ int paged_gather_launch(const void* src, int64_t src_rows, int64_t src_cols, int
                         const int32_t* indices, int64_t n_indices, const int32_t* block_table,
                         int64_t table_len, int block_size, int64_t col_off, int64_t size, void* out,
                         int32_t* err, cudaStream_t stream);
+
+// gemm.cu
+enum GemmEpi : int { kGemmEpiStore = 0, kGemmEpiAtomic = 1, kGemmEpiSwiglu = 2 };
+// D[a_row, b_row] = sum_k A[a_row, k] * B[b_row, k]; A [a_rows, k], B [b_rows_total, k] bf16 K-major.
+// Only the first b_rows rows of B form output columns; with the SwiGLU epilogue the tile at
+// row offset dual_off supplies the second operand.  swap: output written transposed.
+int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total, int b_rows, int k, void* out,
+                     long long ldo, int out_bf16, int swap, int epi, int dual_off, int bn, int k_chunks,
+                     int* err, cudaStream_t stream);
+
+// linear.cpp
+int linear_launch(const void* x, const void* w_packed, float* out, int m, int n, int k, int accumulate, int* err,
+                  cudaStream_t stream);
+size_t ffn_workspace_bytes(int m, int inter);
+int ffn_swiglu_launch(const void* x, const void* w_gate_up, const void* w_down, float* out, int m, int k, int inter,
+                      int n_out, void* workspace, size_t workspace_bytes, int accumulate, int* err,
+                      cudaStream_t stream);
+
+// glue.cu
+int rms_norm_launch(const void* x, int x_dtype, const float* gamma, void* out, int out_dtype, long long rows,
+                    int hidden, float eps, cudaStream_t stream);
+int rope_kv_append_launch(const float* qkv, const int32_t* seq_lens, const float* cos_t, const float* sin_t,
+                          int table_rows, const int32_t* block_table, int max_blocks, void* k_cache, void* v_cache,
+                          void* q_out, int batch, int num_heads, int kv_heads, int head_dim, int block_size,
+                          long long pool_blocks, int* err, cudaStream_t stream);
+int swiglu_act_launch(const float* gate_up, void* act, long long rows, int inter, cudaStream_t stream);
+int cast_launch(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream);
+int pack_weight_launch(const void* src, int src_dtype, void* dst, int k, int n, cudaStream_t stream);
 
 }  // namespace pto

@@ -1,0 +1,109 @@
+// Host-side composition of the tensor-core GEMM into the operators the model programs
+// use: a linear layer over pre-packed weights (q/k/v/o projections,
+// examples/models/qwen3_jit/kernels/projection.py:36-177) and the fused SwiGLU FFN
+// (examples/models/01_ffn.py:112-131; qwen3_jit/kernels/mlp.py:23-61).
+//
+// Orientation and split-K are chosen from the shape: with at most 256 activation rows
+// (decode) the weights take the 128 TMEM lanes and the output is written transposed;
+// K is cut into chunks until there are enough (A tile, B tile, K chunk) units to keep all
+// SMs streaming weights, and partial sums meet in the fp32 output through
+// red.global.add.f32.
+#include <algorithm>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace pto {
+
+namespace {
+
+int pick_bn_tokens(int m) { return m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)); }
+
+// Number of K chunks that best fills the SMs: maximise units / (waves * SMs) subject to
+// chunks of at least `min_kblocks` 64-wide K blocks.
+int pick_k_chunks(int tiles, int kblocks, int min_kblocks) {
+  const int sms = sm_count();
+  int best = 1;
+  double best_eff = 0.0;
+  const int max_chunks = std::max(1, kblocks / std::max(1, min_kblocks));
+  for (int c = 1; c <= max_chunks; ++c) {
+    const int per = (kblocks + c - 1) / c;
+    const int chunks = (kblocks + per - 1) / per;
+    const long long units = static_cast<long long>(tiles) * chunks;
+    const long long waves = (units + sms - 1) / sms;
+    const double eff = static_cast<double>(units) / static_cast<double>(waves * sms);
+    if (eff > best_eff + 0.02) {
+      best_eff = eff;
+      best = chunks;
+    }
+  }
+  return best;
+}
+
+}  // namespace
+
+// out[m, n] (+)= x[m, k] . w_packed[n, k]^T, fp32 out.  accumulate = 0 overwrites.
+int linear_launch(const void* x, const void* w_packed, float* out, int m, int n, int k, int accumulate, int* err,
+                  cudaStream_t stream) {
+  PTO_REQUIRE(x && w_packed && out, "linear: NULL tensor");
+  PTO_REQUIRE(m > 0 && n > 0 && k > 0 && k % 8 == 0, "linear: m, n > 0 and k a positive multiple of 8 required");
+  const int kblocks = (k + 63) / 64;
+  if (m <= 256) {
+    // decode orientation: A = weights [n, k], B = activations [m, k]
+    const int bn = pick_bn_tokens(m);
+    const int tiles = (n + 127) / 128;
+    const int chunks = pick_k_chunks(tiles, kblocks, 8);
+    if (!accumulate) PTO_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * static_cast<size_t>(m) * n, stream));
+    return gemm_bf16_launch(w_packed, n, x, m, m, k, out, n, 0, 1, kGemmEpiAtomic, 0, bn, chunks, err, stream);
+  }
+  const int bn = n >= 256 ? 256 : 128;
+  const int tiles = ((m + 127) / 128) * ((n + bn - 1) / bn);
+  int chunks = tiles >= sm_count() ? 1 : pick_k_chunks(tiles, kblocks, 8);
+  const int epi = (accumulate || chunks > 1) ? kGemmEpiAtomic : kGemmEpiStore;
+  if (epi == kGemmEpiAtomic && !accumulate)
+    PTO_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * static_cast<size_t>(m) * n, stream));
+  return gemm_bf16_launch(x, m, w_packed, n, n, k, out, n, 0, 0, epi, 0, bn, chunks, err, stream);
+}
+
+size_t ffn_workspace_bytes(int m, int inter) {
+  // decode: fp32 gate|up [m, 2*inter] + bf16 act [m, inter]; prefill: bf16 act only
+  const size_t act = (static_cast<size_t>(m) * inter * 2 + 255) / 256 * 256;
+  return m <= 256 ? act + static_cast<size_t>(m) * 2 * inter * 4 : act;
+}
+
+// out[m, n_out] (+)= (silu(x Wg) * (x Wu)) Wd with bf16 operands, fp32 accumulate, the
+// activation rounded to bf16 before the down projection
+// (tests/st/runtime/framework_and_models/test_qwen3_decode_scope3_mixed.py:282-285).
+// w_gate_up packed [2*inter, k] (gate rows first), w_down packed [n_out, inter].
+int ffn_swiglu_launch(const void* x, const void* w_gate_up, const void* w_down, float* out, int m, int k, int inter,
+                      int n_out, void* workspace, size_t workspace_bytes, int accumulate, int* err,
+                      cudaStream_t stream) {
+  PTO_REQUIRE(x && w_gate_up && w_down && out && workspace, "ffn_swiglu: NULL tensor");
+  PTO_REQUIRE(m > 0 && k > 0 && inter > 0 && n_out > 0 && k % 8 == 0 && inter % 8 == 0,
+              "ffn_swiglu: sizes must be positive, k and inter multiples of 8");
+  PTO_REQUIRE(workspace_bytes >= ffn_workspace_bytes(m, inter), "ffn_swiglu: workspace too small");
+  PTO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "ffn_swiglu: workspace must be 256-byte aligned");
+  __nv_bfloat16* act = static_cast<__nv_bfloat16*>(workspace);
+  int st;
+  if (m <= 256) {
+    float* gate_up = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) +
+                                              (static_cast<size_t>(m) * inter * 2 + 255) / 256 * 256);
+    st = linear_launch(x, w_gate_up, gate_up, m, 2 * inter, k, 0, err, stream);
+    if (st != kOk) return st;
+    st = swiglu_act_launch(gate_up, act, m, inter, stream);
+    if (st != kOk) return st;
+  } else {
+    // prefill orientation: gate and up tiles share the activation tile; SiLU*mul in the epilogue
+    PTO_REQUIRE(inter % 32 == 0, "ffn_swiglu: inter must be a multiple of 32");
+    const int a_tiles = (m + 127) / 128;
+    int bn = 128;
+    while (bn > 32 && (inter % bn != 0 || a_tiles * (inter / bn) < sm_count())) bn >>= 1;
+    PTO_REQUIRE(inter % bn == 0, "ffn_swiglu: inter must be a multiple of the column tile");
+    st = gemm_bf16_launch(x, m, w_gate_up, 2 * inter, inter, k, act, inter, 1, 0, kGemmEpiSwiglu, inter, bn, 1, err,
+                          stream);
+    if (st != kOk) return st;
+  }
+  return linear_launch(act, w_down, out, m, n_out, inter, accumulate, err, stream);
+}
+
+}  // namespace pto
