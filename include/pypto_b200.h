@@ -128,6 +128,28 @@ PTO_API int pto_paged_attention(const void* q, const void* k_cache, const void* 
                         int block_size, int max_blocks, int64_t pool_blocks, int q_len, float scale,
                         void* scratch, size_t scratch_bytes, void* stream);
 
+/* Paged-attention decode for callers that must not allocate.  No counterpart in the
+ * reference: it exists for hosts that cannot call cudaMalloc where they launch -- an engine
+ * that has already given all free HBM to its KV pool, a plugin living inside another
+ * framework's arena, a latency-critical loop that cannot take cudaMalloc's device-wide
+ * synchronisation.  Same arguments and results as pto_paged_attention, minus the scratch
+ * buffer: the partial softmax rows and the plan go to a fixed 32 MiB array inside the
+ * library (present on every GPU that loads it, until the process exits).
+ *   - Geometries whose scratch need (pto_paged_attention_scratch_bytes) exceeds 32 MiB are
+ *     rejected with PTO_INVALID_ARGUMENT; the benchmark geometry (batch 64, 32/8 heads,
+ *     q_len 1: about 22 MiB) fits.
+ *   - The first call on a device looks up the array's device address; make that call
+ *     before starting any stream capture.  No call allocates or frees device memory.
+ *   - All calls on one GPU share the array: launches that overlap on the GPU (different
+ *     streams, or two host threads) race and corrupt each other.  Serialise them.
+ *   - status_dev (optional, device int32[4]) receives the error word of this call
+ *     (0 = none; see pto_device_status for the codes), copied on `stream` after the kernels. */
+PTO_API int pto_paged_attention_static(const void* q, const void* k_cache, const void* v_cache,
+                               const int32_t* block_table, const int32_t* context_lens, void* out,
+                               int out_dtype, int batch, int num_heads, int kv_heads, int head_dim,
+                               int block_size, int max_blocks, int64_t pool_blocks, int q_len, float scale,
+                               int32_t* status_dev, void* stream);
+
 /* Block-table row gather.  Replaces `pl.paged_gather`
  * (src/ir/op/tensor_ops/paged_gather.cpp:63-169; semantics
  * tests/st/runtime/ops/test_paged_gather.py:14-17):

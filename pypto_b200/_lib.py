@@ -60,6 +60,7 @@ SIGNATURES = {
     "pto_op_list": (C.POINTER(C.c_char), []),
     "pto_paged_attention_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "pto_paged_attention": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _f, _p, _sz, _p]),
+    "pto_paged_attention_static": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _f, _p, _p]),
     "pto_paged_gather": (_i, [_p, _i64, _i64, _i, _p, _i64, _p, _i64, _i, _i64, _i64, _p, _p, _p]),
 }
 

@@ -17,6 +17,12 @@ int pa_launch(const void* q, const void* kc, const void* vc, const int32_t* bloc
               int kv_heads, int head_dim, int block_size, int max_blocks, int64_t pool_blocks,
               int q_len, float scale, void* scratch, size_t scratch_bytes, cudaStream_t stream);
 
+size_t pa_static_scratch_capacity();
+int pa_launch_static(const void* q, const void* kc, const void* vc, const int32_t* block_table,
+                     const int32_t* context_lens, void* out, int out_fp32, int batch, int num_heads,
+                     int kv_heads, int head_dim, int block_size, int max_blocks, int64_t pool_blocks,
+                     int q_len, float scale, int32_t* status_dev, cudaStream_t stream);
+
 // paged_gather.cu
 int paged_gather_launch(const void* src, int64_t src_rows, int64_t src_cols, int elem_bytes,
                         const int32_t* indices, int64_t n_indices, const int32_t* block_table,

@@ -148,6 +148,20 @@ int pto_paged_attention(const void* q, const void* k_cache, const void* v_cache,
                         scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
 }
 
+int pto_paged_attention_static(const void* q, const void* k_cache, const void* v_cache,
+                               const int32_t* block_table, const int32_t* context_lens, void* out, int out_dtype,
+                               int batch, int num_heads, int kv_heads, int head_dim, int block_size,
+                               int max_blocks, int64_t pool_blocks, int q_len, float scale, int32_t* status_dev,
+                               void* stream) {
+  if (out_dtype != PTO_BF16 && out_dtype != PTO_FP32)
+    return pto::fail(pto::kInvalidArgument, "paged_attention_static: out_dtype must be PTO_BF16 or PTO_FP32");
+  if (!q || !k_cache || !v_cache || !block_table || !context_lens || !out)
+    return pto::fail(pto::kInvalidArgument, "paged_attention_static: NULL tensor");
+  return pto::pa_launch_static(q, k_cache, v_cache, block_table, context_lens, out, out_dtype == PTO_FP32, batch,
+                               num_heads, kv_heads, head_dim, block_size, max_blocks, pool_blocks, q_len, scale,
+                               status_dev, static_cast<cudaStream_t>(stream));
+}
+
 int pto_paged_gather(const void* src, int64_t src_rows, int64_t src_cols, int elem_bytes, const int32_t* indices,
                      int64_t n_indices, const int32_t* block_table, int64_t table_len, int block_size,
                      int64_t col_off, int64_t size, void* out, int32_t* err, void* stream) {

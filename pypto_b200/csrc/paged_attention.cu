@@ -39,6 +39,9 @@
 #include "common.cuh"
 
 #include <math.h>
+#include <stdio.h>
+
+#include <mutex>
 
 #include "kernels.h"
 
@@ -739,5 +742,76 @@ int pa_launch(const void* q, const void* kc, const void* vc, const int32_t* bloc
   pa_merge_kernel<<<mgrid, 128, 0, stream>>>(p);
   return check_cuda(cudaGetLastError(), "pa_merge_kernel launch");
 }
+
+// ---------------------------------------------------------------------------
+// Launch without any allocation.
+//
+// Some callers may not allocate device memory at the point where they launch: a serving
+// loop that has handed the whole HBM budget to its KV-cache pool up front, a plugin
+// running inside another framework's memory arena, a real-time control path where
+// cudaMalloc's implicit device synchronisation is not acceptable.  For them the per-warp
+// partial (m, l, O) rows and the plan live in the fixed array below instead of a buffer
+// the caller or the worker allocates.  The array is part of the loaded module: every GPU
+// that loads this library holds kStaticScratchBytes of it until the process exits.
+//
+// In host code the name `g_pa_static_scratch` is only a handle of the symbol, not a
+// device address; the address is looked up once per device with cudaGetSymbolAddress
+// (with that device current) and that pointer is what the kernels receive.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr size_t kStaticScratchBytes = 32u << 20;
+static __device__ __align__(256) unsigned char g_pa_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_ptr[kMaxDevices] = {nullptr};
+std::mutex g_static_mu;
+
+int static_scratch_ptr(void** out) {
+  int dev = -1;
+  PTO_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(kInvalidArgument, "paged_attention_static: device index out of range");
+  std::lock_guard<std::mutex> g(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    PTO_CUDA(cudaGetSymbolAddress(&ptr, g_pa_static_scratch));
+    if (ptr == nullptr) return fail(kCudaError, "paged_attention_static: cudaGetSymbolAddress returned NULL");
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return kOk;
+}
+}  // namespace
+
+size_t pa_static_scratch_capacity() { return kStaticScratchBytes; }
+
+int pa_launch_static(const void* q, const void* kc, const void* vc, const int32_t* block_table,
+                     const int32_t* context_lens, void* out, int out_fp32, int batch, int num_heads,
+                     int kv_heads, int head_dim, int block_size, int max_blocks, int64_t pool_blocks,
+                     int q_len, float scale, int32_t* status_dev, cudaStream_t stream) {
+  PTO_REQUIRE(batch >= 0 && num_heads > 0 && kv_heads > 0 && q_len > 0 && num_heads % kv_heads == 0,
+              "paged_attention_static: bad geometry");
+  const size_t need = pa_scratch_bytes(batch, num_heads, kv_heads, q_len);
+  if (need > kStaticScratchBytes) {
+    char buf[200];
+    snprintf(buf, sizeof buf,
+             "paged_attention_static: this geometry needs %zu bytes of scratch, the built-in array holds %zu; "
+             "use pto_paged_attention with a caller-provided buffer",
+             need, kStaticScratchBytes);
+    return fail(kInvalidArgument, buf);
+  }
+  void* scratch = nullptr;
+  int st = static_scratch_ptr(&scratch);
+  if (st != kOk) return st;
+  // The array keeps whatever the previous call left.  Only the error word has to start
+  // at zero; plan and partial rows are fully rewritten by every launch before they are read.
+  PTO_CUDA(cudaMemsetAsync(scratch, 0, 64, stream));
+  st = pa_launch(q, kc, vc, block_table, context_lens, out, out_fp32, batch, num_heads, kv_heads, head_dim,
+                 block_size, max_blocks, pool_blocks, q_len, scale, scratch, kStaticScratchBytes, stream);
+  if (st != kOk) return st;
+  if (status_dev != nullptr)
+    PTO_CUDA(cudaMemcpyAsync(status_dev, scratch, 4 * sizeof(int32_t), cudaMemcpyDeviceToDevice, stream));
+  return kOk;
+}
+
 
 }  // namespace pto
