@@ -162,6 +162,56 @@ PTO_API int pto_paged_gather(const void* src, int64_t src_rows, int64_t src_cols
                      int64_t table_len, int block_size, int64_t col_off, int64_t size, void* out,
                      int32_t* err, void* stream);
 
+/* ---- tensor-core linear algebra (weights pre-packed) ---- */
+
+/* One-time weight packing: w [k, n] row-major (fp32 or bf16), the layout of the reference's
+ * `x @ W` weights (examples/models/01_ffn.py:157-160) -> packed [n, k] bf16, the K-major
+ * operand layout of the tcgen05 GEMM. */
+PTO_API int pto_pack_weight(const void* w, int w_dtype, void* packed, int k, int n, void* stream);
+/* fp32 <-> bf16 element cast. */
+PTO_API int pto_cast(const void* in, int in_dtype, void* out, int out_dtype, int64_t n, void* stream);
+
+/* out[m, n] = x[m, k] @ W (accumulate = 0) or out += x @ W (accumulate = 1; out then holds
+ * e.g. the residual), x bf16, W packed [n, k] bf16, out fp32, fp32 accumulation.  Replaces the
+ * projection kernels of examples/models/qwen3_jit/kernels/projection.py:36-177 and
+ * `matmul_kernel` of examples/models/01_ffn.py:37-45.  `err` (may be NULL): device int32[4]
+ * error word. */
+PTO_API int pto_linear(const void* x, const void* w_packed, void* out, int m, int n, int k, int accumulate,
+                       int32_t* err, void* stream);
+
+/* Fused SwiGLU FFN: out[m, n_out] (+)= bf16(silu(x Wg) * (x Wu)) Wd.  Replaces `ffn_swiglu`
+ * (examples/models/01_ffn.py:112-131) and `mlp_block` + `down_projection_residual`
+ * (examples/models/qwen3_jit/kernels/mlp.py:23-61, kernels/projection.py:146-177).
+ *   x bf16 [m, k]; w_gate_up packed [2*inter, k] (gate rows, then up rows);
+ *   w_down packed [n_out, inter]; out fp32 [m, n_out];
+ *   workspace: device buffer of pto_ffn_swiglu_workspace_bytes(m, inter), 256-byte aligned. */
+PTO_API size_t pto_ffn_swiglu_workspace_bytes(int m, int inter);
+PTO_API int pto_ffn_swiglu(const void* x, const void* w_gate_up, const void* w_down, void* out, int m, int k,
+                           int inter, int n_out, void* workspace, size_t workspace_bytes, int accumulate,
+                           int32_t* err, void* stream);
+
+/* ---- decoder-layer glue ---- */
+
+/* out = x * rsqrt(mean(x^2) + eps) * gamma, fp32 statistics; x and out fp32 or bf16, gamma
+ * fp32 [hidden] or NULL (examples/models/qwen3_jit/kernels/rmsnorm.py:27-89;
+ * examples/models/08_llama_mini.py:94-118 is the gamma-free form). */
+PTO_API int pto_rms_norm(const void* x, int x_dtype, const float* gamma, void* out, int out_dtype, int64_t rows,
+                         int hidden, float eps, void* stream);
+
+/* RoPE (rotate-half) on Q and K at pos = seq_len - 1 and append of the rotated K row and the
+ * V row to the paged cache (examples/models/qwen3_jit/kernels/attention.py:40-111).
+ *   qkv fp32 [batch, (num_heads + 2*kv_heads) * head_dim]: q heads, k heads, v heads;
+ *   cos/sin fp32 [table_rows, head_dim]; caches bf16 [(block, kv head, token), head_dim];
+ *   q_out bf16 [batch * num_heads, head_dim]. */
+PTO_API int pto_rope_kv_append(const float* qkv, const int32_t* seq_lens, const float* cos_table,
+                               const float* sin_table, int table_rows, const int32_t* block_table,
+                               int max_blocks, void* k_cache, void* v_cache, void* q_out, int batch,
+                               int num_heads, int kv_heads, int head_dim, int block_size, int64_t pool_blocks,
+                               int32_t* err, void* stream);
+
+/* act[r, c] = bf16(silu(gate_up[r, c]) * gate_up[r, inter + c]), gate_up fp32 [rows, 2*inter]. */
+PTO_API int pto_swiglu_act(const float* gate_up, void* act, int64_t rows, int inter, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -61,6 +61,14 @@ SIGNATURES = {
     "pto_paged_attention_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "pto_paged_attention": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _f, _p, _sz, _p]),
     "pto_paged_attention_static": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _f, _p, _p]),
+    "pto_pack_weight": (_i, [_p, _i, _p, _i, _i, _p]),
+    "pto_cast": (_i, [_p, _i, _p, _i, _i64, _p]),
+    "pto_linear": (_i, [_p, _p, _p, _i, _i, _i, _i, _p, _p]),
+    "pto_ffn_swiglu_workspace_bytes": (_sz, [_i, _i]),
+    "pto_ffn_swiglu": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p, _sz, _i, _p, _p]),
+    "pto_rms_norm": (_i, [_p, _i, _p, _p, _i, _i64, _i, _f, _p]),
+    "pto_rope_kv_append": (_i, [_p, _p, _p, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i64, _p, _p]),
+    "pto_swiglu_act": (_i, [_p, _p, _i64, _i, _p]),
     "pto_paged_gather": (_i, [_p, _i64, _i64, _i, _p, _i64, _p, _i64, _i, _i64, _i64, _p, _p, _p]),
 }
 

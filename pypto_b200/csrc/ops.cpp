@@ -172,4 +172,48 @@ int pto_paged_gather(const void* src, int64_t src_rows, int64_t src_cols, int el
                                   static_cast<cudaStream_t>(stream));
 }
 
+int pto_pack_weight(const void* w, int w_dtype, void* packed, int k, int n, void* stream) {
+  return pto::pack_weight_launch(w, w_dtype, packed, k, n, static_cast<cudaStream_t>(stream));
+}
+
+int pto_cast(const void* in, int in_dtype, void* out, int out_dtype, int64_t n, void* stream) {
+  return pto::cast_launch(in, in_dtype, out, out_dtype, n, static_cast<cudaStream_t>(stream));
+}
+
+int pto_linear(const void* x, const void* w_packed, void* out, int m, int n, int k, int accumulate, int32_t* err,
+               void* stream) {
+  return pto::linear_launch(x, w_packed, static_cast<float*>(out), m, n, k, accumulate, err,
+                            static_cast<cudaStream_t>(stream));
+}
+
+size_t pto_ffn_swiglu_workspace_bytes(int m, int inter) {
+  if (m <= 0 || inter <= 0) return 0;
+  return pto::ffn_workspace_bytes(m, inter);
+}
+
+int pto_ffn_swiglu(const void* x, const void* w_gate_up, const void* w_down, void* out, int m, int k, int inter,
+                   int n_out, void* workspace, size_t workspace_bytes, int accumulate, int32_t* err, void* stream) {
+  return pto::ffn_swiglu_launch(x, w_gate_up, w_down, static_cast<float*>(out), m, k, inter, n_out, workspace,
+                                workspace_bytes, accumulate, err, static_cast<cudaStream_t>(stream));
+}
+
+int pto_rms_norm(const void* x, int x_dtype, const float* gamma, void* out, int out_dtype, int64_t rows, int hidden,
+                 float eps, void* stream) {
+  return pto::rms_norm_launch(x, x_dtype, gamma, out, out_dtype, rows, hidden, eps,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int pto_rope_kv_append(const float* qkv, const int32_t* seq_lens, const float* cos_table, const float* sin_table,
+                       int table_rows, const int32_t* block_table, int max_blocks, void* k_cache, void* v_cache,
+                       void* q_out, int batch, int num_heads, int kv_heads, int head_dim, int block_size,
+                       int64_t pool_blocks, int32_t* err, void* stream) {
+  return pto::rope_kv_append_launch(qkv, seq_lens, cos_table, sin_table, table_rows, block_table, max_blocks,
+                                    k_cache, v_cache, q_out, batch, num_heads, kv_heads, head_dim, block_size,
+                                    pool_blocks, err, static_cast<cudaStream_t>(stream));
+}
+
+int pto_swiglu_act(const float* gate_up, void* act, int64_t rows, int inter, void* stream) {
+  return pto::swiglu_act_launch(gate_up, act, rows, inter, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

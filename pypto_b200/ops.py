@@ -157,3 +157,136 @@ def paged_gather(src, indices, block_table, block_size: int, size: int | None = 
             block_table.data_ptr(), block_table.numel(), block_size, col_off, size, out.data_ptr(),
             buf.data_ptr(), _stream_ptr(dev)))
     return out
+
+
+# ---------------------------------------------------------------------------
+# tensor-core linear algebra and decoder-layer glue
+# ---------------------------------------------------------------------------
+
+def _err_ptr(dev) -> int:
+    return scratch(dev, 256).data_ptr()
+
+
+def pack_weight(w: torch.Tensor) -> torch.Tensor:
+    """[K, N] fp32/bf16 (the ``x @ W`` layout) -> packed [N, K] bf16, once per weight."""
+    dev = _need_cuda(w)
+    if w.dim() != 2 or w.dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("pack_weight expects a 2-D fp32 or bf16 tensor")
+    k, n = w.shape
+    out = torch.empty(n, k, dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_pack_weight(w.data_ptr(), dtype_code(w.dtype), out.data_ptr(), k, n,
+                                               _stream_ptr(dev)))
+    return out
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    dev = _need_cuda(x)
+    out = torch.empty(x.shape, dtype=dtype, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_cast(x.data_ptr(), dtype_code(x.dtype), out.data_ptr(), dtype_code(dtype),
+                                        x.numel(), _stream_ptr(dev)))
+    return out
+
+
+def linear(x: torch.Tensor, w_packed: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False):
+    """fp32 out[m, n] (+)= x[m, k] @ W with W packed [n, k] bf16, x bf16."""
+    dev = _need_cuda(x, w_packed)
+    if x.dtype != torch.bfloat16 or w_packed.dtype != torch.bfloat16:
+        raise TypeError("linear: x and packed weight must be bfloat16")
+    m, k = x.shape
+    n, k2 = w_packed.shape
+    if k != k2:
+        raise ValueError(f"linear: x has k={k}, packed weight has k={k2}")
+    if out is None:
+        if accumulate:
+            raise ValueError("linear: accumulate needs an existing output")
+        out = torch.empty(m, n, dtype=torch.float32, device=dev)
+    elif out.dtype != torch.float32 or tuple(out.shape) != (m, n) or not out.is_contiguous():
+        raise ValueError("linear: out must be a contiguous fp32 [m, n] tensor")
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_linear(x.data_ptr(), w_packed.data_ptr(), out.data_ptr(), m, n, k,
+                                          1 if accumulate else 0, _err_ptr(dev), _stream_ptr(dev)))
+    return out
+
+
+_ffn_ws: dict = {}
+
+
+def ffn_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, out: torch.Tensor | None = None,
+               accumulate: bool = False):
+    """fp32 out[m, n_out] (+)= bf16(silu(x Wg) * (x Wu)) Wd; packed weights
+    (w_gate_up [2*inter, k] gate rows first, w_down [n_out, inter])."""
+    dev = _need_cuda(x, w_gate_up, w_down)
+    if any(t.dtype != torch.bfloat16 for t in (x, w_gate_up, w_down)):
+        raise TypeError("ffn_swiglu: x and packed weights must be bfloat16")
+    m, k = x.shape
+    inter = w_gate_up.shape[0] // 2
+    n_out = w_down.shape[0]
+    if w_gate_up.shape != (2 * inter, k) or w_down.shape != (n_out, inter):
+        raise ValueError("ffn_swiglu: weight shapes do not match [2*inter, k] / [n_out, inter]")
+    if out is None:
+        if accumulate:
+            raise ValueError("ffn_swiglu: accumulate needs an existing output")
+        out = torch.empty(m, n_out, dtype=torch.float32, device=dev)
+    elif out.dtype != torch.float32 or tuple(out.shape) != (m, n_out) or not out.is_contiguous():
+        raise ValueError("ffn_swiglu: out must be a contiguous fp32 [m, n_out] tensor")
+    lib = _lib.load()
+    need = lib.pto_ffn_swiglu_workspace_bytes(m, inter)
+    key = (dev.index, _stream_ptr(dev))
+    ws = _ffn_ws.get(key)
+    if ws is None or ws.numel() < need:
+        ws = _ffn_ws[key] = torch.empty(need, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.pto_ffn_swiglu(x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), out.data_ptr(), m, k,
+                                      inter, n_out, ws.data_ptr(), ws.numel(), 1 if accumulate else 0,
+                                      _err_ptr(dev), _stream_ptr(dev)))
+    return out
+
+
+def rms_norm(x: torch.Tensor, gamma: torch.Tensor | None, eps: float, out_dtype: torch.dtype = torch.bfloat16):
+    dev = _need_cuda(x) if gamma is None else _need_cuda(x, gamma)
+    if gamma is not None and (gamma.dtype != torch.float32 or gamma.numel() != x.shape[-1]):
+        raise ValueError("rms_norm: gamma must be fp32 with hidden elements")
+    hidden = x.shape[-1]
+    out = torch.empty(x.shape, dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_rms_norm(x.data_ptr(), dtype_code(x.dtype), gamma.data_ptr() if gamma is not None else None,
+                                            out.data_ptr(), dtype_code(out_dtype), x.numel() // hidden, hidden,
+                                            float(eps), _stream_ptr(dev)))
+    return out
+
+
+def rope_kv_append(qkv, seq_lens, cos, sin, block_table, k_cache, v_cache, *, num_heads, kv_heads, head_dim,
+                   block_size, q_out=None):
+    """RoPE on Q/K at pos = seq_len - 1 + paged cache append; returns rotated Q (bf16)."""
+    dev = _need_cuda(qkv, seq_lens, cos, sin, block_table, k_cache, v_cache)
+    batch = seq_lens.numel()
+    if qkv.dtype != torch.float32 or qkv.numel() != batch * (num_heads + 2 * kv_heads) * head_dim:
+        raise ValueError("rope_kv_append: qkv must be fp32 [batch, (num_heads + 2*kv_heads) * head_dim]")
+    if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape != sin.shape or cos.shape[-1] != head_dim:
+        raise ValueError("rope_kv_append: cos/sin must be fp32 [rows, head_dim]")
+    if seq_lens.dtype != torch.int32 or block_table.dtype != torch.int32:
+        raise TypeError("rope_kv_append: seq_lens and block_table must be int32")
+    if k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16:
+        raise TypeError("rope_kv_append: caches must be bfloat16")
+    rows = k_cache.numel() // head_dim
+    pool_blocks = rows // (kv_heads * block_size)
+    if q_out is None:
+        q_out = torch.empty(batch * num_heads, head_dim, dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_rope_kv_append(
+            qkv.data_ptr(), seq_lens.data_ptr(), cos.data_ptr(), sin.data_ptr(), cos.shape[0],
+            block_table.data_ptr(), block_table.numel() // max(batch, 1), k_cache.data_ptr(), v_cache.data_ptr(),
+            q_out.data_ptr(), batch, num_heads, kv_heads, head_dim, block_size, pool_blocks, _err_ptr(dev),
+            _stream_ptr(dev)))
+    return q_out
+
+
+def swiglu_act(gate_up: torch.Tensor) -> torch.Tensor:
+    dev = _need_cuda(gate_up)
+    rows, two_i = gate_up.shape
+    out = torch.empty(rows, two_i // 2, dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_swiglu_act(gate_up.data_ptr(), out.data_ptr(), rows, two_i // 2, _stream_ptr(dev)))
+    return out
