@@ -212,6 +212,52 @@ PTO_API int pto_rope_kv_append(const float* qkv, const int32_t* seq_lens, const 
 /* act[r, c] = bf16(silu(gate_up[r, c]) * gate_up[r, inter + c]), gate_up fp32 [rows, 2*inter]. */
 PTO_API int pto_swiglu_act(const float* gate_up, void* act, int64_t rows, int inter, void* stream);
 
+/* ---- mixture of experts ---- */
+
+/* Top-k routing.  `scores` fp32 [tokens, experts] holds gate logits (is_logits = 1: sigmoid is
+ * applied) or ready scores (0).  Experts are chosen by the top-k of score + bias (bias may be
+ * NULL), listed in descending order, ties to the lower expert id; weight = score / sum of the
+ * chosen scores.  The index contract is that of the reference's descending sort with original
+ * indices (sort32 + mrgsort + gather, tests/st/runtime/ops/test_sort.py:602-632): exact integers. */
+PTO_API int pto_moe_topk(const float* scores, const float* bias, int is_logits, int tokens, int experts,
+                         int topk, int32_t* idx, float* weights, void* stream);
+
+/* Per-(row, 128 columns) e4m3 quantisation: scale = amax / 448 (1 for an all-zero group),
+ * q = e4m3(x / scale) round-to-nearest-even.  x bf16 or fp32 [rows, cols], cols % 128 == 0. */
+PTO_API int pto_quantize_rows(const void* x, int x_dtype, void* q, float* scale, int64_t rows, int cols,
+                              void* stream);
+
+/* Dispatch plan (dispatch_step, tests/st/distributed/test_l3_ep_dispatch_combine.py:104-299):
+ * bucket of route r is expert_of[r]; inside a bucket routes keep ascending r = t * TOPK + k.
+ * Outputs: counts [buckets], offsets [buckets + 1], pos [routes] (slot of each route in the
+ * bucket-sorted order), route_at [routes] (inverse).  rank_tmp: int32 [routes] work array. */
+PTO_API int pto_moe_dispatch_plan(const int32_t* expert_of, int routes, int buckets, int32_t* counts,
+                                  int32_t* offsets, int32_t* pos, int32_t* route_at, int32_t* rank_tmp,
+                                  void* stream);
+
+/* dst_i[p, :] = src_i[index[p] / div, :] for up to 3 byte arrays with row sizes row_bytes[i]
+ * (index NULL: identity).  Bit-exact row copies (the payload move of dispatch_step). */
+PTO_API int pto_moe_gather_rows(const void* const* src, void* const* dst, const int* row_bytes, int n_arrays,
+                                const int32_t* index, int div, int64_t rows, void* stream);
+PTO_API int pto_moe_gather_f32(const float* src, const int32_t* index, int64_t n, float* dst, void* stream);
+
+/* Grouped FP8 expert GEMM over tokens sorted by expert (replaces local_expert_step,
+ * test_l3_ep_dispatch_combine.py:309-327, by the SwiGLU expert FFN).
+ *   w fp8 [experts * w_rows, k] K-major, w_scale fp32 [experts][w_rows / 128][k / 128]
+ *   x fp8 [rows, k], x_scale fp32 [rows][k / 128], offsets int32 [experts + 1]
+ * dual = 1: w_rows = 2 * n_out (gate rows then up rows); writes act_q fp8 [rows, n_out] and
+ *           act_scale fp32 [rows, n_out / 128] = requantised bf16(silu(gate) * up).
+ * dual = 0: w_rows = n_out; writes out bf16 [rows, n_out] = acc * route_w[row] (route_w may be NULL). */
+PTO_API int pto_moe_expert_gemm(int dual, const void* w, const float* w_scale, int experts, int w_rows,
+                                int n_out, int k, const void* x, const float* x_scale, const int32_t* offsets,
+                                int rows, const float* route_w, void* act_q, float* act_scale, void* out,
+                                int32_t* err, void* stream);
+
+/* Combine (combine_step, test_l3_ep_dispatch_combine.py:337-402): y[t] = sum_k fp32(rows[pos[t*topk+k]])
+ * (+ fp32(shared[t]) if given), k ascending; written as bf16 (y_bf16) and/or fp32 (y_f32). */
+PTO_API int pto_moe_combine(const void* rows, const int32_t* pos, const void* shared, int tokens, int topk,
+                            int hidden, void* y_bf16, float* y_f32, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

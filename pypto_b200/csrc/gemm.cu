@@ -14,10 +14,13 @@
 // lanes are filled by output features and the token count becomes the small N of the
 // MMA; the output is then written transposed (`swap`).
 //
-// Work units.  unit = (A tile, B tile, K chunk); CTAs are persistent and take units
-// round-robin.  With more than one K chunk the partial sums are added to the output
-// with red.global.add.f32 (the output then has to be initialised by the caller: zeros,
-// or the residual that the reference adds after the projection).
+// Work split.  The (tile, K block) iterations of the whole problem form one index space
+// that is cut into equal contiguous ranges, one per persistent CTA (stream-K): every CTA
+// streams the same number of operand bytes.  A maximal run of K blocks of one tile inside
+// a range is a segment; with the atomic epilogue a segment adds its partial sums to the
+// output with red.global.add.f32 (the output is initialised by the caller: zeros, or the
+// residual that the reference adds after the projection).  The other epilogues need whole
+// tiles, so ranges are then rounded to tile boundaries.
 //
 // CTA = 6 warps: warp 0 TMA producer, warp 1 MMA issuer (owns the TMEM allocation),
 // warps 2-5 epilogue (TMEM -> registers -> global).  smem ring of (A, B[, B2]) stages with
@@ -36,8 +39,8 @@ constexpr int kMaxStages = 12;
 
 struct GemmParams {
   int a_rows, b_rows, k;
-  int a_tiles, b_tiles, k_chunks, kblocks_per_chunk, kblocks_total;
-  int units;
+  int a_tiles, b_tiles, kblocks_total;
+  int iters_total, iters_per_cta;  // (tile, K block) iterations; per CTA a multiple of kblocks_total unless atomic
   int bn;
   int dual, dual_off;  // SwiGLU: second B tile (up weights) at row offset dual_off
   int swap;            // out[b_row * ldo + a_row] instead of out[a_row * ldo + b_row]
@@ -52,6 +55,31 @@ struct GemmParams {
 __device__ __forceinline__ float silu_mul(float g, float u) {
   // sigmoid as recip(1 + exp(-g)), the form of examples/models/01_ffn.py:66-77
   return g * (1.f / (1.f + __expf(-g))) * u;
+}
+
+// Segment walk shared by the three roles: iterations [lo, hi) of this CTA, cut at tile
+// boundaries.
+struct Seg {
+  int tile, kb0, kb1;
+};
+// stride == 0: contiguous iteration range [it, hi) (stream-K).  stride > 0: whole tiles
+// it, it + stride, ... below hi, so that CTAs running at the same time work on
+// neighbouring tiles and share operand tiles in L2.
+__device__ __forceinline__ bool next_seg(int& it, int hi, int kblocks, int stride, Seg& s) {
+  if (it >= hi) return false;
+  if (stride > 0) {
+    s.tile = it;
+    s.kb0 = 0;
+    s.kb1 = kblocks;
+    it += stride;
+    return true;
+  }
+  s.tile = it / kblocks;
+  s.kb0 = it - s.tile * kblocks;
+  const int len = min(kblocks - s.kb0, hi - it);
+  s.kb1 = s.kb0 + len;
+  it += len;
+  return true;
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -93,19 +121,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  const bool stream_k = p.epi == kGemmEpiAtomic;
+  const int stride = stream_k ? 0 : static_cast<int>(gridDim.x);
+  const int it_lo = stream_k ? min(p.iters_total, static_cast<int>(blockIdx.x) * p.iters_per_cta)
+                             : static_cast<int>(blockIdx.x);
+  const int it_hi = stream_k ? min(p.iters_total, it_lo + p.iters_per_cta) : p.a_tiles * p.b_tiles;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-        const int kc = u % p.k_chunks;
-        const int bt = (u / p.k_chunks) % p.b_tiles;
-        const int at = u / (p.k_chunks * p.b_tiles);
-        const int kb0 = kc * p.kblocks_per_chunk;
-        const int kb1 = min(p.kblocks_total, kb0 + p.kblocks_per_chunk);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+      int cur = it_lo;
+      Seg sg;
+      while (ok && next_seg(cur, it_hi, p.kblocks_total, stride, sg)) {
+        const int at = sg.tile / p.b_tiles, bt = sg.tile - at * p.b_tiles;
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
           const uint32_t s = it % p.stages, round = it / p.stages;
           if (!mbar_wait(&empty[s], (round & 1u) ^ 1u)) {
             report_error(p.err, kErrBarrierTimeout, 40, static_cast<int>(it));
@@ -124,12 +155,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(kBM, p.bn, 1, 1);
+      const uint32_t idesc2 = umma_idesc(kBM, 2 * p.bn, 1, 1);  // gate and up tiles are adjacent in smem
       uint32_t it = 0, ui = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x, ++ui) {
-        const int kc = u % p.k_chunks;
-        const int kb0 = kc * p.kblocks_per_chunk;
-        const int kb1 = min(p.kblocks_total, kb0 + p.kblocks_per_chunk);
+      int cur = it_lo;
+      Seg sg;
+      for (; ok && next_seg(cur, it_hi, p.kblocks_total, stride, sg); ++ui) {
+        const int kb0 = sg.kb0, kb1 = sg.kb1;
         const uint32_t ab = ui & 1u;
         if (!mbar_wait(&tmem_empty[ab], ((ui >> 1) & 1u) ^ 1u)) {
           report_error(p.err, kErrBarrierTimeout, 41, static_cast<int>(ui));
@@ -150,9 +182,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             const uint32_t acc = (kb > kb0 || k > 0) ? 1u : 0u;
-            const uint64_t ad = umma_desc_sw128(a_addr + k * 32);
-            umma_bf16(d0, ad, umma_desc_sw128(b_addr + k * 32), idesc, acc);
-            if (p.dual) umma_bf16(d0 + p.bn, ad, umma_desc_sw128(b_addr + b_bytes + k * 32), idesc, acc);
+            umma_bf16(d0, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32),
+                      p.dual ? idesc2 : idesc, acc);
           }
           umma_commit(&empty[s]);
         }
@@ -164,9 +195,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     // -------------------------------- epilogue --------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t ui = 0;
-    for (int u = blockIdx.x; u < p.units; u += gridDim.x, ++ui) {
-      const int bt = (u / p.k_chunks) % p.b_tiles;
-      const int at = u / (p.k_chunks * p.b_tiles);
+    int cur = it_lo;
+    Seg sg;
+    for (; next_seg(cur, it_hi, p.kblocks_total, stride, sg); ++ui) {
+      const int at = sg.tile / p.b_tiles, bt = sg.tile - at * p.b_tiles;
       const uint32_t ab = ui & 1u;
       if (!mbar_wait(&tmem_full[ab], (ui >> 1) & 1u)) {
         report_error(p.err, kErrBarrierTimeout, 43, static_cast<int>(ui));
@@ -257,18 +289,28 @@ int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total,
   PTO_REQUIRE(bn == 32 || bn == 64 || bn == 128 || bn == 256, "gemm: bn must be 32, 64, 128 or 256");
   const int dual = epi == kGemmEpiSwiglu ? 1 : 0;
   PTO_REQUIRE(!dual || (bn <= 128 && !swap), "gemm: SwiGLU epilogue needs bn <= 128 and the normal orientation");
-  PTO_REQUIRE(k_chunks >= 1 && (k_chunks == 1 || epi == kGemmEpiAtomic), "gemm: split-K needs the atomic epilogue");
   PTO_REQUIRE(epi != kGemmEpiAtomic || !out_bf16, "gemm: atomic epilogue accumulates in fp32");
+  (void)k_chunks;
 
   GemmParams p;
   p.a_rows = a_rows; p.b_rows = b_rows; p.k = k;
   p.a_tiles = (a_rows + kBM - 1) / kBM;
   p.b_tiles = (b_rows + bn - 1) / bn;
   p.kblocks_total = (k + kBK - 1) / kBK;
-  if (k_chunks > p.kblocks_total) k_chunks = p.kblocks_total;
-  p.kblocks_per_chunk = (p.kblocks_total + k_chunks - 1) / k_chunks;
-  p.k_chunks = (p.kblocks_total + p.kblocks_per_chunk - 1) / p.kblocks_per_chunk;
-  p.units = p.a_tiles * p.b_tiles * p.k_chunks;
+  const int tiles = p.a_tiles * p.b_tiles;
+  PTO_REQUIRE(static_cast<long long>(tiles) * p.kblocks_total < (1ll << 31), "gemm: problem too large");
+  p.iters_total = tiles * p.kblocks_total;
+  int grid = sm_count();
+  if (epi == kGemmEpiAtomic) {
+    // stream-K; keep segments at least 4 K blocks long on average
+    const int max_ctas = (p.iters_total + 3) / 4;
+    if (grid > max_ctas) grid = max_ctas;
+    p.iters_per_cta = (p.iters_total + grid - 1) / grid;
+  } else {
+    if (grid > tiles) grid = tiles;
+    p.iters_per_cta = 0;  // whole tiles, taken round-robin
+  }
+  if (epi == kGemmEpiAtomic) grid = (p.iters_total + p.iters_per_cta - 1) / p.iters_per_cta;
   p.bn = bn; p.dual = dual; p.dual_off = dual_off; p.swap = swap; p.epi = epi; p.out_bf16 = out_bf16;
   p.out = out; p.ldo = ldo; p.err = err;
   const int stage_bytes = kBM * 128 + (dual ? 2 : 1) * bn * 128;
@@ -290,8 +332,6 @@ int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total,
     PTO_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
-  int grid = sm_count();
-  if (grid > p.units) grid = p.units;
   gemm_bf16_kernel<<<grid, kGemmThreads, smem, stream>>>(tm_a, tm_b, p);
   return check_cuda(cudaGetLastError(), "gemm_bf16_kernel launch");
 }

@@ -57,4 +57,23 @@ int swiglu_act_launch(const float* gate_up, void* act, long long rows, int inter
 int cast_launch(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream);
 int pack_weight_launch(const void* src, int src_dtype, void* dst, int k, int n, cudaStream_t stream);
 
+// moe_route.cu
+int moe_topk_launch(const float* scores, const float* bias, int is_logits, int tokens, int experts, int topk,
+                    int32_t* idx, float* weights, cudaStream_t stream);
+int quantize_rows_launch(const void* x, int x_dtype, void* q, float* scale, long long rows, int cols,
+                         cudaStream_t stream);
+int moe_dispatch_plan_launch(const int32_t* expert_of, int routes, int buckets, int32_t* counts, int32_t* offsets,
+                             int32_t* pos, int32_t* route_at, int32_t* rank_tmp, cudaStream_t stream);
+int moe_gather_rows_launch(const void* const* src, void* const* dst, const int* row_bytes, int n_arrays,
+                           const int32_t* src_row_of, int div, long long rows, cudaStream_t stream);
+int moe_gather_f32_launch(const float* src, const int32_t* index, long long n, float* dst, cudaStream_t stream);
+int moe_combine_launch(const void* rows, const int32_t* pos, const void* shared, int tokens, int topk, int hidden,
+                       void* y_bf16, float* y_f32, cudaStream_t stream);
+
+// moe_gemm.cu
+int moe_gemm_fp8_launch(int dual, const void* w, const float* w_scale, int experts, int w_rows_per_expert,
+                        int n_out, int k, const void* x, const float* x_scale, const int32_t* offsets,
+                        int total_rows, const float* route_w, void* act_q, float* act_scale, void* out, int* err,
+                        cudaStream_t stream);
+
 }  // namespace pto

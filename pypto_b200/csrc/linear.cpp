@@ -5,11 +5,8 @@
 //
 // Orientation and split-K are chosen from the shape: with at most 256 activation rows
 // (decode) the weights take the 128 TMEM lanes and the output is written transposed;
-// K is cut into chunks until there are enough (A tile, B tile, K chunk) units to keep all
-// SMs streaming weights, and partial sums meet in the fp32 output through
-// red.global.add.f32.
-#include <algorithm>
-
+// the (tile, K block) iterations are split evenly over the SMs (stream-K) and partial sums
+// meet in the fp32 output through red.global.add.f32.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -19,27 +16,6 @@ namespace {
 
 int pick_bn_tokens(int m) { return m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)); }
 
-// Number of K chunks that best fills the SMs: maximise units / (waves * SMs) subject to
-// chunks of at least `min_kblocks` 64-wide K blocks.
-int pick_k_chunks(int tiles, int kblocks, int min_kblocks) {
-  const int sms = sm_count();
-  int best = 1;
-  double best_eff = 0.0;
-  const int max_chunks = std::max(1, kblocks / std::max(1, min_kblocks));
-  for (int c = 1; c <= max_chunks; ++c) {
-    const int per = (kblocks + c - 1) / c;
-    const int chunks = (kblocks + per - 1) / per;
-    const long long units = static_cast<long long>(tiles) * chunks;
-    const long long waves = (units + sms - 1) / sms;
-    const double eff = static_cast<double>(units) / static_cast<double>(waves * sms);
-    if (eff > best_eff + 0.02) {
-      best_eff = eff;
-      best = chunks;
-    }
-  }
-  return best;
-}
-
 }  // namespace
 
 // out[m, n] (+)= x[m, k] . w_packed[n, k]^T, fp32 out.  accumulate = 0 overwrites.
@@ -47,22 +23,19 @@ int linear_launch(const void* x, const void* w_packed, float* out, int m, int n,
                   cudaStream_t stream) {
   PTO_REQUIRE(x && w_packed && out, "linear: NULL tensor");
   PTO_REQUIRE(m > 0 && n > 0 && k > 0 && k % 8 == 0, "linear: m, n > 0 and k a positive multiple of 8 required");
-  const int kblocks = (k + 63) / 64;
   if (m <= 256) {
     // decode orientation: A = weights [n, k], B = activations [m, k]
     const int bn = pick_bn_tokens(m);
-    const int tiles = (n + 127) / 128;
-    const int chunks = pick_k_chunks(tiles, kblocks, 8);
     if (!accumulate) PTO_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * static_cast<size_t>(m) * n, stream));
-    return gemm_bf16_launch(w_packed, n, x, m, m, k, out, n, 0, 1, kGemmEpiAtomic, 0, bn, chunks, err, stream);
+    return gemm_bf16_launch(w_packed, n, x, m, m, k, out, n, 0, 1, kGemmEpiAtomic, 0, bn, 1, err, stream);
   }
   const int bn = n >= 256 ? 256 : 128;
   const int tiles = ((m + 127) / 128) * ((n + bn - 1) / bn);
-  int chunks = tiles >= sm_count() ? 1 : pick_k_chunks(tiles, kblocks, 8);
-  const int epi = (accumulate || chunks > 1) ? kGemmEpiAtomic : kGemmEpiStore;
+  // few tiles: stream-K over (tile, K block) with the atomic epilogue keeps every SM busy
+  const int epi = (accumulate || tiles < 2 * sm_count()) ? kGemmEpiAtomic : kGemmEpiStore;
   if (epi == kGemmEpiAtomic && !accumulate)
     PTO_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * static_cast<size_t>(m) * n, stream));
-  return gemm_bf16_launch(x, m, w_packed, n, n, k, out, n, 0, 0, epi, 0, bn, chunks, err, stream);
+  return gemm_bf16_launch(x, m, w_packed, n, n, k, out, n, 0, 0, epi, 0, bn, 1, err, stream);
 }
 
 size_t ffn_workspace_bytes(int m, int inter) {

@@ -1,0 +1,340 @@
+// MoE routing and data movement: gate scores -> top-k, per-token FP8 quantisation, the
+// dispatch permutation (counts, offsets, slots), row permutes, and the weighted combine.
+//
+// The integer parts follow the expert-parallel dispatch protocol of the reference
+// (tests/st/distributed/test_l3_ep_dispatch_combine.py:104-299, golden :562-614):
+// bucket = global expert id (destination rank = id / L, local expert = id % L); inside a
+// bucket routes keep (t, k) lexicographic order; the route id carried with a row is
+// t * TOPK + k.  Counts, offsets, slots and route ids are exact integers, rows are copied
+// bit for bit.  The top-k is the descending selection with original indices that the
+// reference builds from sort32 + mrgsort + gather (tests/st/runtime/ops/test_sort.py:602-632),
+// ties going to the lower index.  The combine is combine_step (:337-402): y[t] = sum over k of
+// fp32(row), in k order.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace pto {
+namespace {
+
+constexpr int kMaxExpertsPerLane = 32;  // up to 1024 experts per token row
+
+// One warp per token.  scores_in holds logits (is_logits = 1: sigmoid applied here) or scores.
+__global__ void __launch_bounds__(256)
+moe_topk_kernel(const float* __restrict__ scores_in, const float* __restrict__ bias, int is_logits, int tokens,
+                int experts, int topk, int32_t* __restrict__ idx_out, float* __restrict__ w_out) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  float s[kMaxExpertsPerLane], sel[kMaxExpertsPerLane];
+  const int per = (experts + 31) / 32;
+#pragma unroll
+  for (int j = 0; j < kMaxExpertsPerLane; ++j) {
+    s[j] = 0.f;
+    sel[j] = -INFINITY;
+    if (j < per) {
+      const int e = j * 32 + lane;
+      if (e < experts) {
+        float v = scores_in[static_cast<size_t>(t) * experts + e];
+        if (is_logits) v = 1.f / (1.f + expf(-v));
+        s[j] = v;
+        sel[j] = v + (bias ? bias[e] : 0.f);
+      }
+    }
+  }
+  float picked_sum = 0.f, my_pick = 0.f;
+  int my_idx = 0;
+  for (int k = 0; k < topk; ++k) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < kMaxExpertsPerLane; ++j) {
+      if (j < per) {
+        const int e = j * 32 + lane;
+        if (sel[j] > best) { best = sel[j]; best_e = e; }  // ascending e per lane: ties keep the lower id
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    const int owner = best_e & 31, slot = best_e >> 5;
+    float sc = 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxExpertsPerLane; ++j)
+      if (j == slot && lane == owner) { sc = s[j]; sel[j] = -INFINITY; }
+    sc = __shfl_sync(0xffffffffu, sc, owner);
+    picked_sum += sc;
+    if (lane == k) { my_pick = sc; my_idx = best_e; }
+  }
+  if (lane < topk) {
+    idx_out[static_cast<size_t>(t) * topk + lane] = my_idx;
+    w_out[static_cast<size_t>(t) * topk + lane] = my_pick / picked_sum;
+  }
+}
+
+// One warp per (row, 128-column group): scale = amax / 448 (1 if the group is all zero),
+// q = e4m3(x / scale), round to nearest even, saturating.
+template <typename TI>
+__global__ void __launch_bounds__(256)
+quantize_rows_kernel(const TI* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale, long long rows,
+                     int cols) {
+  const int lane = threadIdx.x & 31;
+  const int groups = cols / 128;
+  const long long total = rows * groups;
+  for (long long g = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); g < total;
+       g += static_cast<long long>(gridDim.x) * (blockDim.x >> 5)) {
+    const long long r = g / groups;
+    const int c0 = static_cast<int>(g - r * groups) * 128 + lane * 4;
+    const TI* src = x + r * cols + c0;
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (sizeof(TI) == 2) v[i] = __bfloat162float(src[i]); else v[i] = src[i];
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    amax = warp_max(amax);
+    const float sc = amax > 0.f ? amax / 448.f : 1.f;
+    uint32_t packed = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(v[i] / sc, __NV_SATFINITE, __NV_E4M3);
+      packed |= static_cast<uint32_t>(b) << (8 * i);
+    }
+    *reinterpret_cast<uint32_t*>(q + r * cols + c0) = packed;
+    if (lane == 0) scale[g] = sc;
+  }
+}
+
+// One CTA per bucket (global expert id): count the routes of the bucket and give each its
+// rank in (t, k) order.  rank[r] is written only for routes of this bucket.
+__global__ void __launch_bounds__(256)
+moe_count_rank_kernel(const int32_t* __restrict__ expert_of, int routes, int32_t* __restrict__ counts,
+                      int32_t* __restrict__ rank) {
+  __shared__ int warp_tot[8];
+  __shared__ int running_s;
+  const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) running_s = 0;
+  __syncthreads();
+  for (int base = 0; base < routes; base += 256) {
+    const int r = base + threadIdx.x;
+    const bool mine = r < routes && expert_of[r] == e;
+    const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+    if (lane == 0) warp_tot[warp] = __popc(ballot);
+    __syncthreads();
+    int before = running_s;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    if (mine) rank[r] = before + __popc(ballot & ((1u << lane) - 1u));
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int tot = 0;
+      for (int w = 0; w < 8; ++w) tot += warp_tot[w];
+      running_s += tot;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) counts[e] = running_s;
+}
+
+// Single CTA: offsets[0..n] = exclusive scan of counts[0..n).
+__global__ void __launch_bounds__(1024) moe_offsets_kernel(const int32_t* __restrict__ counts, int n,
+                                                           int32_t* __restrict__ offsets) {
+  __shared__ int warp_sum_s[32];
+  __shared__ int carry_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  for (int base = 0; base < n; base += 1024) {
+    const int i = base + threadIdx.x;
+    const int v = i < n ? counts[i] : 0;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += u;
+    }
+    if (lane == 31) warp_sum_s[warp] = inc;
+    __syncthreads();
+    int before = carry_s;
+    for (int w = 0; w < warp; ++w) before += warp_sum_s[w];
+    if (i < n) offsets[i] = before + inc - v;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry_s = before + inc;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) offsets[n] = carry_s;
+}
+
+// pos[r] = offsets[expert_of[r]] + rank[r]; route_at[pos[r]] = r.
+__global__ void moe_positions_kernel(const int32_t* __restrict__ expert_of, const int32_t* __restrict__ rank,
+                                     const int32_t* __restrict__ offsets, int routes, int32_t* __restrict__ pos,
+                                     int32_t* __restrict__ route_at) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= routes) return;
+  const int p = offsets[expert_of[r]] + rank[r];
+  pos[r] = p;
+  route_at[p] = r;
+}
+
+// dst row p = src row (route_at[p] / topk) for each of `n_arrays` row-major byte arrays.
+// One warp per destination row; 16-byte copies (row sizes are multiples of 16 bytes or small).
+struct RowArrays {
+  const uint8_t* src[3];
+  uint8_t* dst[3];
+  int row_bytes[3];
+  int n;
+};
+
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(RowArrays a, const int32_t* __restrict__ src_row_of, int div, long long rows) {
+  const int lane = threadIdx.x & 31;
+  for (long long p = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); p < rows;
+       p += static_cast<long long>(gridDim.x) * (blockDim.x >> 5)) {
+    const long long s = src_row_of ? src_row_of[p] / div : p;
+    for (int i = 0; i < a.n; ++i) {
+      const int rb = a.row_bytes[i];
+      const uint8_t* sp = a.src[i] + s * rb;
+      uint8_t* dp = a.dst[i] + p * rb;
+      if ((rb & 15) == 0 && ((reinterpret_cast<uintptr_t>(sp) | reinterpret_cast<uintptr_t>(dp)) & 15) == 0) {
+        for (int c = lane; c < rb / 16; c += 32) reinterpret_cast<uint4*>(dp)[c] = reinterpret_cast<const uint4*>(sp)[c];
+      } else {
+        for (int c = lane; c < rb; c += 32) dp[c] = sp[c];
+      }
+    }
+  }
+}
+
+// route_weight_sorted[p] = weights[route_at[p]]
+__global__ void moe_gather_f32_kernel(const float* __restrict__ src, const int32_t* __restrict__ index, long long n,
+                                      float* __restrict__ dst) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = src[index[i]];
+}
+
+// y[t] = bf16( sum_k fp32(rows[pos[t*topk + k]]) + fp32(shared[t]) ), k ascending.
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __nv_bfloat16* __restrict__ rows, const int32_t* __restrict__ pos,
+                   const __nv_bfloat16* __restrict__ shared, int topk, int hidden, __nv_bfloat16* __restrict__ y,
+                   float* __restrict__ y32) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int k = 0; k < topk; ++k) {
+      const int p = pos[static_cast<size_t>(t) * topk + k];
+      if (p < 0) continue;
+      const uint4 v = *reinterpret_cast<const uint4*>(rows + static_cast<size_t>(p) * hidden + c);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[2 * i] += bf16_lo_to_float(w[i]);
+        acc[2 * i + 1] += bf16_hi_to_float(w[i]);
+      }
+    }
+    if (shared) {
+      const uint4 v = *reinterpret_cast<const uint4*>(shared + static_cast<size_t>(t) * hidden + c);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[2 * i] += bf16_lo_to_float(w[i]);
+        acc[2 * i + 1] += bf16_hi_to_float(w[i]);
+      }
+    }
+    if (y32) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y32[static_cast<size_t>(t) * hidden + c + i] = acc[i];
+    }
+    if (y) {
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * hidden + c) = o;
+    }
+  }
+}
+
+int grid_rows(long long rows, int warps_per_cta) {
+  long long g = (rows + warps_per_cta - 1) / warps_per_cta;
+  const long long cap = static_cast<long long>(sm_count()) * 8;
+  return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace
+
+int moe_topk_launch(const float* scores, const float* bias, int is_logits, int tokens, int experts, int topk,
+                    int32_t* idx, float* weights, cudaStream_t stream) {
+  PTO_REQUIRE(scores && idx && weights, "moe_topk: NULL tensor");
+  PTO_REQUIRE(experts > 0 && experts <= 32 * kMaxExpertsPerLane, "moe_topk: at most 1024 experts");
+  PTO_REQUIRE(topk > 0 && topk <= 32 && topk <= experts, "moe_topk: 1 <= topk <= min(32, experts)");
+  if (tokens <= 0) return kOk;
+  moe_topk_kernel<<<(tokens + 7) / 8, 256, 0, stream>>>(scores, bias, is_logits, tokens, experts, topk, idx, weights);
+  return check_cuda(cudaGetLastError(), "moe_topk_kernel launch");
+}
+
+int quantize_rows_launch(const void* x, int x_dtype, void* q, float* scale, long long rows, int cols,
+                         cudaStream_t stream) {
+  PTO_REQUIRE(x && q && scale, "quantize_rows: NULL tensor");
+  PTO_REQUIRE(cols > 0 && cols % 128 == 0, "quantize_rows: columns must be a multiple of 128");
+  if (rows <= 0) return kOk;
+  const int g = grid_rows(rows * (cols / 128), 8);
+  if (x_dtype == PTO_BF16)
+    quantize_rows_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scale, rows, cols);
+  else if (x_dtype == PTO_FP32)
+    quantize_rows_kernel<float><<<g, 256, 0, stream>>>(static_cast<const float*>(x), static_cast<uint8_t*>(q), scale, rows, cols);
+  else
+    return fail(kInvalidArgument, "quantize_rows: input must be bf16 or fp32");
+  return check_cuda(cudaGetLastError(), "quantize_rows_kernel launch");
+}
+
+// expert_of int32 [routes] -> counts [buckets], offsets [buckets + 1], pos [routes], route_at [routes].
+// `rank_tmp` is an int32 [routes] work array.
+int moe_dispatch_plan_launch(const int32_t* expert_of, int routes, int buckets, int32_t* counts, int32_t* offsets,
+                             int32_t* pos, int32_t* route_at, int32_t* rank_tmp, cudaStream_t stream) {
+  PTO_REQUIRE(expert_of && counts && offsets && pos && route_at && rank_tmp, "moe_dispatch_plan: NULL tensor");
+  PTO_REQUIRE(buckets > 0 && routes >= 0, "moe_dispatch_plan: bad sizes");
+  moe_count_rank_kernel<<<buckets, 256, 0, stream>>>(expert_of, routes, counts, rank_tmp);
+  PTO_CUDA(cudaGetLastError());
+  moe_offsets_kernel<<<1, 1024, 0, stream>>>(counts, buckets, offsets);
+  PTO_CUDA(cudaGetLastError());
+  if (routes > 0) {
+    moe_positions_kernel<<<(routes + 255) / 256, 256, 0, stream>>>(expert_of, rank_tmp, offsets, routes, pos, route_at);
+    PTO_CUDA(cudaGetLastError());
+  }
+  return kOk;
+}
+
+int moe_gather_rows_launch(const void* const* src, void* const* dst, const int* row_bytes, int n_arrays,
+                           const int32_t* src_row_of, int div, long long rows, cudaStream_t stream) {
+  PTO_REQUIRE(n_arrays >= 1 && n_arrays <= 3 && div >= 1, "moe_gather_rows: 1..3 arrays, div >= 1");
+  if (rows <= 0) return kOk;
+  RowArrays a;
+  a.n = n_arrays;
+  for (int i = 0; i < n_arrays; ++i) {
+    PTO_REQUIRE(src[i] && dst[i] && row_bytes[i] > 0, "moe_gather_rows: NULL array or empty row");
+    a.src[i] = static_cast<const uint8_t*>(src[i]);
+    a.dst[i] = static_cast<uint8_t*>(dst[i]);
+    a.row_bytes[i] = row_bytes[i];
+  }
+  moe_gather_rows_kernel<<<grid_rows(rows, 8), 256, 0, stream>>>(a, src_row_of, div, rows);
+  return check_cuda(cudaGetLastError(), "moe_gather_rows_kernel launch");
+}
+
+int moe_gather_f32_launch(const float* src, const int32_t* index, long long n, float* dst, cudaStream_t stream) {
+  PTO_REQUIRE(src && index && dst, "moe_gather_f32: NULL tensor");
+  if (n <= 0) return kOk;
+  moe_gather_f32_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(src, index, n, dst);
+  return check_cuda(cudaGetLastError(), "moe_gather_f32_kernel launch");
+}
+
+int moe_combine_launch(const void* rows, const int32_t* pos, const void* shared, int tokens, int topk, int hidden,
+                       void* y_bf16, float* y_f32, cudaStream_t stream) {
+  PTO_REQUIRE(rows && pos && (y_bf16 || y_f32), "moe_combine: NULL tensor");
+  PTO_REQUIRE(hidden > 0 && hidden % 8 == 0 && topk > 0, "moe_combine: hidden must be a multiple of 8");
+  if (tokens <= 0) return kOk;
+  moe_combine_kernel<<<tokens, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(rows), pos,
+                                                 static_cast<const __nv_bfloat16*>(shared), topk, hidden,
+                                                 static_cast<__nv_bfloat16*>(y_bf16), y_f32);
+  return check_cuda(cudaGetLastError(), "moe_combine_kernel launch");
+}
+
+}  // namespace pto

@@ -216,4 +216,44 @@ int pto_swiglu_act(const float* gate_up, void* act, int64_t rows, int inter, voi
   return pto::swiglu_act_launch(gate_up, act, rows, inter, static_cast<cudaStream_t>(stream));
 }
 
+int pto_moe_topk(const float* scores, const float* bias, int is_logits, int tokens, int experts, int topk,
+                 int32_t* idx, float* weights, void* stream) {
+  return pto::moe_topk_launch(scores, bias, is_logits, tokens, experts, topk, idx, weights,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int pto_quantize_rows(const void* x, int x_dtype, void* q, float* scale, int64_t rows, int cols, void* stream) {
+  return pto::quantize_rows_launch(x, x_dtype, q, scale, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+int pto_moe_dispatch_plan(const int32_t* expert_of, int routes, int buckets, int32_t* counts, int32_t* offsets,
+                          int32_t* pos, int32_t* route_at, int32_t* rank_tmp, void* stream) {
+  return pto::moe_dispatch_plan_launch(expert_of, routes, buckets, counts, offsets, pos, route_at, rank_tmp,
+                                       static_cast<cudaStream_t>(stream));
+}
+
+int pto_moe_gather_rows(const void* const* src, void* const* dst, const int* row_bytes, int n_arrays,
+                        const int32_t* index, int div, int64_t rows, void* stream) {
+  if (!src || !dst || !row_bytes) return pto::fail(pto::kInvalidArgument, "moe_gather_rows: NULL argument");
+  return pto::moe_gather_rows_launch(src, dst, row_bytes, n_arrays, index, div, rows,
+                                     static_cast<cudaStream_t>(stream));
+}
+
+int pto_moe_gather_f32(const float* src, const int32_t* index, int64_t n, float* dst, void* stream) {
+  return pto::moe_gather_f32_launch(src, index, n, dst, static_cast<cudaStream_t>(stream));
+}
+
+int pto_moe_expert_gemm(int dual, const void* w, const float* w_scale, int experts, int w_rows, int n_out, int k,
+                        const void* x, const float* x_scale, const int32_t* offsets, int rows, const float* route_w,
+                        void* act_q, float* act_scale, void* out, int32_t* err, void* stream) {
+  return pto::moe_gemm_fp8_launch(dual, w, w_scale, experts, w_rows, n_out, k, x, x_scale, offsets, rows, route_w,
+                                  act_q, act_scale, out, err, static_cast<cudaStream_t>(stream));
+}
+
+int pto_moe_combine(const void* rows, const int32_t* pos, const void* shared, int tokens, int topk, int hidden,
+                    void* y_bf16, float* y_f32, void* stream) {
+  return pto::moe_combine_launch(rows, pos, shared, tokens, topk, hidden, y_bf16, y_f32,
+                                 static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

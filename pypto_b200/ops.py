@@ -290,3 +290,123 @@ def swiglu_act(gate_up: torch.Tensor) -> torch.Tensor:
     with torch.cuda.device(dev):
         _lib.check(_lib.load().pto_swiglu_act(gate_up.data_ptr(), out.data_ptr(), rows, two_i // 2, _stream_ptr(dev)))
     return out
+
+
+# ---------------------------------------------------------------------------
+# mixture of experts
+# ---------------------------------------------------------------------------
+
+FP8 = torch.float8_e4m3fn
+
+
+def moe_topk(scores: torch.Tensor, bias: torch.Tensor | None, topk: int, is_logits: bool = False):
+    """(indices int32 [T, k], weights fp32 [T, k]); selection on score + bias, ties to the lower id."""
+    dev = _need_cuda(scores) if bias is None else _need_cuda(scores, bias)
+    if scores.dtype != torch.float32 or scores.dim() != 2:
+        raise TypeError("moe_topk: scores must be fp32 [tokens, experts]")
+    t, e = scores.shape
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != e):
+        raise ValueError("moe_topk: bias must be fp32 [experts]")
+    idx = torch.empty(t, topk, dtype=torch.int32, device=dev)
+    w = torch.empty(t, topk, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_moe_topk(scores.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                            1 if is_logits else 0, t, e, topk, idx.data_ptr(), w.data_ptr(),
+                                            _stream_ptr(dev)))
+    return idx, w
+
+
+def quantize_rows(x: torch.Tensor):
+    """(q e4m3 [rows, cols], scale fp32 [rows, cols/128]) with scale = amax/448 per 128 columns."""
+    dev = _need_cuda(x)
+    if x.dim() != 2 or x.shape[1] % 128 or x.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("quantize_rows: x must be bf16/fp32 [rows, cols] with cols % 128 == 0")
+    rows, cols = x.shape
+    q = torch.empty(rows, cols, dtype=FP8, device=dev)
+    s = torch.empty(rows, cols // 128, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_quantize_rows(x.data_ptr(), dtype_code(x.dtype), q.data_ptr(), s.data_ptr(), rows,
+                                                 cols, _stream_ptr(dev)))
+    return q, s
+
+
+def moe_dispatch_plan(expert_of: torch.Tensor, buckets: int):
+    """counts [buckets], offsets [buckets+1], pos [routes], route_at [routes] (all int32)."""
+    dev = _need_cuda(expert_of)
+    if expert_of.dtype != torch.int32:
+        raise TypeError("moe_dispatch_plan: expert ids must be int32")
+    n = expert_of.numel()
+    counts = torch.empty(buckets, dtype=torch.int32, device=dev)
+    offsets = torch.empty(buckets + 1, dtype=torch.int32, device=dev)
+    pos = torch.empty(n, dtype=torch.int32, device=dev)
+    route_at = torch.empty(n, dtype=torch.int32, device=dev)
+    tmp = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_moe_dispatch_plan(expert_of.data_ptr(), n, buckets, counts.data_ptr(),
+                                                     offsets.data_ptr(), pos.data_ptr(), route_at.data_ptr(),
+                                                     tmp.data_ptr(), _stream_ptr(dev)))
+    return counts, offsets, pos, route_at
+
+
+def gather_rows(sources: list, index: torch.Tensor | None, div: int = 1, rows: int | None = None):
+    """dst_i[p] = src_i[index[p] // div] for up to three 2-D (or 1-D) tensors; bit-exact copies."""
+    import ctypes as C
+    dev = _need_cuda(*sources) if index is None else _need_cuda(*sources, index)
+    n = len(sources)
+    if not 1 <= n <= 3:
+        raise ValueError("gather_rows: 1..3 source tensors")
+    rows = (index.numel() if index is not None else sources[0].shape[0]) if rows is None else rows
+    outs = [torch.empty((rows,) + tuple(s.shape[1:]), dtype=s.dtype, device=dev) for s in sources]
+    rb = [(s.numel() // s.shape[0]) * s.element_size() if s.shape[0] else 0 for s in sources]
+    if rows == 0 or any(b == 0 for b in rb):
+        return outs
+    src = (C.c_void_p * n)(*[s.data_ptr() for s in sources])
+    dst = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+    rbs = (C.c_int * n)(*rb)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_moe_gather_rows(src, dst, rbs, n, index.data_ptr() if index is not None else None,
+                                                   div, rows, _stream_ptr(dev)))
+    return outs
+
+
+def moe_expert_gemm(dual: bool, w: torch.Tensor, w_scale: torch.Tensor, x: torch.Tensor, x_scale: torch.Tensor,
+                    offsets: torch.Tensor, route_w: torch.Tensor | None = None):
+    """Grouped FP8 GEMM over tokens sorted by expert.  w [E, rows, K] e4m3 (K-major), w_scale
+    [E, rows/128, K/128]; x [R, K] e4m3, x_scale [R, K/128]; offsets int32 [E+1].
+    dual: returns (act_q [R, rows/2] e4m3, act_scale [R, rows/256]); else bf16 [R, rows]."""
+    dev = _need_cuda(w, w_scale, x, x_scale, offsets)
+    e, w_rows, k = w.shape
+    r = x.shape[0]
+    n_out = w_rows // 2 if dual else w_rows
+    if x.shape[1] != k or x_scale.shape != (r, k // 128) or w_scale.shape != (e, w_rows // 128, k // 128):
+        raise ValueError("moe_expert_gemm: operand shapes do not match")
+    if offsets.dtype != torch.int32 or offsets.numel() != e + 1:
+        raise ValueError("moe_expert_gemm: offsets must be int32 [experts + 1]")
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        if dual:
+            act_q = torch.empty(r, n_out, dtype=FP8, device=dev)
+            act_s = torch.empty(r, n_out // 128, dtype=torch.float32, device=dev)
+            _lib.check(lib.pto_moe_expert_gemm(1, w.data_ptr(), w_scale.data_ptr(), e, w_rows, n_out, k, x.data_ptr(),
+                                               x_scale.data_ptr(), offsets.data_ptr(), r, None, act_q.data_ptr(),
+                                               act_s.data_ptr(), None, _err_ptr(dev), _stream_ptr(dev)))
+            return act_q, act_s
+        out = torch.empty(r, n_out, dtype=torch.bfloat16, device=dev)
+        _lib.check(lib.pto_moe_expert_gemm(0, w.data_ptr(), w_scale.data_ptr(), e, w_rows, n_out, k, x.data_ptr(),
+                                           x_scale.data_ptr(), offsets.data_ptr(), r,
+                                           route_w.data_ptr() if route_w is not None else None, None, None,
+                                           out.data_ptr(), _err_ptr(dev), _stream_ptr(dev)))
+        return out
+
+
+def moe_combine(rows: torch.Tensor, pos: torch.Tensor, shared: torch.Tensor | None, tokens: int, topk: int,
+                want_f32: bool = False):
+    dev = _need_cuda(rows, pos) if shared is None else _need_cuda(rows, pos, shared)
+    hidden = rows.shape[1]
+    y = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=dev)
+    y32 = torch.empty(tokens, hidden, dtype=torch.float32, device=dev) if want_f32 else None
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_moe_combine(rows.data_ptr(), pos.data_ptr(),
+                                               shared.data_ptr() if shared is not None else None, tokens, topk, hidden,
+                                               y.data_ptr(), y32.data_ptr() if want_f32 else None, _stream_ptr(dev)))
+    return (y, y32) if want_f32 else y
