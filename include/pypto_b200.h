@@ -245,13 +245,12 @@ PTO_API int pto_moe_gather_f32(const float* src, const int32_t* index, int64_t n
  * test_l3_ep_dispatch_combine.py:309-327, by the SwiGLU expert FFN).
  *   w fp8 [experts * w_rows, k] K-major, w_scale fp32 [experts][w_rows / 128][k / 128]
  *   x fp8 [rows, k], x_scale fp32 [rows][k / 128], offsets int32 [experts + 1]
- * dual = 1: w_rows = 2 * n_out (gate rows then up rows); writes act_q fp8 [rows, n_out] and
- *           act_scale fp32 [rows, n_out / 128] = requantised bf16(silu(gate) * up).
- * dual = 0: w_rows = n_out; writes out bf16 [rows, n_out] = acc * route_w[row] (route_w may be NULL). */
-PTO_API int pto_moe_expert_gemm(int dual, const void* w, const float* w_scale, int experts, int w_rows,
+ * swiglu = 1: w_rows = 2 * n_out (gate rows then up rows); out bf16 [rows, n_out] =
+ *             bf16(silu(gate) * up) (re-quantise it with pto_quantize_rows for the down projection).
+ * swiglu = 0: w_rows = n_out; out bf16 [rows, n_out] = acc * route_w[row] (route_w may be NULL). */
+PTO_API int pto_moe_expert_gemm(int swiglu, const void* w, const float* w_scale, int experts, int w_rows,
                                 int n_out, int k, const void* x, const float* x_scale, const int32_t* offsets,
-                                int rows, const float* route_w, void* act_q, float* act_scale, void* out,
-                                int32_t* err, void* stream);
+                                int rows, const float* route_w, void* out, int32_t* err, void* stream);
 
 /* Combine (combine_step, test_l3_ep_dispatch_combine.py:337-402): y[t] = sum_k fp32(rows[pos[t*topk+k]])
  * (+ fp32(shared[t]) if given), k ascending; written as bf16 (y_bf16) and/or fp32 (y_f32). */

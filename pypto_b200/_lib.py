@@ -74,7 +74,7 @@ SIGNATURES = {
     "pto_moe_dispatch_plan": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p]),
     "pto_moe_gather_rows": (_i, [C.POINTER(_p), C.POINTER(_p), C.POINTER(_i), _i, _p, _i, _i64, _p]),
     "pto_moe_gather_f32": (_i, [_p, _p, _i64, _p, _p]),
-    "pto_moe_expert_gemm": (_i, [_i, _p, _p, _i, _i, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p, _p]),
+    "pto_moe_expert_gemm": (_i, [_i, _p, _p, _i, _i, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p]),
     "pto_moe_combine": (_i, [_p, _p, _p, _i, _i, _i, _p, _p, _p]),
     "pto_paged_gather": (_i, [_p, _i64, _i64, _i, _p, _i64, _p, _i64, _i, _i64, _i64, _p, _p, _p]),
 }

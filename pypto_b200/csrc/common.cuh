@@ -106,16 +106,50 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait: every spin in these kernels gives up after a fixed number of
-// polls so that a protocol bug ends the kernel with an error word instead of
-// hanging the device.  Returns false on timeout.
-constexpr uint32_t kMaxPolls = 1u << 22;
+// Bounded wait: every spin in these kernels gives up after about one second of wall time
+// (measured with %globaltimer, checked every 256 polls) so that a protocol bug ends the
+// kernel with an error word instead of hanging the device.  Returns false on timeout.
+constexpr unsigned long long kWaitTimeoutNs = 1000ull * 1000ull * 1000ull;
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Low-latency variant: non-suspending polls (mbarrier.test_wait), same one-second bound.
+__device__ __forceinline__ bool mbar_spin_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 1024; ++i)
+      if (mbar_test_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > kWaitTimeoutNs) return false;
+  }
+}
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kMaxPolls; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > kWaitTimeoutNs) return false;
   }
-  return false;
 }
 
 // 2-D tiled TMA load into this CTA's shared memory; completion is signalled on

@@ -71,9 +71,8 @@ int moe_combine_launch(const void* rows, const int32_t* pos, const void* shared,
                        void* y_bf16, float* y_f32, cudaStream_t stream);
 
 // moe_gemm.cu
-int moe_gemm_fp8_launch(int dual, const void* w, const float* w_scale, int experts, int w_rows_per_expert,
+int moe_gemm_fp8_launch(int swiglu, const void* w, const float* w_scale, int experts, int w_rows_per_expert,
                         int n_out, int k, const void* x, const float* x_scale, const int32_t* offsets,
-                        int total_rows, const float* route_w, void* act_q, float* act_scale, void* out, int* err,
-                        cudaStream_t stream);
+                        int total_rows, const float* route_w, void* out, int* err, cudaStream_t stream);
 
 }  // namespace pto

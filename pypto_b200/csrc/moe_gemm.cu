@@ -12,20 +12,20 @@
 //               ( sum_k xq[t, k] * wq[n, k] ) * xs[t, kb] * ws[n / 128, kb]
 //
 // Tokens arrive sorted by expert (rows offsets[e] .. offsets[e+1]).  One work unit is
-// (expert, 128-feature tile, chunk of up to 128 tokens).  The weight tile fills the 128 TMEM
-// lanes (A operand), the tokens are the MMA N dimension, so every weight byte of an expert
+// (expert, 128-row weight tile, chunk of up to 128 tokens).  The weight tile fills the 128
+// TMEM lanes (A operand), tokens are the MMA N dimension, so every weight byte of an expert
 // is streamed once per token chunk -- the kernel is weight-bandwidth bound at ~128 tokens per
-// expert.  Per K block the raw fp8 product lands in a TMEM partial buffer (double buffered);
-// sixteen promotion warps pull it into registers, multiply by the two scales and accumulate in
-// fp32 while the tensor core works on the next K block.
+// expert.  Per K block the raw fp8 products land in one of four TMEM partial buffers; sixteen
+// promotion warps pull them into registers (32 fp32 accumulators per thread), multiply by the
+// two scales and accumulate while the tensor core fills the other buffers.
 //
-//   mode GEMM1 (dual): gate and up tiles share the token tile; epilogue = bf16(silu(g) * u),
-//                      then re-quantisation per (token, 128 features) to e4m3 + scale, which
-//                      is exactly one tile wide.
-//   mode GEMM2:        epilogue = bf16(acc * route_weight[token]).
+//   SwiGLU mode: the tile is 64 gate rows + the 64 matching up rows; the epilogue pairs them
+//                through shared memory and writes bf16(silu(g) * u).  (The per-(token, 128)
+//                re-quantisation for the down projection is a separate row pass.)
+//   plain mode:  128 output features; epilogue = bf16(acc * route_weight[token]).
 //
-// CTA = 18 warps: TMA producer, MMA issuer, 16 promotion/epilogue warps (4 per TMEM lane
-// quarter, 32 token columns each).  Bounded waits.
+// CTA = 20 warps: two TMA producers and two MMA issuers (alternating K blocks), 16
+// promotion/epilogue warps (4 per TMEM lane quarter, 32 token columns each).  Bounded waits.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -34,56 +34,58 @@ namespace {
 
 constexpr int kTN = 128;          // tokens per chunk = MMA N
 constexpr int kPromoWarps = 16;
-constexpr int kMoeThreads = 64 + kPromoWarps * 32;
-constexpr int kColsPerWarp = kTN / (kPromoWarps / 4);  // 32 token columns per promotion warp
+constexpr int kRoleWarps = 4;      // two TMA producers and two MMA issuers, alternating K blocks
+constexpr int kMoeThreads = (kRoleWarps + kPromoWarps) * 32;
+constexpr int kNumPartial = 4;    // TMEM partial buffers of 128 token columns
 constexpr int kMoeMaxStages = 8;
 
 struct MoeGemmParams {
   const int32_t* offsets;   // [experts + 1]
-  int experts, n_tiles, kblocks, dual;
-  int w_rows_per_expert, up_row_off;
+  int experts, n_tiles, kblocks;
+  int w_rows_per_expert, up_row_off;   // SwiGLU: up rows start up_row_off rows after the gate rows
+  int n_out;                // output features per row
   const float* w_scale;     // [experts][w_rows_per_expert / 128][kblocks]
   const float* x_scale;     // [rows][kblocks]
   const float* route_w;     // [rows] or NULL
-  uint8_t* act_q;           // GEMM1: [rows][n_tiles * 128]
-  float* act_scale;         // GEMM1: [rows][n_tiles]
-  __nv_bfloat16* out;       // GEMM2: [rows][n_tiles * 128]
+  __nv_bfloat16* out;       // [rows][n_out]
   int total_rows, stages;
   int* err;
 };
 
-__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-
-template <bool DUAL>
+// A unit = (expert, weight tile, chunk of 128 tokens).
+//   plain mode:  the tile is 128 consecutive output features.
+//   SwiGLU mode: the tile is 64 gate rows (TMEM lanes 0-63) followed by the 64 matching up
+//                rows (lanes 64-127); the epilogue pairs them through shared memory and
+//                writes bf16(silu(g) * u) for 64 features.
+template <bool SWIGLU>
 __global__ void __launch_bounds__(kMoeThreads, 1)
 moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                     const MoeGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  constexpr int nacc = DUAL ? 2 : 1;
   const uint32_t tile_bytes = 128 * 128;
-  const uint32_t stage_bytes = (nacc + 1) * tile_bytes;
+  const uint32_t stage_bytes = 2 * tile_bytes;   // weight tile, token tile
   uint8_t* after = smem + static_cast<size_t>(p.stages) * stage_bytes;
   float* xs_s = reinterpret_cast<float*>(after);                       // [kblocks][kTN]
   float* ws_s = xs_s + static_cast<size_t>(p.kblocks) * kTN;           // [2][kblocks]
-  float* amax_s = ws_s + 2 * p.kblocks;                                // [4][kTN]
-  int* prefix = reinterpret_cast<int*>(amax_s + 4 * kTN);              // [experts + 1] chunk prefix
+  float* exch = ws_s + 2 * p.kblocks;                                  // SwiGLU: [kTN][64] up values
+  int* prefix = reinterpret_cast<int*>(exch + (SWIGLU ? 64 * kTN : 0)); // [experts + 1] chunk prefix
   uint64_t* full = reinterpret_cast<uint64_t*>(prefix + ((p.experts + 2) & ~1));
   uint64_t* empty = full + kMoeMaxStages;
   uint64_t* pfull = empty + kMoeMaxStages;
-  uint64_t* pempty = pfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pempty + 2);
+  uint64_t* pempty = pfull + kNumPartial;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pempty + kNumPartial);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr uint32_t tmem_cols = DUAL ? 512 : 256;  // 2 partial buffers x nacc x 128 columns
+  constexpr uint32_t tmem_cols = kNumPartial * kTN;  // 512
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < p.stages; ++i) {
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kNumPartial; ++i) {
       mbar_init(&pfull[i], 1);
       mbar_init(&pempty[i], kPromoWarps);
     }
@@ -91,7 +93,7 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_x);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
+  if (warp == 2) tmem_alloc(tmem_slot, tmem_cols);
   // chunk prefix over experts: prefix[e] = number of token chunks of experts before e
   for (int e = threadIdx.x; e < p.experts; e += kMoeThreads) {
     const int n = p.offsets[e + 1] - p.offsets[e];
@@ -135,17 +137,21 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     chunk = rem - tile * chunks;
   };
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
+  // A single thread needs several hundred cycles per K block for its barrier waits, TMA or MMA
+  // issues and commits; two producers and two issuers take alternate K blocks to keep up.
+  if (warp < 2) {
+    // ------------------------------ TMA producers ------------------------------
     if (lane == 0) {
+      const uint32_t me = static_cast<uint32_t>(warp);
       uint32_t it = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
         int e, tile, chunk;
         decode(u, e, tile, chunk);
         const int row0 = p.offsets[e] + chunk * kTN;
-        const int wrow = e * p.w_rows_per_expert + tile * 128;
+        const int wrow = e * p.w_rows_per_expert + tile * (SWIGLU ? 64 : 128);
         for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          if ((it & 1u) != me) continue;
           const uint32_t s = it % p.stages, round = it / p.stages;
           if (!mbar_wait(&empty[s], (round & 1u) ^ 1u)) {
             report_error(p.err, kErrBarrierTimeout, 50, static_cast<int>(it));
@@ -154,37 +160,40 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           }
           uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
           mbar_arrive_expect_tx(&full[s], stage_bytes);
-          tma_load_2d(st, &tm_w, kb * 128, wrow, &full[s]);
-          if (DUAL) tma_load_2d(st + tile_bytes, &tm_w, kb * 128, wrow + p.up_row_off, &full[s]);
-          tma_load_2d(st + nacc * tile_bytes, &tm_x, kb * 128, row0, &full[s]);
+          if (SWIGLU) {   // two 64-row boxes: gate rows, then the matching up rows
+            tma_load_2d(st, &tm_w, kb * 128, wrow, &full[s]);
+            tma_load_2d(st + 64 * 128, &tm_w, kb * 128, wrow + p.up_row_off, &full[s]);
+          } else {
+            tma_load_2d(st, &tm_w, kb * 128, wrow, &full[s]);
+          }
+          tma_load_2d(st + tile_bytes, &tm_x, kb * 128, row0, &full[s]);
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
+  } else if (warp < kRoleWarps) {
+    // ------------------------------- MMA issuers -------------------------------
     if (lane == 0) {
+      const uint32_t me = static_cast<uint32_t>(warp - 2);
       const uint32_t idesc = umma_idesc(128, kTN, 0, 0);  // e4m3 x e4m3 -> fp32
       uint32_t it = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
         for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          if ((it & 1u) != me) continue;
           const uint32_t s = it % p.stages, round = it / p.stages;
-          const uint32_t pb = it & 1u;
-          if (!mbar_wait(&full[s], round & 1u) || !mbar_wait(&pempty[pb], ((it >> 1) & 1u) ^ 1u)) {
+          const uint32_t pb = it % kNumPartial;
+          if (!mbar_wait(&full[s], round & 1u) || !mbar_wait(&pempty[pb], ((it / kNumPartial) & 1u) ^ 1u)) {
             report_error(p.err, kErrBarrierTimeout, 51, static_cast<int>(it));
             ok = false;
             break;
           }
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
-          const uint32_t x_addr = a_addr + nacc * tile_bytes;
-          const uint32_t d0 = tmem_base + pb * (nacc * kTN);
+          const uint32_t x_addr = a_addr + tile_bytes;
+          const uint32_t d0 = tmem_base + pb * kTN;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t xd = umma_desc_sw128(x_addr + k * 32);
-            umma_fp8(d0, umma_desc_sw128(a_addr + k * 32), xd, idesc, k > 0 ? 1u : 0u);
-            if (DUAL) umma_fp8(d0 + kTN, umma_desc_sw128(a_addr + tile_bytes + k * 32), xd, idesc, k > 0 ? 1u : 0u);
-          }
+          for (int k = 0; k < 4; ++k)
+            umma_fp8(d0, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(x_addr + k * 32), idesc, k > 0 ? 1u : 0u);
           umma_commit(&empty[s]);
           umma_commit(&pfull[pb]);
         }
@@ -193,10 +202,10 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     __syncwarp();
   } else {
     // -------------------------- promotion + epilogue --------------------------
-    const int pw = warp - 2;         // 0..15
+    const int pw = warp - kRoleWarps; // 0..15
     const int q = warp & 3;          // TMEM lane quarter of this warp
-    const int col0 = (pw >> 2) * kColsPerWarp;  // first token column of this warp
-    const int ptid = threadIdx.x - 64;
+    const int col0 = (pw >> 2) * 32; // first of this warp's 32 token columns
+    const int ptid = threadIdx.x - kRoleWarps * 32;
     uint32_t it = 0;
     bool dead = false;
     for (int u = blockIdx.x; u < units; u += gridDim.x) {
@@ -204,135 +213,114 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       decode(u, e, tile, chunk);
       const int row0 = p.offsets[e] + chunk * kTN;
       const int row_end = min(p.offsets[e + 1], p.total_rows);
-      named_bar_sync(1, kPromoWarps * 32);  // previous unit's scales no longer in use
+      named_bar_sync(1, kPromoWarps * 32);  // previous unit's scales / exchange buffer no longer in use
       for (int i = ptid; i < kTN * p.kblocks; i += kPromoWarps * 32) {
-        const int col = i / p.kblocks, kb = i - col * p.kblocks;
+        const int kb = i / kTN, col = i - kb * kTN;
         const int row = row0 + col;
-        xs_s[kb * kTN + col] = row < row_end ? p.x_scale[static_cast<size_t>(row) * p.kblocks + kb] : 0.f;
+        xs_s[i] = row < row_end ? p.x_scale[static_cast<size_t>(row) * p.kblocks + kb] : 0.f;
       }
-      for (int i = ptid; i < nacc * p.kblocks; i += kPromoWarps * 32) {
+      for (int i = ptid; i < 2 * p.kblocks; i += kPromoWarps * 32) {
         const int a = i / p.kblocks, kb = i - a * p.kblocks;
-        const int wblk = (e * p.w_rows_per_expert + a * p.up_row_off) / 128 + tile;
-        ws_s[a * p.kblocks + kb] = p.w_scale[static_cast<size_t>(wblk) * p.kblocks + kb];
+        const int wrow = e * p.w_rows_per_expert + (SWIGLU ? tile * 64 + a * p.up_row_off : tile * 128);
+        ws_s[i] = p.w_scale[static_cast<size_t>(wrow / 128) * p.kblocks + kb];
       }
       named_bar_sync(1, kPromoWarps * 32);
+      const float* ws = ws_s + ((SWIGLU && q >= 2) ? p.kblocks : 0);   // lanes 64-127 hold up rows
 
-      float acc_g[kColsPerWarp], acc_u[DUAL ? kColsPerWarp : 1];
+      float acc[32];
 #pragma unroll
-      for (int j = 0; j < kColsPerWarp; ++j) acc_g[j] = 0.f;
-#pragma unroll
-      for (int j = 0; j < (DUAL ? kColsPerWarp : 1); ++j) acc_u[j] = 0.f;
+      for (int j = 0; j < 32; ++j) acc[j] = 0.f;
 
       for (int kb = 0; kb < p.kblocks && !dead; ++kb, ++it) {
-        const uint32_t pb = it & 1u;
-        if (!mbar_wait(&pfull[pb], (it >> 1) & 1u)) {
+        const uint32_t pb = it % kNumPartial;
+        if (!mbar_wait(&pfull[pb], (it / kNumPartial) & 1u)) {
           report_error(p.err, kErrBarrierTimeout, 52, static_cast<int>(it));
           dead = true;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + pb * (nacc * kTN) + col0;
-        const float sg = ws_s[kb], su = DUAL ? ws_s[p.kblocks + kb] : 0.f;
-        const float* xs = xs_s + kb * kTN + col0;
-#pragma unroll
-        for (int c = 0; c < kColsPerWarp; c += 16) {
-          uint32_t v[16];
-          tmem_ld_32x16(taddr + c, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; j += 4) {
-            const float4 x4 = *reinterpret_cast<const float4*>(xs + c + j);
-            acc_g[c + j] += __uint_as_float(v[j]) * (sg * x4.x);
-            acc_g[c + j + 1] += __uint_as_float(v[j + 1]) * (sg * x4.y);
-            acc_g[c + j + 2] += __uint_as_float(v[j + 2]) * (sg * x4.z);
-            acc_g[c + j + 3] += __uint_as_float(v[j + 3]) * (sg * x4.w);
-          }
-          if constexpr (DUAL) {
-            tmem_ld_32x16(taddr + kTN + c, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; j += 4) {
-              const float4 x4 = *reinterpret_cast<const float4*>(xs + c + j);
-              acc_u[c + j] += __uint_as_float(v[j]) * (su * x4.x);
-              acc_u[c + j + 1] += __uint_as_float(v[j + 1]) * (su * x4.y);
-              acc_u[c + j + 2] += __uint_as_float(v[j + 2]) * (su * x4.z);
-              acc_u[c + j + 3] += __uint_as_float(v[j + 3]) * (su * x4.w);
-            }
-          }
-        }
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + pb * kTN + col0;
+        uint32_t v[32];
+        tmem_ld_32x32(taddr, v);
+        tmem_ld_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&pempty[pb]);
-      }
-
-      const int feat = tile * 128 + q * 32 + lane;
-      const int ld = p.n_tiles * 128;
-      if constexpr (DUAL) {
-        // bf16(silu(g) * u), then one e4m3 scale per (token, this 128-feature tile)
+        const float sw = ws[kb];
+        const float* xs = xs_s + kb * kTN + col0;
 #pragma unroll
-        for (int j = 0; j < kColsPerWarp; ++j) {
-          const float g = acc_g[j];
-          const float a = bf16_round(g * (1.f / (1.f + __expf(-g))) * acc_u[j]);
-          acc_g[j] = a;
-          const unsigned m = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(a)));
-          if (lane == j) amax_s[q * kTN + col0 + j] = __uint_as_float(m);
+        for (int j = 0; j < 32; j += 4) {
+          const float4 x4 = *reinterpret_cast<const float4*>(xs + j);
+          acc[j] = fmaf(__uint_as_float(v[j]), sw * x4.x, acc[j]);
+          acc[j + 1] = fmaf(__uint_as_float(v[j + 1]), sw * x4.y, acc[j + 1]);
+          acc[j + 2] = fmaf(__uint_as_float(v[j + 2]), sw * x4.z, acc[j + 2]);
+          acc[j + 3] = fmaf(__uint_as_float(v[j + 3]), sw * x4.w, acc[j + 3]);
         }
-        named_bar_sync(1, kPromoWarps * 32);
-        if (!dead) {
+      }
+      // a warp that timed out keeps walking the units so that the named barriers stay matched
+
+      if constexpr (SWIGLU) {
+        // lanes 64-127 (up rows) hand their values to lanes 0-63 (gate rows) of the same feature
+        if (q >= 2 && !dead) {
 #pragma unroll
-          for (int j = 0; j < kColsPerWarp; ++j) {
-            const int col = col0 + j, row = row0 + col;
-            if (row >= row_end) break;
-            const float amax = fmaxf(fmaxf(amax_s[col], amax_s[kTN + col]), fmaxf(amax_s[2 * kTN + col], amax_s[3 * kTN + col]));
-            const float sc = amax > 0.f ? amax / 448.f : 1.f;
-            p.act_q[static_cast<size_t>(row) * ld + feat] =
-                static_cast<uint8_t>(__nv_cvt_float_to_fp8(acc_g[j] / sc, __NV_SATFINITE, __NV_E4M3));
-            if (q == 0 && lane == j) p.act_scale[static_cast<size_t>(row) * p.n_tiles + tile] = sc;
+          for (int j = 0; j < 32; ++j) exch[(col0 + j) * 64 + (q - 2) * 32 + lane] = acc[j];
+        }
+        named_bar_sync(2, kPromoWarps * 32);
+        if (q < 2 && !dead) {
+          const int feat = tile * 64 + q * 32 + lane;
+          const float* up = exch + col0 * 64 + q * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int row = row0 + col0 + j;
+            if (row < row_end) {
+              const float g = acc[j];
+              p.out[static_cast<size_t>(row) * p.n_out + feat] =
+                  __float2bfloat16_rn(g * (1.f / (1.f + __expf(-g))) * up[j * 64]);
+            }
           }
         }
-      } else {
-        if (!dead) {
+      } else if (!dead) {
+        const int feat = tile * 128 + q * 32 + lane;
 #pragma unroll
-        for (int j = 0; j < kColsPerWarp; ++j) {
+        for (int j = 0; j < 32; ++j) {
           const int row = row0 + col0 + j;
-          if (row >= row_end) break;
-          const float wgt = p.route_w ? p.route_w[row] : 1.f;
-          p.out[static_cast<size_t>(row) * ld + feat] = __float2bfloat16_rn(acc_g[j] * wgt);
-        }
+          if (row < row_end) {
+            const float wgt = p.route_w ? p.route_w[row] : 1.f;
+            p.out[static_cast<size_t>(row) * p.n_out + feat] = __float2bfloat16_rn(acc[j] * wgt);
+          }
         }
       }
     }
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+  if (warp == 2) tmem_dealloc(tmem_base, tmem_cols);
 }
 
 }  // namespace
 
-// dual = 1: act_q/act_scale outputs (SwiGLU + requantise); dual = 0: bf16 `out` scaled by route_w.
+// swiglu = 1: w rows per expert = 2 * n_out (gate rows then up rows), out = bf16(silu(g) * u) [rows, n_out];
+// swiglu = 0: w rows per expert = n_out, out = bf16(acc * route_w[row]).
 // w: fp8 [experts * w_rows_per_expert, k] K-major; w_scale [experts][w_rows_per_expert/128][k/128];
 // x: fp8 [rows, k]; x_scale [rows][k/128]; offsets int32 [experts + 1] (device).
-int moe_gemm_fp8_launch(int dual, const void* w, const float* w_scale, int experts, int w_rows_per_expert,
+int moe_gemm_fp8_launch(int swiglu, const void* w, const float* w_scale, int experts, int w_rows_per_expert,
                         int n_out, int k, const void* x, const float* x_scale, const int32_t* offsets,
-                        int total_rows, const float* route_w, void* act_q, float* act_scale, void* out, int* err,
-                        cudaStream_t stream) {
-  PTO_REQUIRE(w && w_scale && x && x_scale && offsets, "moe_gemm: NULL tensor");
+                        int total_rows, const float* route_w, void* out, int* err, cudaStream_t stream) {
+  PTO_REQUIRE(w && w_scale && x && x_scale && offsets && out, "moe_gemm: NULL tensor");
   PTO_REQUIRE(experts > 0 && experts <= 4096, "moe_gemm: 1..4096 experts");
   PTO_REQUIRE(k > 0 && k % 128 == 0 && k <= 64 * 128, "moe_gemm: K must be a multiple of 128, at most 8192");
   PTO_REQUIRE(n_out > 0 && n_out % 128 == 0, "moe_gemm: output features must be a multiple of 128");
-  PTO_REQUIRE(w_rows_per_expert == (dual ? 2 * n_out : n_out), "moe_gemm: weight rows per expert mismatch");
-  PTO_REQUIRE(dual ? (act_q && act_scale) : (out != nullptr), "moe_gemm: missing output");
+  PTO_REQUIRE(w_rows_per_expert == (swiglu ? 2 * n_out : n_out), "moe_gemm: weight rows per expert mismatch");
   if (total_rows <= 0) return kOk;
   MoeGemmParams p;
-  p.offsets = offsets; p.experts = experts; p.n_tiles = n_out / 128; p.kblocks = k / 128; p.dual = dual;
-  p.w_rows_per_expert = w_rows_per_expert; p.up_row_off = dual ? n_out : 0;
-  p.w_scale = w_scale; p.x_scale = x_scale; p.route_w = route_w;
-  p.act_q = static_cast<uint8_t*>(act_q); p.act_scale = act_scale; p.out = static_cast<__nv_bfloat16*>(out);
+  p.offsets = offsets; p.experts = experts; p.kblocks = k / 128; p.n_out = n_out;
+  p.n_tiles = swiglu ? n_out / 64 : n_out / 128;
+  p.w_rows_per_expert = w_rows_per_expert; p.up_row_off = swiglu ? n_out : 0;
+  p.w_scale = w_scale; p.x_scale = x_scale; p.route_w = route_w; p.out = static_cast<__nv_bfloat16*>(out);
   p.total_rows = total_rows; p.err = err;
-  const size_t stage_bytes = static_cast<size_t>(dual ? 3 : 2) * 128 * 128;
-  const size_t fixed = 1024 + sizeof(float) * (static_cast<size_t>(p.kblocks) * kTN + 2 * p.kblocks + 4 * kTN) +
-                       sizeof(int) * (experts + 2) + 8 * (2 * kMoeMaxStages + 4) + 16;
+  const size_t stage_bytes = static_cast<size_t>(2) * 128 * 128;
+  const size_t fixed = 1024 + sizeof(float) * (static_cast<size_t>(p.kblocks) * kTN + 2 * p.kblocks + (swiglu ? 64 * kTN : 0)) +
+                       sizeof(int) * (experts + 2) + 8 * (2 * kMoeMaxStages + 2 * kNumPartial) + 16;
   int stages = static_cast<int>((227 * 1024 - fixed) / stage_bytes);
   if (stages > kMoeMaxStages) stages = kMoeMaxStages;
   PTO_REQUIRE(stages >= 2, "moe_gemm: shared memory does not fit two pipeline stages");
@@ -341,7 +329,7 @@ int moe_gemm_fp8_launch(int dual, const void* w, const float* w_scale, int exper
 
   CUtensorMap tm_w, tm_x;
   int st = make_tensor_map_2d(&tm_w, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
-                              static_cast<uint64_t>(experts) * w_rows_per_expert, k, k, 128, 128,
+                              static_cast<uint64_t>(experts) * w_rows_per_expert, k, k, 128, swiglu ? 64 : 128,
                               CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != kOk) return st;
   st = make_tensor_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, total_rows, k, k, 128, kTN,
@@ -353,7 +341,7 @@ int moe_gemm_fp8_launch(int dual, const void* w, const float* w_scale, int exper
     PTO_CUDA(cudaFuncSetAttribute(moe_gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
-  if (dual) moe_gemm_fp8_kernel<true><<<sm_count(), kMoeThreads, smem, stream>>>(tm_w, tm_x, p);
+  if (swiglu) moe_gemm_fp8_kernel<true><<<sm_count(), kMoeThreads, smem, stream>>>(tm_w, tm_x, p);
   else moe_gemm_fp8_kernel<false><<<sm_count(), kMoeThreads, smem, stream>>>(tm_w, tm_x, p);
   return check_cuda(cudaGetLastError(), "moe_gemm_fp8_kernel launch");
 }

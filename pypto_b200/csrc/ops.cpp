@@ -96,6 +96,55 @@ int op_paged_gather(Worker* w, const pto_task_args* a) {
                              w->stream);
 }
 
+// tensors: x [rows, hidden] (fp32 or bf16), gamma fp32 [hidden] (or [1, hidden]), out (fp32 or bf16)
+// scalars: eps (fp32 bits)
+int op_rms_norm(Worker* w, const pto_task_args* a) {
+  if (a->n_tensors != 3 || a->n_scalars != 1) return fail(kInvalidArgument, "rms_norm: expects 3 tensors and 1 scalar");
+  const pto_chip_tensor* t = a->tensors;
+  if (t[0].ndims < 1 || t[1].dtype != PTO_FP32) return fail(kInvalidArgument, "rms_norm: gamma must be fp32");
+  const int hidden = (int)t[0].shapes[t[0].ndims - 1];
+  if (numel(t[1]) != hidden || numel(t[2]) != numel(t[0]))
+    return fail(kInvalidArgument, "rms_norm: gamma/out sizes do not match x");
+  return rms_norm_launch(tptr(t[0], dtype_bytes(t[0].dtype)), (int)t[0].dtype, static_cast<const float*>(tptr(t[1], 4)),
+                         tptr(t[2], dtype_bytes(t[2].dtype)), (int)t[2].dtype, numel(t[0]) / hidden, hidden,
+                         f32_from_bits(a->scalars[0]), w->stream);
+}
+
+// The reference's ffn_swiglu signature (examples/models/01_ffn.py:112-131): all fp32,
+// weights in the x @ W layout.  tensors: x [m, k], w_gate [k, i], w_up [k, i], w_down [i, n], out [m, n]
+// The operands are cast / packed to bf16 in the worker's scratch arena on every call (a one-shot
+// call has nowhere to keep packed weights; resident use goes through pto_pack_weight + pto_ffn_swiglu).
+int op_ffn_swiglu(Worker* w, const pto_task_args* a) {
+  if (a->n_tensors != 5 || a->n_scalars != 0) return fail(kInvalidArgument, "ffn_swiglu: expects 5 tensors");
+  const pto_chip_tensor* t = a->tensors;
+  for (int i = 0; i < 5; ++i)
+    if (t[i].ndims != 2 || (t[i].dtype != PTO_FP32 && !(i < 4 && t[i].dtype == PTO_BF16)))
+      return fail(kInvalidArgument, "ffn_swiglu: 2-D fp32 (or bf16 input) tensors expected, fp32 output");
+  const int m = t[0].shapes[0], k = t[0].shapes[1], inter = t[1].shapes[1], n = t[3].shapes[1];
+  if ((int)t[1].shapes[0] != k || (int)t[2].shapes[0] != k || (int)t[2].shapes[1] != inter ||
+      (int)t[3].shapes[0] != inter || (int)t[4].shapes[0] != m || (int)t[4].shapes[1] != n)
+    return fail(kInvalidArgument, "ffn_swiglu: operand shapes do not chain");
+  auto al = [](size_t v) { return (v + 255) / 256 * 256; };
+  const size_t x_b = al((size_t)m * k * 2), gu_b = al((size_t)2 * inter * k * 2), d_b = al((size_t)n * inter * 2);
+  const size_t ws_b = ffn_workspace_bytes(m, inter);
+  int st = w->ensure_scratch(4096 + x_b + gu_b + d_b + ws_b);
+  if (st != kOk) return st;
+  uint8_t* base = static_cast<uint8_t*>(w->scratch) + 4096;
+  void* xb = base; void* gu = base + x_b; void* wd = base + x_b + gu_b; void* ws = base + x_b + gu_b + d_b;
+  if (t[0].dtype == PTO_FP32) st = cast_launch(tptr(t[0], 4), PTO_FP32, xb, PTO_BF16, (long long)m * k, w->stream);
+  else st = check_cuda(cudaMemcpyAsync(xb, tptr(t[0], 2), (size_t)m * k * 2, cudaMemcpyDeviceToDevice, w->stream), "copy x");
+  if (st != kOk) return st;
+  st = pack_weight_launch(tptr(t[1], dtype_bytes(t[1].dtype)), (int)t[1].dtype, gu, k, inter, w->stream);
+  if (st != kOk) return st;
+  st = pack_weight_launch(tptr(t[2], dtype_bytes(t[2].dtype)), (int)t[2].dtype,
+                          static_cast<uint8_t*>(gu) + (size_t)inter * k * 2, k, inter, w->stream);
+  if (st != kOk) return st;
+  st = pack_weight_launch(tptr(t[3], dtype_bytes(t[3].dtype)), (int)t[3].dtype, wd, inter, n, w->stream);
+  if (st != kOk) return st;
+  return ffn_swiglu_launch(xb, gu, wd, static_cast<float*>(tptr(t[4], 4)), m, k, inter, n, ws, ws_b, 0,
+                           static_cast<int*>(w->scratch), w->stream);
+}
+
 struct OpEntry {
   const char* name;
   OpFn fn;
@@ -104,6 +153,8 @@ struct OpEntry {
 const OpEntry kOps[] = {
     {"paged_attention", op_paged_attention},
     {"paged_gather", op_paged_gather},
+    {"rms_norm", op_rms_norm},
+    {"ffn_swiglu", op_ffn_swiglu},
 };
 
 }  // namespace
@@ -243,11 +294,11 @@ int pto_moe_gather_f32(const float* src, const int32_t* index, int64_t n, float*
   return pto::moe_gather_f32_launch(src, index, n, dst, static_cast<cudaStream_t>(stream));
 }
 
-int pto_moe_expert_gemm(int dual, const void* w, const float* w_scale, int experts, int w_rows, int n_out, int k,
+int pto_moe_expert_gemm(int swiglu, const void* w, const float* w_scale, int experts, int w_rows, int n_out, int k,
                         const void* x, const float* x_scale, const int32_t* offsets, int rows, const float* route_w,
-                        void* act_q, float* act_scale, void* out, int32_t* err, void* stream) {
-  return pto::moe_gemm_fp8_launch(dual, w, w_scale, experts, w_rows, n_out, k, x, x_scale, offsets, rows, route_w,
-                                  act_q, act_scale, out, err, static_cast<cudaStream_t>(stream));
+                        void* out, int32_t* err, void* stream) {
+  return pto::moe_gemm_fp8_launch(swiglu, w, w_scale, experts, w_rows, n_out, k, x, x_scale, offsets, rows, route_w,
+                                  out, err, static_cast<cudaStream_t>(stream));
 }
 
 int pto_moe_combine(const void* rows, const int32_t* pos, const void* shared, int tokens, int topk, int hidden,

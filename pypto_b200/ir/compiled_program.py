@@ -101,11 +101,13 @@ class CompiledProgram:
         full, returned = self._coerce_args(args)
         host = {p.name: a for p, a in zip(self.params, full)}
         plan = self.fused.plan(self, host, worker)   # host-side reads (config tensor), validation
+        replace = plan.get("replace", {})
         dev, staged = {}, []
         try:
             for p, a in zip(self.params, full):
                 if not p.is_tensor:
                     continue
+                a = replace.get(p.name, a)
                 if isinstance(a, DeviceTensor):
                     if not worker.owns(a):
                         raise ValueError(f"argument '{p.name}': DeviceTensor is not a live allocation owned by this worker")

@@ -81,12 +81,30 @@ class MoELayer:
         self.shared = pack_expert_weights({k: v.unsqueeze(0) for k, v in shared.items()}) if shared else None
         self.hidden = gate_w.shape[0]
 
+    @classmethod
+    def from_packed(cls, gate_packed: torch.Tensor, bias: torch.Tensor, routed: dict, shared: dict | None,
+                    topk: int, n_experts: int | None = None, group=None) -> "MoELayer":
+        """Build from weights already in the kernels' layout (gate packed [E, H] bf16; expert
+        dicts with w_gu / s_gu / w_d / s_d as produced by pack_expert_weights)."""
+        import torch.distributed as dist
+        self = cls.__new__(cls)
+        self.group = group
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.local_experts = routed["w_gu"].shape[0]
+        self.n_experts = n_experts or self.local_experts * self.world
+        assert self.n_experts == self.local_experts * self.world
+        self.topk, self.gate_packed, self.bias = topk, gate_packed, bias.float().contiguous()
+        self.routed, self.shared, self.hidden = routed, shared, gate_packed.shape[1]
+        return self
+
     def route(self, x: torch.Tensor):
         logits = ops.linear(x, self.gate_packed)
         return ops.moe_topk(logits, self.bias, self.topk, is_logits=True)
 
     def _experts(self, weights: dict, xq, xs, offsets, route_w):
-        act_q, act_s = ops.moe_expert_gemm(True, weights["w_gu"], weights["s_gu"], xq, xs, offsets)
+        act = ops.moe_expert_gemm(True, weights["w_gu"], weights["s_gu"], xq, xs, offsets)
+        act_q, act_s = ops.quantize_rows(act)
         return ops.moe_expert_gemm(False, weights["w_d"], weights["s_d"], act_q, act_s, offsets, route_w)
 
     def forward(self, x: torch.Tensor, routing=None):

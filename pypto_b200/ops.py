@@ -369,34 +369,27 @@ def gather_rows(sources: list, index: torch.Tensor | None, div: int = 1, rows: i
     return outs
 
 
-def moe_expert_gemm(dual: bool, w: torch.Tensor, w_scale: torch.Tensor, x: torch.Tensor, x_scale: torch.Tensor,
+def moe_expert_gemm(swiglu: bool, w: torch.Tensor, w_scale: torch.Tensor, x: torch.Tensor, x_scale: torch.Tensor,
                     offsets: torch.Tensor, route_w: torch.Tensor | None = None):
     """Grouped FP8 GEMM over tokens sorted by expert.  w [E, rows, K] e4m3 (K-major), w_scale
     [E, rows/128, K/128]; x [R, K] e4m3, x_scale [R, K/128]; offsets int32 [E+1].
-    dual: returns (act_q [R, rows/2] e4m3, act_scale [R, rows/256]); else bf16 [R, rows]."""
+    swiglu: rows = 2*n_out (gate then up), returns bf16(silu(g)*u) [R, n_out];
+    else returns bf16 [R, rows] scaled by route_w."""
     dev = _need_cuda(w, w_scale, x, x_scale, offsets)
     e, w_rows, k = w.shape
     r = x.shape[0]
-    n_out = w_rows // 2 if dual else w_rows
+    n_out = w_rows // 2 if swiglu else w_rows
     if x.shape[1] != k or x_scale.shape != (r, k // 128) or w_scale.shape != (e, w_rows // 128, k // 128):
         raise ValueError("moe_expert_gemm: operand shapes do not match")
     if offsets.dtype != torch.int32 or offsets.numel() != e + 1:
         raise ValueError("moe_expert_gemm: offsets must be int32 [experts + 1]")
-    lib = _lib.load()
+    out = torch.empty(r, n_out, dtype=torch.bfloat16, device=dev)
     with torch.cuda.device(dev):
-        if dual:
-            act_q = torch.empty(r, n_out, dtype=FP8, device=dev)
-            act_s = torch.empty(r, n_out // 128, dtype=torch.float32, device=dev)
-            _lib.check(lib.pto_moe_expert_gemm(1, w.data_ptr(), w_scale.data_ptr(), e, w_rows, n_out, k, x.data_ptr(),
-                                               x_scale.data_ptr(), offsets.data_ptr(), r, None, act_q.data_ptr(),
-                                               act_s.data_ptr(), None, _err_ptr(dev), _stream_ptr(dev)))
-            return act_q, act_s
-        out = torch.empty(r, n_out, dtype=torch.bfloat16, device=dev)
-        _lib.check(lib.pto_moe_expert_gemm(0, w.data_ptr(), w_scale.data_ptr(), e, w_rows, n_out, k, x.data_ptr(),
-                                           x_scale.data_ptr(), offsets.data_ptr(), r,
-                                           route_w.data_ptr() if route_w is not None else None, None, None,
-                                           out.data_ptr(), _err_ptr(dev), _stream_ptr(dev)))
-        return out
+        _lib.check(_lib.load().pto_moe_expert_gemm(
+            1 if swiglu else 0, w.data_ptr(), w_scale.data_ptr(), e, w_rows, n_out, k, x.data_ptr(),
+            x_scale.data_ptr(), offsets.data_ptr(), r, route_w.data_ptr() if route_w is not None else None,
+            out.data_ptr(), _err_ptr(dev), _stream_ptr(dev)))
+    return out
 
 
 def moe_combine(rows: torch.Tensor, pos: torch.Tensor, shared: torch.Tensor | None, tokens: int, topk: int,

@@ -103,7 +103,82 @@ class PagedGatherOp(FusedOp):
         worker.launch("paged_gather", [dev[n] for n in self.names], plan["scalars"])
 
 
-REGISTRY: list[FusedOp] = [PagedAttentionOp(), PagedGatherOp()]
+class PagedAttentionSpmdOp(FusedOp):
+    """``paged_attention_spmd(query, key_cache, value_cache, block_table, context_lens, scale, out,
+    config)`` (examples/models/09_paged_attention_spmd.py:446-456): the softmax scale is a [1] fp32
+    tensor and config[6] is the number of active KV blocks (the golden stops there, :604-607)."""
+
+    op_names = ("paged_attention",)
+    names = ("query", "key_cache", "value_cache", "block_table", "context_lens", "scale", "out", "config")
+
+    def matches(self, entry) -> bool:
+        return tuple(p.name for p in entry.params) == self.names
+
+    def plan(self, compiled, host, worker):
+        from .device_tensor import DeviceTensor
+        cfg = _host_values(host["config"], worker)
+        batch, heads, kvh, hd, bs, nblk, active = cfg[:7]
+        sc = host["scale"]
+        sc = worker.read_tensor(sc) if isinstance(sc, DeviceTensor) else sc
+        bits = struct.unpack("I", struct.pack("f", float(sc.flatten()[0])))[0]
+        ctx = host["context_lens"]
+        extra = {}
+        if not isinstance(ctx, DeviceTensor) and int(ctx.max()) > active * bs:
+            extra["context_lens"] = torch.clamp(ctx, max=active * bs).contiguous()   # blocks past `active` are not read
+        return dict(scalars=[batch, heads, max(kvh, 1), hd, bs, nblk, 1, bits], host_only=("config", "scale"),
+                    replace=extra)
+
+    def launch(self, worker, dev, host, plan):
+        order = ("query", "key_cache", "value_cache", "block_table", "context_lens", "out")
+        worker.launch("paged_attention", [dev[n] for n in order], plan["scalars"])
+
+
+class FfnSwigluOp(FusedOp):
+    """``ffn_swiglu(hidden_states, gate_proj_weight, up_proj_weight, down_proj_weight, output)``
+    (examples/models/01_ffn.py:112-131), all fp32 in the ``x @ W`` layout."""
+
+    op_names = ("ffn_swiglu",)
+    names = ("hidden_states", "gate_proj_weight", "up_proj_weight", "down_proj_weight", "output")
+
+    def matches(self, entry) -> bool:
+        return entry.name == "ffn_swiglu" and tuple(p.name for p in entry.params) == self.names
+
+    def plan(self, compiled, host, worker):
+        x, wg, wu, wd, out = (host[n] for n in self.names)
+        if wg.shape != wu.shape or x.shape[1] != wg.shape[0] or wd.shape[0] != wg.shape[1] or \
+                tuple(out.shape) != (x.shape[0], wd.shape[1]):
+            raise ValueError("ffn_swiglu: operand shapes do not chain")
+        if out.dtype != torch.float32:
+            raise TypeError("ffn_swiglu: output must be float32")
+        if x.shape[1] % 8 or wg.shape[1] % 32:
+            raise ValueError("ffn_swiglu: hidden size must be a multiple of 8 and the intermediate size of 32")
+        return {}
+
+    def launch(self, worker, dev, host, plan):
+        worker.launch("ffn_swiglu", [dev[n] for n in self.names], [])
+
+
+class RmsNormOp(FusedOp):
+    """``rms_norm(x, gamma, output)`` (examples/intermediate/03_normalization.py:34-65), eps 1e-5
+    (tests/st/examples/02_intermediate/test_rms_norm.py:35)."""
+
+    op_names = ("rms_norm",)
+    names = ("x", "gamma", "output")
+    eps = 1e-5
+
+    def matches(self, entry) -> bool:
+        return entry.name == "rms_norm" and tuple(p.name for p in entry.params) == self.names
+
+    def plan(self, compiled, host, worker):
+        if host["gamma"].dtype != torch.float32:
+            raise TypeError("rms_norm: gamma must be float32")
+        return dict(scalars=[struct.unpack("I", struct.pack("f", self.eps))[0]])
+
+    def launch(self, worker, dev, host, plan):
+        worker.launch("rms_norm", [dev[n] for n in self.names], plan["scalars"])
+
+
+REGISTRY: list[FusedOp] = [PagedAttentionOp(), PagedAttentionSpmdOp(), PagedGatherOp(), FfnSwigluOp(), RmsNormOp()]
 
 
 def lookup(entry) -> FusedOp:

@@ -1,0 +1,74 @@
+"""GPU: reference-style programs for the remaining fused entries -- the SPMD paged-attention
+signature, the @pl.jit ffn_swiglu and rms_norm functions -- run through run() / the JIT call
+and are checked against the oracle."""
+
+import pytest
+import torch
+
+import oracle
+import pypto_b200.language as pl
+from oracle import ffn as offn
+from oracle import layer as olayer
+from oracle import paged_attention as opa
+from pypto_b200.runtime import RunConfig, run, validate_golden
+
+pytestmark = pytest.mark.gpu
+
+
+def test_jit_ffn_swiglu_reference_signature():
+    @pl.jit
+    def ffn_swiglu(hidden_states: pl.Tensor, gate_proj_weight: pl.Tensor, up_proj_weight: pl.Tensor,
+                   down_proj_weight: pl.Tensor, output: pl.Out[pl.Tensor]):
+        ...
+    x, wg, wu, wd = oracle.inputs.ffn_inputs(64, 64, 64, seed=0, w_std=1.0)      # 01_ffn.py:155-160
+    out = torch.zeros(64, 64)
+    ffn_swiglu(x, wg, wu, wd, out, config=RunConfig())
+    exp = offn.ffn_swiglu(x, wg, wu, wd)
+    assert (out - exp).abs().max() <= 2e-2 * exp.abs().max()
+    x, wg, wu, wd = oracle.inputs.ffn_inputs(128, 1024, 4096, seed=0)             # the benchmark shape
+    out = torch.zeros(128, 1024)
+    ffn_swiglu(x, wg, wu, wd, out)
+    exp = offn.ffn_swiglu(x, wg, wu, wd)
+    assert (out - exp).abs().max() <= 2e-2 * exp.abs().max()
+    assert len(ffn_swiglu._cache) == 2
+
+
+def test_jit_rms_norm_reference_signature():
+    @pl.jit
+    def rms_norm(x: pl.Tensor, gamma: pl.Tensor, output: pl.Out[pl.Tensor]):
+        ...
+    torch.manual_seed(0)                                                           # test_rms_norm.py:25-37
+    x, gamma = torch.randn(32, 64), torch.randn(1, 64)
+    out = torch.zeros_like(x)
+    rms_norm(x, gamma, out)
+    validate_golden({"output": out}, {"output": olayer.rms_norm_sqrt_div(x, gamma, 1e-5)}, rtol=1e-5, atol=1e-5)
+
+
+def test_spmd_paged_attention_signature(golden):
+    t = golden("pa09_empty_seq")
+    cfg = t["config"]
+    batch, heads, hd, bs, nblk = int(cfg[0]), int(cfg[1]), int(cfg[3]), int(cfg[4]), int(cfg[5])
+
+    @pl.program
+    class SpmdPagedAttention:
+        @pl.function(type=pl.FunctionType.Orchestration)
+        def paged_attention_spmd(self, query: pl.Tensor[[batch * heads, hd], pl.BF16], key_cache: pl.Tensor[pl.BF16],
+                                 value_cache: pl.Tensor[pl.BF16], block_table: pl.Tensor[[batch * nblk], pl.INT32],
+                                 context_lens: pl.Tensor[[batch], pl.INT32], scale: pl.Tensor[[1], pl.FP32],
+                                 out: pl.Out[pl.Tensor[[batch * heads, hd], pl.FP32]],
+                                 config: pl.Tensor[[7], pl.INT64]):
+            ...
+    out = torch.zeros_like(t["out"])
+    run(SpmdPagedAttention, t["query"], t["key_cache"], t["value_cache"], t["block_table"], t["context_lens"],
+        t["scale"], out, cfg)
+    validate_golden({"out": out}, {"out": t["out"]}, rtol=2e-2, atol=4e-3)
+    # fewer active blocks than the contexts need: blocks past them are not read (09_...:604-607)
+    cfg2 = cfg.clone()
+    cfg2[6] = 1
+    out2 = torch.zeros_like(out)
+    run(SpmdPagedAttention, t["query"], t["key_cache"], t["value_cache"], t["block_table"], t["context_lens"],
+        t["scale"], out2, cfg2)
+    exp = opa.paged_attention(t["query"], t["key_cache"], t["value_cache"], t["block_table"],
+                              torch.clamp(t["context_lens"], max=bs), num_heads=heads, head_dim=hd, block_size=bs,
+                              scale=float(t["scale"][0]))
+    validate_golden({"out": out2}, {"out": exp.reshape(out2.shape)}, rtol=2e-2, atol=4e-3)

@@ -126,7 +126,7 @@ def test_grouped_fp8_gemms_match_oracle(experts, hidden, inter, rows_per):
     xq, xs = omoe.quantize_rows(m["x"])
     off = torch.tensor([0] + list(torch.tensor(rows_per).cumsum(0)), dtype=torch.int32)
     pk = _pack(m["routed"])
-    act_q, act_s = ops.moe_expert_gemm(True, pk["w_gu"], pk["s_gu"], xq.cuda(), xs.cuda(), off.cuda())
+    act_dev = ops.moe_expert_gemm(True, pk["w_gu"], pk["s_gu"], xq.cuda(), xs.cuda(), off.cuda())
     torch.cuda.synchronize()
     ops.check_device_status()
     route_w = torch.rand(sum(rows_per)) + 0.5
@@ -137,11 +137,10 @@ def test_grouped_fp8_gemms_match_oracle(experts, hidden, inter, rows_per):
         ex = omoe.expert_slice(m["routed"], e)
         g = omoe.fp8_gemm(xq[lo:hi], xs[lo:hi], ex["wg"], ex["sg"])
         u = omoe.fp8_gemm(xq[lo:hi], xs[lo:hi], ex["wu"], ex["su"])
-        act = (g * torch.sigmoid(g) * u).bfloat16()
-        got_act = act_q[lo:hi].cpu().float() * act_s[lo:hi].cpu().repeat_interleave(128, 1)
-        scale = act.float().abs().max().item() + 1e-9
-        # the requantised activation is within one e4m3 step (2^-3 relative) of the bf16 value
-        assert (got_act - act.float()).abs().max().item() <= 0.07 * scale
+        act = (g * torch.sigmoid(g) * u).bfloat16().float()
+        got = act_dev[lo:hi].cpu().float()
+        assert (got - act).abs().max().item() <= 1e-2 * act.abs().max().item() + 1e-7
+    act_q, act_s = ops.quantize_rows(act_dev)
     # GEMM2 on the device's own (act_q, act_s): compare with the oracle GEMM on the same operands
     out = ops.moe_expert_gemm(False, pk["w_d"], pk["s_d"], act_q, act_s, off.cuda(), route_w.cuda())
     torch.cuda.synchronize()
