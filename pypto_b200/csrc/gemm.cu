@@ -47,6 +47,7 @@ struct GemmParams {
   int epi;             // GemmEpi
   int out_bf16;
   int stages;
+  int katoms;          // 64-wide K atoms per pipeline stage (2 amortises the per-stage barrier traffic)
   void* out;
   long long ldo;
   int* err;
@@ -89,9 +90,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   const int nacc = p.dual ? 2 : 1;
-  const uint32_t a_bytes = kBM * 128;
+  const uint32_t a_atom = kBM * 128, b_atom = nacc * p.bn * 128;   // one 64-wide K atom of A / of B (gate|up)
+  const uint32_t a_bytes = p.katoms * a_atom;
   const uint32_t b_bytes = p.bn * 128;
-  const uint32_t stage_bytes = a_bytes + nacc * b_bytes;
+  const uint32_t stage_bytes = a_bytes + p.katoms * b_atom;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
   uint64_t* empty = full + kMaxStages;
   uint64_t* tmem_full = empty + kMaxStages;
@@ -145,9 +147,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
           uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
           mbar_arrive_expect_tx(&full[s], stage_bytes);
-          tma_load_2d(st, &tm_a, kb * kBK, at * kBM, &full[s]);
-          tma_load_2d(st + a_bytes, &tm_b, kb * kBK, bt * p.bn, &full[s]);
-          if (p.dual) tma_load_2d(st + a_bytes + b_bytes, &tm_b, kb * kBK, p.dual_off + bt * p.bn, &full[s]);
+          for (int a = 0; a < p.katoms; ++a) {
+            const int kx = (kb * p.katoms + a) * kBK;   // past K the box is zero filled
+            tma_load_2d(st + a * a_atom, &tm_a, kx, at * kBM, &full[s]);
+            tma_load_2d(st + a_bytes + a * b_atom, &tm_b, kx, bt * p.bn, &full[s]);
+            if (p.dual) tma_load_2d(st + a_bytes + a * b_atom + b_bytes, &tm_b, kx, p.dual_off + bt * p.bn, &full[s]);
+          }
         }
       }
     }
@@ -179,11 +184,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
           const uint32_t b_addr = a_addr + a_bytes;
+          for (int a = 0; a < p.katoms; ++a) {
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
-            const uint32_t acc = (kb > kb0 || k > 0) ? 1u : 0u;
-            umma_bf16(d0, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32),
-                      p.dual ? idesc2 : idesc, acc);
+            for (int k = 0; k < kBK / 16; ++k) {
+              const uint32_t acc = (kb > kb0 || a > 0 || k > 0) ? 1u : 0u;
+              umma_bf16(d0, umma_desc_sw128(a_addr + a * a_atom + k * 32),
+                        umma_desc_sw128(b_addr + a * b_atom + k * 32), p.dual ? idesc2 : idesc, acc);
+            }
           }
           umma_commit(&empty[s]);
         }
@@ -296,7 +303,9 @@ int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total,
   p.a_rows = a_rows; p.b_rows = b_rows; p.k = k;
   p.a_tiles = (a_rows + kBM - 1) / kBM;
   p.b_tiles = (b_rows + bn - 1) / bn;
-  p.kblocks_total = (k + kBK - 1) / kBK;
+  const int stage_atom_bytes = kBM * 128 + (dual ? 2 : 1) * bn * 128;
+  p.katoms = (stage_atom_bytes <= 24 * 1024 && k > kBK) ? 2 : 1;   // small stages: two K atoms per barrier round
+  p.kblocks_total = (k + kBK * p.katoms - 1) / (kBK * p.katoms);
   const int tiles = p.a_tiles * p.b_tiles;
   PTO_REQUIRE(static_cast<long long>(tiles) * p.kblocks_total < (1ll << 31), "gemm: problem too large");
   p.iters_total = tiles * p.kblocks_total;
@@ -313,7 +322,7 @@ int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total,
   if (epi == kGemmEpiAtomic) grid = (p.iters_total + p.iters_per_cta - 1) / p.iters_per_cta;
   p.bn = bn; p.dual = dual; p.dual_off = dual_off; p.swap = swap; p.epi = epi; p.out_bf16 = out_bf16;
   p.out = out; p.ldo = ldo; p.err = err;
-  const int stage_bytes = kBM * 128 + (dual ? 2 : 1) * bn * 128;
+  const int stage_bytes = p.katoms * stage_atom_bytes;
   int stages = (200 * 1024) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
