@@ -289,8 +289,8 @@ def run_attention(args, d: Dist, which: str):
         g = paged_inputs_device(d.dev, 100 + d.rank, **w)
         host = None
         scaling, metric = "strong", "paged_attn_verify_GBps"
-        desc = (f"speculative_verify batch256 total ({w['batch']}/GPU) q_len4 causal hq64 hkv8 d128 block128 "
-                "ctx U[8192,32768]")
+        desc = (f"speculative_verify batch{VERIFY['batch']} total ({w['batch']}/GPU) q_len4 causal hq64 hkv8 d128 "
+                "block128 ctx U[8192,32768]")
     out = torch.empty(g["query"].shape, dtype=torch.bfloat16, device=d.dev)
     kw = dict(num_heads=g["num_heads"], kv_heads=g["kv_heads"], head_dim=g["head_dim"], block_size=g["block_size"],
               scale=g["scale"], q_len=g["q_len"])
@@ -589,7 +589,7 @@ def run_moe(args, d: Dist):
         t_rank = ms / 1e3 / args.steps
         emit(args, d, metric="moe_layer_TFLOPs", unit="TFLOP/s", value=flops / sec / 1e12, sec_per_step=sec,
              scaling="strong", dtype="fp8_e4m3",
-             config={"workload": f"deepseek_v3_moe tokens4096 hidden7168 experts256+1 inter2048 top8 fp8 block128; "
+             config={"workload": f"deepseek_v3_moe tokens{T} hidden7168 experts{E}+1 inter2048 top8 fp8 block128; "
                                  f"{L} routed experts and {tl} tokens per GPU",
                      "l2": f"expert weights per GPU {w_bytes / 1e9:.2f} GB, larger than L2",
                      "parallelism": f"ep{d.world}" if d.world > 1 else "single GPU, all experts local"},
@@ -644,6 +644,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "verify", "ffn", "layer", "moe"])
     ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs (profiler captures)")
+    ap.add_argument("--small", action="store_true",
+                    help="reduced case of the workload for profiler captures (a few GB on the device at most): "
+                         "verify batch 16, moe 16 experts / 256 tokens; other workloads unchanged")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = min(args.steps or 5, 5)      # each step is about a second of CPU work
@@ -652,6 +655,9 @@ def main():
         return
     if args.steps is None:
         args.steps = {"decode": 1000, "verify": 50, "ffn": 2000, "layer": 500, "moe": 20}[args.workload]
+    if args.small:
+        VERIFY.update(batch=16)
+        MOE.update(tokens=256, n_experts=16)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
     d = Dist().init()

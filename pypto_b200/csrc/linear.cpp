@@ -32,16 +32,16 @@ int linear_launch(const void* x, const void* w_packed, float* out, int m, int n,
   const int bn = n >= 256 ? 256 : 128;
   const int tiles = ((m + 127) / 128) * ((n + bn - 1) / bn);
   // few tiles: stream-K over (tile, K block) with the atomic epilogue keeps every SM busy
-  const int epi = (accumulate || tiles < 2 * sm_count()) ? kGemmEpiAtomic : kGemmEpiStore;
+  const int epi = (accumulate || tiles < sm_count()) ? kGemmEpiAtomic : kGemmEpiStore;
   if (epi == kGemmEpiAtomic && !accumulate)
     PTO_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * static_cast<size_t>(m) * n, stream));
   return gemm_bf16_launch(x, m, w_packed, n, n, k, out, n, 0, 0, epi, 0, bn, 1, err, stream);
 }
 
 size_t ffn_workspace_bytes(int m, int inter) {
-  // decode: fp32 gate|up [m, 2*inter] + bf16 act [m, inter]; prefill: bf16 act only
+  // bf16 activation [m, inter]; plus fp32 gate|up [m, 2*inter] when the SwiGLU epilogue cannot be used
   const size_t act = (static_cast<size_t>(m) * inter * 2 + 255) / 256 * 256;
-  return m <= 256 ? act + static_cast<size_t>(m) * 2 * inter * 4 : act;
+  return inter % 32 == 0 ? act : act + static_cast<size_t>(m) * 2 * inter * 4;
 }
 
 // out[m, n_out] (+)= (silu(x Wg) * (x Wu)) Wd with bf16 operands, fp32 accumulate, the
@@ -58,22 +58,21 @@ int ffn_swiglu_launch(const void* x, const void* w_gate_up, const void* w_down, 
   PTO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "ffn_swiglu: workspace must be 256-byte aligned");
   __nv_bfloat16* act = static_cast<__nv_bfloat16*>(workspace);
   int st;
-  if (m <= 256) {
+  if (inter % 32 == 0) {
+    // activations on the TMEM lanes (rows past m are zero filled by TMA), gate and up weight
+    // tiles side by side as one MMA N; SiLU(gate) * up in the epilogue, no intermediate in HBM
+    const int a_tiles = (m + 127) / 128;
+    int bn = 128;
+    while (bn > 32 && (inter % bn != 0 || a_tiles * (inter / bn) < sm_count())) bn >>= 1;
+    st = gemm_bf16_launch(x, m, w_gate_up, 2 * inter, inter, k, act, inter, 1, 0, kGemmEpiSwiglu, inter, bn, 1, err,
+                          stream);
+    if (st != kOk) return st;
+  } else {
     float* gate_up = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) +
                                               (static_cast<size_t>(m) * inter * 2 + 255) / 256 * 256);
     st = linear_launch(x, w_gate_up, gate_up, m, 2 * inter, k, 0, err, stream);
     if (st != kOk) return st;
     st = swiglu_act_launch(gate_up, act, m, inter, stream);
-    if (st != kOk) return st;
-  } else {
-    // prefill orientation: gate and up tiles share the activation tile; SiLU*mul in the epilogue
-    PTO_REQUIRE(inter % 32 == 0, "ffn_swiglu: inter must be a multiple of 32");
-    const int a_tiles = (m + 127) / 128;
-    int bn = 128;
-    while (bn > 32 && (inter % bn != 0 || a_tiles * (inter / bn) < sm_count())) bn >>= 1;
-    PTO_REQUIRE(inter % bn == 0, "ffn_swiglu: inter must be a multiple of the column tile");
-    st = gemm_bf16_launch(x, m, w_gate_up, 2 * inter, inter, k, act, inter, 1, 0, kGemmEpiSwiglu, inter, bn, 1, err,
-                          stream);
     if (st != kOk) return st;
   }
   return linear_launch(act, w_down, out, m, n_out, inter, accumulate, err, stream);
