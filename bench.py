@@ -48,7 +48,11 @@ MOE = dict(tokens=4096, hidden=7168, inter=2048, n_experts=256, topk=8)
 
 # dram bytes (read + write) of one launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None where no capture exists yet)
-NCU_TRAFFIC = {"decode": 1406460304, "verify": None, "ffn": None, "layer": None, "moe": None}
+NCU_TRAFFIC = {"decode": 1406460304,   # pa_decode_kernel<1>, profiles/pa_decode_kernel_decode_batch64_ctx1k-8k.md
+               "verify": None,
+               "ffn": None,
+               "layer": 243135232,     # gate/up gemm_bf16_kernel launch (235.4 MB read + 7.7 MB written), profiles/gemm_bf16_*.md
+               "moe": 500529664 * 16}  # gate/up moe_gemm_fp8_kernel: 500.5 MB on the 16-expert capture, x16 for 256 experts
 
 
 def peaks():

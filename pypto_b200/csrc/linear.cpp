@@ -38,10 +38,32 @@ int linear_launch(const void* x, const void* w_packed, float* out, int m, int n,
   return gemm_bf16_launch(x, m, w_packed, n, n, k, out, n, 0, 0, epi, 0, bn, 1, err, stream);
 }
 
+namespace {
+// Column tile for the SwiGLU-epilogue GEMM (whole tiles, no stream-K): the bn in {128, 64, 32}
+// dividing `inter` whose tile count fills the SMs best.  Returns the fill fraction.
+double pick_swiglu_bn(int m, int inter, int* bn_out) {
+  const int sms = sm_count(), a_tiles = (m + 127) / 128;
+  double best = 0.0;
+  *bn_out = 0;
+  for (int bn = 128; bn >= 32; bn >>= 1) {
+    if (inter % bn) continue;
+    const long long tiles = static_cast<long long>(a_tiles) * (inter / bn);
+    const double eff = static_cast<double>(tiles) / static_cast<double>((tiles + sms - 1) / sms * sms);
+    if (eff > best + 0.03) { best = eff; *bn_out = bn; }
+  }
+  return best;
+}
+bool use_swiglu_epilogue(int m, int inter, int* bn) {
+  const double eff = pick_swiglu_bn(m, inter, bn);
+  return *bn != 0 && (m > 256 || eff >= 0.85);   // decode sizes fall back to stream-K when tiles quantise badly
+}
+}  // namespace
+
 size_t ffn_workspace_bytes(int m, int inter) {
-  // bf16 activation [m, inter]; plus fp32 gate|up [m, 2*inter] when the SwiGLU epilogue cannot be used
+  // bf16 activation [m, inter]; plus fp32 gate|up [m, 2*inter] for the stream-K path
   const size_t act = (static_cast<size_t>(m) * inter * 2 + 255) / 256 * 256;
-  return inter % 32 == 0 ? act : act + static_cast<size_t>(m) * 2 * inter * 4;
+  int bn;
+  return use_swiglu_epilogue(m, inter, &bn) ? act : act + static_cast<size_t>(m) * 2 * inter * 4;
 }
 
 // out[m, n_out] (+)= (silu(x Wg) * (x Wu)) Wd with bf16 operands, fp32 accumulate, the
@@ -58,12 +80,10 @@ int ffn_swiglu_launch(const void* x, const void* w_gate_up, const void* w_down, 
   PTO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "ffn_swiglu: workspace must be 256-byte aligned");
   __nv_bfloat16* act = static_cast<__nv_bfloat16*>(workspace);
   int st;
-  if (inter % 32 == 0) {
+  int bn = 0;
+  if (use_swiglu_epilogue(m, inter, &bn)) {
     // activations on the TMEM lanes (rows past m are zero filled by TMA), gate and up weight
     // tiles side by side as one MMA N; SiLU(gate) * up in the epilogue, no intermediate in HBM
-    const int a_tiles = (m + 127) / 128;
-    int bn = 128;
-    while (bn > 32 && (inter % bn != 0 || a_tiles * (inter / bn) < sm_count())) bn >>= 1;
     st = gemm_bf16_launch(x, m, w_gate_up, 2 * inter, inter, k, act, inter, 1, 0, kGemmEpiSwiglu, inter, bn, 1, err,
                           stream);
     if (st != kOk) return st;
