@@ -227,9 +227,9 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       named_bar_sync(1, kPromoWarps * 32);
       const float* ws = ws_s + ((SWIGLU && q >= 2) ? p.kblocks : 0);   // lanes 64-127 hold up rows
 
-      float acc[32];
+      unsigned long long acc2[16];   // 32 fp32 accumulators as packed pairs (FFMA2)
 #pragma unroll
-      for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+      for (int j = 0; j < 16; ++j) acc2[j] = 0ull;
 
       for (int kb = 0; kb < p.kblocks && !dead; ++kb, ++it) {
         const uint32_t pb = it % kNumPartial;
@@ -247,16 +247,19 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         __syncwarp();
         if (lane == 0) mbar_arrive(&pempty[pb]);
         const float sw = ws[kb];
+        const unsigned long long sw2 = pack_f32x2(sw, sw);
         const float* xs = xs_s + kb * kTN + col0;
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
-          const float4 x4 = *reinterpret_cast<const float4*>(xs + j);
-          acc[j] = fmaf(__uint_as_float(v[j]), sw * x4.x, acc[j]);
-          acc[j + 1] = fmaf(__uint_as_float(v[j + 1]), sw * x4.y, acc[j + 1]);
-          acc[j + 2] = fmaf(__uint_as_float(v[j + 2]), sw * x4.z, acc[j + 2]);
-          acc[j + 3] = fmaf(__uint_as_float(v[j + 3]), sw * x4.w, acc[j + 3]);
+          const ulonglong2 x4 = *reinterpret_cast<const ulonglong2*>(xs + j);   // four token scales
+          fma_f32x2(acc2[j / 2], pack_f32x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), mul_f32x2(sw2, x4.x));
+          fma_f32x2(acc2[j / 2 + 1], pack_f32x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])),
+                    mul_f32x2(sw2, x4.y));
         }
       }
+      float acc[32];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) unpack_f32x2(acc2[j], acc[2 * j], acc[2 * j + 1]);
       // a warp that timed out keeps walking the units so that the named barriers stay matched
 
       if constexpr (SWIGLU) {
