@@ -48,6 +48,8 @@ struct GemmParams {
   int out_bf16;
   int stages;
   int katoms;          // 64-wide K atoms per pipeline stage (2 amortises the per-stage barrier traffic)
+  int mt;              // 128-row A tiles per CTA tile (2: a 256-row tile halves the B traffic per FLOP)
+  int nbuf;            // TMEM accumulator buffers (2 = epilogue overlaps the next main loop)
   void* out;
   long long ldo;
   int* err;
@@ -90,7 +92,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   const int nacc = p.dual ? 2 : 1;
-  const uint32_t a_atom = kBM * 128, b_atom = nacc * p.bn * 128;   // one 64-wide K atom of A / of B (gate|up)
+  const uint32_t a_atom = p.mt * kBM * 128, b_atom = nacc * p.bn * 128;   // one 64-wide K atom of A / of B (gate|up)
   const uint32_t a_bytes = p.katoms * a_atom;
   const uint32_t b_bytes = p.bn * 128;
   const uint32_t stage_bytes = a_bytes + p.katoms * b_atom;
@@ -101,9 +103,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t acc_cols = nacc * p.bn;
+  const uint32_t acc_cols = nacc * p.bn;                // columns of one 128-row accumulator
+  const uint32_t buf_cols = p.mt * acc_cols;            // columns of one accumulator buffer
   uint32_t tmem_cols = 32;
-  while (tmem_cols < 2 * acc_cols) tmem_cols <<= 1;
+  while (tmem_cols < p.nbuf * buf_cols) tmem_cols <<= 1;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < p.stages; ++i) {
@@ -149,7 +152,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           mbar_arrive_expect_tx(&full[s], stage_bytes);
           for (int a = 0; a < p.katoms; ++a) {
             const int kx = (kb * p.katoms + a) * kBK;   // past K the box is zero filled
-            tma_load_2d(st + a * a_atom, &tm_a, kx, at * kBM, &full[s]);
+            tma_load_2d(st + a * a_atom, &tm_a, kx, at * p.mt * kBM, &full[s]);
             tma_load_2d(st + a_bytes + a * b_atom, &tm_b, kx, bt * p.bn, &full[s]);
             if (p.dual) tma_load_2d(st + a_bytes + a * b_atom + b_bytes, &tm_b, kx, p.dual_off + bt * p.bn, &full[s]);
           }
@@ -167,13 +170,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       Seg sg;
       for (; ok && next_seg(cur, it_hi, p.kblocks_total, stride, sg); ++ui) {
         const int kb0 = sg.kb0, kb1 = sg.kb1;
-        const uint32_t ab = ui & 1u;
-        if (!mbar_wait(&tmem_empty[ab], ((ui >> 1) & 1u) ^ 1u)) {
+        const uint32_t ab = ui % p.nbuf;
+        if (!mbar_wait(&tmem_empty[ab], ((ui / p.nbuf) & 1u) ^ 1u)) {
           report_error(p.err, kErrBarrierTimeout, 41, static_cast<int>(ui));
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d0 = tmem_base + ab * acc_cols;
+        const uint32_t d0 = tmem_base + ab * buf_cols;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % p.stages, round = it / p.stages;
           if (!mbar_wait(&full[s], round & 1u)) {
@@ -188,8 +191,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
             for (int k = 0; k < kBK / 16; ++k) {
               const uint32_t acc = (kb > kb0 || a > 0 || k > 0) ? 1u : 0u;
-              umma_bf16(d0, umma_desc_sw128(a_addr + a * a_atom + k * 32),
-                        umma_desc_sw128(b_addr + a * b_atom + k * 32), p.dual ? idesc2 : idesc, acc);
+              const uint64_t bd = umma_desc_sw128(b_addr + a * b_atom + k * 32);
+              for (int mi = 0; mi < p.mt; ++mi)
+                umma_bf16(d0 + mi * acc_cols, umma_desc_sw128(a_addr + a * a_atom + mi * (kBM * 128) + k * 32), bd,
+                          p.dual ? idesc2 : idesc, acc);
             }
           }
           umma_commit(&empty[s]);
@@ -206,14 +211,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     Seg sg;
     for (; next_seg(cur, it_hi, p.kblocks_total, stride, sg); ++ui) {
       const int at = sg.tile / p.b_tiles, bt = sg.tile - at * p.b_tiles;
-      const uint32_t ab = ui & 1u;
-      if (!mbar_wait(&tmem_full[ab], (ui >> 1) & 1u)) {
+      const uint32_t ab = ui % p.nbuf;
+      if (!mbar_wait(&tmem_full[ab], (ui / p.nbuf) & 1u)) {
         report_error(p.err, kErrBarrierTimeout, 43, static_cast<int>(ui));
         break;
       }
       tc_fence_after_sync();
-      const int a_row = at * kBM + q * 32 + lane;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * acc_cols;
+      for (int mi = 0; mi < p.mt; ++mi) {
+      const int a_row = (at * p.mt + mi) * kBM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * buf_cols + mi * acc_cols;
       for (int c0 = 0; c0 < p.bn; c0 += 32) {
         uint32_t v[32], w[32];
         tmem_ld_32x32(taddr + c0, v);
@@ -275,6 +281,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
         }
       }
+      }  // mi
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[ab]);
@@ -301,9 +308,15 @@ int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total,
 
   GemmParams p;
   p.a_rows = a_rows; p.b_rows = b_rows; p.k = k;
-  p.a_tiles = (a_rows + kBM - 1) / kBM;
+  // 256-row CTA tiles when the problem is large enough to be L2->SM bound (whole-tile epilogues only):
+  // the B tile is then shared by two A tiles and the accumulators take all 512 TMEM columns
+  const int acc_cols = (dual ? 2 : 1) * bn;
+  const long long tiles128 = static_cast<long long>((a_rows + kBM - 1) / kBM) * ((b_rows + bn - 1) / bn);
+  p.mt = (epi != kGemmEpiAtomic && !swap && acc_cols == 256 && a_rows >= 512 && tiles128 >= 4ll * sm_count()) ? 2 : 1;
+  p.nbuf = (p.mt * acc_cols * 2 <= 512) ? 2 : 1;
+  p.a_tiles = (a_rows + p.mt * kBM - 1) / (p.mt * kBM);
   p.b_tiles = (b_rows + bn - 1) / bn;
-  const int stage_atom_bytes = kBM * 128 + (dual ? 2 : 1) * bn * 128;
+  const int stage_atom_bytes = p.mt * kBM * 128 + (dual ? 2 : 1) * bn * 128;
   p.katoms = (stage_atom_bytes <= 24 * 1024 && k > kBK) ? 2 : 1;   // small stages: two K atoms per barrier round
   p.kblocks_total = (k + kBK * p.katoms - 1) / (kBK * p.katoms);
   const int tiles = p.a_tiles * p.b_tiles;
@@ -331,7 +344,7 @@ int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total,
 
   CUtensorMap tm_a, tm_b;
   int st = make_tensor_map_2d(&tm_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_rows, k, static_cast<uint64_t>(k) * 2,
-                              kBK, kBM, CU_TENSOR_MAP_SWIZZLE_128B);
+                              kBK, p.mt * kBM, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != kOk) return st;
   st = make_tensor_map_2d(&tm_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_rows_total, k,
                           static_cast<uint64_t>(k) * 2, kBK, bn, CU_TENSOR_MAP_SWIZZLE_128B);

@@ -113,6 +113,16 @@ class MoELayer:
         k = self.topk
         idx, w = routing if routing is not None else self.route(x)
         xq, xs = ops.quantize_rows(x)
+        # The shared expert depends on nothing but the quantised tokens: run it on a side stream so
+        # that it fills the GPU while the host waits for the row counts of the exchange.
+        shared_out, side = None, None
+        if self.shared is not None:
+            main = torch.cuda.current_stream()
+            side = self._side_stream(x.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                off = torch.tensor([0, t], dtype=torch.int32, device=x.device)
+                shared_out = self._experts(self.shared, xq, xs, off, None)
         counts, offsets, pos, route_at = ops.moe_dispatch_plan(idx.reshape(-1), self.n_experts)
         xq_s, xs_s = ops.gather_rows([xq, xs], route_at, div=k)
         (w_s,) = ops.gather_rows([w.reshape(-1, 1)], route_at, div=1)
@@ -122,8 +132,8 @@ class MoELayer:
             L = self.local_experts
             send_counts = counts.view(self.world, L)
             recv_counts = exchange_counts(send_counts, self.group)
-            in_split = send_counts.sum(1).tolist()     # rows this rank sends to each destination
-            out_split = recv_counts.sum(1).tolist()    # rows this rank receives from each source
+            splits = torch.stack([send_counts.sum(1), recv_counts.sum(1)]).tolist()   # the one host sync
+            in_split, out_split = splits     # rows sent to each destination / received from each source
             r2 = sum(out_split)
             xq_r = exchange_rows(xq_s, r2, out_split, in_split, self.group)
             xs_r = exchange_rows(xs_s, r2, out_split, in_split, self.group)
@@ -133,10 +143,19 @@ class MoELayer:
             xq_g, xs_g, w_g = ops.gather_rows([xq_r, xs_r, w_r], route_at2, div=1)
             y_g = self._experts(self.routed, xq_g, xs_g, offsets2, w_g)
             (y_r,) = ops.gather_rows([y_g], pos2, div=1)          # back to arrival order
-            y_rows = exchange_rows(y_r, t * k, in_split, out_split, self.group)    # back to the senders' sorted order
-        shared_out = None
-        if self.shared is not None:
-            off = torch.tensor([0, t], dtype=torch.int32, device=x.device)
-            shared_out = self._experts(self.shared, xq, xs, off, None)
+            y_rows = exchange_rows(y_r, t * k, in_split, out_split, self.group)   # back to the senders' sorted order
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
+            for tns in (xq, xs, shared_out):
+                tns.record_stream(side)
         y = ops.moe_combine(y_rows, pos, shared_out, t, k)
         return y, idx, w
+
+    _streams: dict = {}
+
+    def _side_stream(self, dev):
+        key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+        s = MoELayer._streams.get(key)
+        if s is None:
+            s = MoELayer._streams[key] = torch.cuda.Stream(device=dev)
+        return s

@@ -46,6 +46,27 @@ def test_linear_matches_fp32_matmul(m, n, k):
     _check(acc, exp + base, 2e-3, f"linear accumulate {m}x{n}x{k}")
 
 
+def test_large_m_256_row_tiles():
+    """Sizes that take the 256-row CTA tile (two A tiles share the B tile, all 512 TMEM columns
+    in use), with a ragged last tile."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(5)
+    m, n, k = 8000, 4096, 256
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(k, n, generator=g) * 0.05).bfloat16()
+    got = ops.linear(x.cuda(), ops.pack_weight(w.cuda()))
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    _check(got, x.float() @ w.float(), 2e-3, "linear 8000x4096x256")
+    from pypto_b200.layers import SwiGLUFFN
+    xf, wg, wu, wd = oracle.inputs.ffn_inputs(5000, 256, 2048, seed=6)
+    xb, wgb, wub, wdb = xf.bfloat16(), wg.bfloat16(), wu.bfloat16(), wd.bfloat16()
+    got = SwiGLUFFN(wgb.cuda(), wub.cuda(), wdb.cuda())(xb.cuda())
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    _check(got, offn.ffn_swiglu_bf16(xb, wgb, wub, wdb), 5e-3, "ffn 5000x256x2048")
+
+
 def test_pack_weight_from_fp32_rounds_to_bf16():
     w = torch.randn(96, 40)
     wp = _ops().pack_weight(w.cuda())
