@@ -425,7 +425,27 @@ def run_ffn(args, d: Dist):
                 torch.cuda.synchronize()
                 t = e0.elapsed_time(e1) / 20 / 1e3
                 tf = offn.ffn_flops(ms_, k, inter) / t / 1e12
-                sweep.append({"M": ms_, "us": t * 1e6, "tflops": tf, "frac_bf16_peak": tf / pk["bf16"]})
+                sweep.append({"M": ms_, "K": k, "I": inter, "us": t * 1e6, "tflops": tf, "frac_bf16_peak": tf / pk["bf16"]})
+            # the decoder layer's FFN shape (hidden 4096, intermediate 14336) at prefill size
+            gk, gi, gm = LAYER["hidden"], LAYER["inter"], 8192
+            gen = torch.Generator(device=d.dev).manual_seed(1)
+            big = SwiGLUFFN(*[(torch.randn(a, b, device=d.dev, generator=gen) * 0.02).bfloat16()
+                              for a, b in ((gk, gi), (gk, gi), (gi, gk))])
+            xs = torch.randn(gm, gk, device=d.dev, generator=gen).bfloat16()
+            o = torch.empty(gm, gk, dtype=torch.float32, device=d.dev)
+            for _ in range(3):
+                big(xs, out=o)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(10):
+                big(xs, out=o)
+            e1.record()
+            torch.cuda.synchronize()
+            t = e0.elapsed_time(e1) / 10 / 1e3
+            tf = offn.ffn_flops(gm, gk, gi) / t / 1e12
+            sweep.append({"M": gm, "K": gk, "I": gi, "us": t * 1e6, "tflops": tf, "frac_bf16_peak": tf / pk["bf16"]})
+            del big, xs, o
         xh, yh = x.pin_memory(), torch.empty(m, k).pin_memory()
 
         def call():

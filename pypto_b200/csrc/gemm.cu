@@ -312,7 +312,9 @@ int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total,
   // the B tile is then shared by two A tiles and the accumulators take all 512 TMEM columns
   const int acc_cols = (dual ? 2 : 1) * bn;
   const long long tiles128 = static_cast<long long>((a_rows + kBM - 1) / kBM) * ((b_rows + bn - 1) / bn);
-  p.mt = (epi != kGemmEpiAtomic && !swap && acc_cols == 256 && a_rows >= 512 && tiles128 >= 4ll * sm_count()) ? 2 : 1;
+  // (with a short K the single-buffered accumulators cost more than the halved B traffic gains)
+  p.mt = (epi != kGemmEpiAtomic && !swap && acc_cols == 256 && a_rows >= 512 && k >= 2048 &&
+          tiles128 >= 4ll * sm_count()) ? 2 : 1;
   p.nbuf = (p.mt * acc_cols * 2 <= 512) ? 2 : 1;
   p.a_tiles = (a_rows + p.mt * kBM - 1) / (p.mt * kBM);
   p.b_tiles = (b_rows + bn - 1) / bn;

@@ -51,20 +51,20 @@ def test_large_m_256_row_tiles():
     in use), with a ragged last tile."""
     ops = _ops()
     g = torch.Generator().manual_seed(5)
-    m, n, k = 8000, 4096, 256
+    m, n, k = 8000, 4096, 2048
     x = torch.randn(m, k, generator=g).bfloat16()
     w = (torch.randn(k, n, generator=g) * 0.05).bfloat16()
     got = ops.linear(x.cuda(), ops.pack_weight(w.cuda()))
     torch.cuda.synchronize()
     ops.check_device_status()
-    _check(got, x.float() @ w.float(), 2e-3, "linear 8000x4096x256")
+    _check(got, x.float() @ w.float(), 2e-3, "linear 8000x4096x2048")
     from pypto_b200.layers import SwiGLUFFN
-    xf, wg, wu, wd = oracle.inputs.ffn_inputs(5000, 256, 2048, seed=6)
+    xf, wg, wu, wd = oracle.inputs.ffn_inputs(5000, 2048, 2048, seed=6)
     xb, wgb, wub, wdb = xf.bfloat16(), wg.bfloat16(), wu.bfloat16(), wd.bfloat16()
     got = SwiGLUFFN(wgb.cuda(), wub.cuda(), wdb.cuda())(xb.cuda())
     torch.cuda.synchronize()
     ops.check_device_status()
-    _check(got, offn.ffn_swiglu_bf16(xb, wgb, wub, wdb), 5e-3, "ffn 5000x256x2048")
+    _check(got, offn.ffn_swiglu_bf16(xb, wgb, wub, wdb), 5e-3, "ffn 5000x2048x2048")
 
 
 def test_pack_weight_from_fp32_rounds_to_bf16():
