@@ -56,10 +56,38 @@ constexpr int kErrWords = 16;
 constexpr int kErrBarrierTimeout = 1;
 constexpr int kErrBadBlockId = 2;
 
+// Programmatic dependent launch: every kernel of this library is launched with the
+// programmatic-stream-serialization attribute (unless PTO_PDL=0) so that its prologue (barrier
+// init, TMEM allocation, descriptor prefetch) overlaps the tail of the kernel before it on the
+// stream.  Each kernel calls pdl_launch_dependents() first and pdl_wait() before it touches
+// global memory.
+bool pdl_enabled();
+
 #ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---------------------------------------------------------------------------
 // Device helpers
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

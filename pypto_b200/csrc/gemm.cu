@@ -88,6 +88,7 @@ __device__ __forceinline__ bool next_seg(int& it, int hi, int kblocks, int strid
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const GemmParams p) {
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -126,6 +127,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // the prologue above overlaps the previous kernel; operands and outputs are touched below
   const bool stream_k = p.epi == kGemmEpiAtomic;
   const int stride = stream_k ? 0 : static_cast<int>(gridDim.x);
   const int it_lo = stream_k ? min(p.iters_total, static_cast<int>(blockIdx.x) * p.iters_per_cta)
@@ -356,7 +358,7 @@ int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total,
     PTO_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
-  gemm_bf16_kernel<<<grid, kGemmThreads, smem, stream>>>(tm_a, tm_b, p);
+  launch_kernel(gemm_bf16_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, tm_a, tm_b, p);
   return check_cuda(cudaGetLastError(), "gemm_bf16_kernel launch");
 }
 

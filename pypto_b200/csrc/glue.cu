@@ -47,6 +47,8 @@ template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 rms_norm_kernel(const TI* __restrict__ x, const float* __restrict__ gamma, TO* __restrict__ out, int hidden,
                 float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[8];
   const TI* xr = x + static_cast<size_t>(blockIdx.x) * hidden;
   TO* orow = out + static_cast<size_t>(blockIdx.x) * hidden;
@@ -71,6 +73,8 @@ __global__ void rope_kv_append_kernel(const float* __restrict__ qkv, const int* 
                                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                       __nv_bfloat16* __restrict__ q_out, int num_heads, int kv_heads, int head_dim,
                                       int block_size, int pool_blocks, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y, i = threadIdx.x, half = head_dim / 2;
   const int len = seq_lens[b];
   int pos = len - 1;
@@ -110,6 +114,8 @@ __global__ void rope_kv_append_kernel(const float* __restrict__ qkv, const int* 
 // gate_up fp32 [rows, 2 * inter] (gate columns first) -> act bf16 [rows, inter]
 __global__ void swiglu_act_kernel(const float* __restrict__ gate_up, __nv_bfloat16* __restrict__ act, long long rows,
                                   int inter) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long n = rows * inter;
   for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < n;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -122,6 +128,8 @@ __global__ void swiglu_act_kernel(const float* __restrict__ gate_up, __nv_bfloat
 
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, long long n) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x)
     out[i] = from_f32<TO>(to_f32(in[i]));
@@ -131,6 +139,8 @@ __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, lon
 template <typename TI>
 __global__ void __launch_bounds__(256) pack_weight_kernel(const TI* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                                                           int k, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float tile[32][33];
   const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -159,13 +169,13 @@ int rms_norm_launch(const void* x, int x_dtype, const float* gamma, void* out, i
   if (rows == 0) return kOk;
   const unsigned g = static_cast<unsigned>(rows);
   if (x_dtype == PTO_BF16 && out_dtype == PTO_BF16)
-    rms_norm_kernel<__nv_bfloat16, __nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), gamma, static_cast<__nv_bfloat16*>(out), hidden, eps);
+    launch_kernel(rms_norm_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(g), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), gamma, static_cast<__nv_bfloat16*>(out), hidden, eps);
   else if (x_dtype == PTO_FP32 && out_dtype == PTO_BF16)
-    rms_norm_kernel<float, __nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const float*>(x), gamma, static_cast<__nv_bfloat16*>(out), hidden, eps);
+    launch_kernel(rms_norm_kernel<float, __nv_bfloat16>, dim3(g), dim3(256), 0, stream, static_cast<const float*>(x), gamma, static_cast<__nv_bfloat16*>(out), hidden, eps);
   else if (x_dtype == PTO_FP32 && out_dtype == PTO_FP32)
-    rms_norm_kernel<float, float><<<g, 256, 0, stream>>>(static_cast<const float*>(x), gamma, static_cast<float*>(out), hidden, eps);
+    launch_kernel(rms_norm_kernel<float, float>, dim3(g), dim3(256), 0, stream, static_cast<const float*>(x), gamma, static_cast<float*>(out), hidden, eps);
   else if (x_dtype == PTO_BF16 && out_dtype == PTO_FP32)
-    rms_norm_kernel<__nv_bfloat16, float><<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), gamma, static_cast<float*>(out), hidden, eps);
+    launch_kernel(rms_norm_kernel<__nv_bfloat16, float>, dim3(g), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), gamma, static_cast<float*>(out), hidden, eps);
   else
     return fail(kInvalidArgument, "rms_norm: dtypes must be fp32 or bf16");
   return check_cuda(cudaGetLastError(), "rms_norm_kernel launch");
@@ -179,7 +189,7 @@ int rope_kv_append_launch(const float* qkv, const int32_t* seq_lens, const float
   PTO_REQUIRE(head_dim % 2 == 0 && head_dim <= 2048 && num_heads > 0 && kv_heads > 0, "rope: bad head geometry");
   if (batch == 0) return kOk;
   dim3 grid(batch, num_heads + kv_heads);
-  rope_kv_append_kernel<<<grid, head_dim / 2, 0, stream>>>(
+  launch_kernel(rope_kv_append_kernel, dim3(grid), dim3(head_dim / 2), 0, stream, 
       qkv, seq_lens, cos_t, sin_t, table_rows, block_table, max_blocks, static_cast<__nv_bfloat16*>(k_cache),
       static_cast<__nv_bfloat16*>(v_cache), static_cast<__nv_bfloat16*>(q_out), num_heads, kv_heads, head_dim,
       block_size, static_cast<int>(pool_blocks), err);
@@ -189,7 +199,7 @@ int rope_kv_append_launch(const float* qkv, const int32_t* seq_lens, const float
 int swiglu_act_launch(const float* gate_up, void* act, long long rows, int inter, cudaStream_t stream) {
   PTO_REQUIRE(gate_up && act && rows >= 0 && inter > 0, "swiglu_act: bad arguments");
   if (rows == 0) return kOk;
-  swiglu_act_kernel<<<grid_for(rows * inter, 256), 256, 0, stream>>>(gate_up, static_cast<__nv_bfloat16*>(act), rows, inter);
+  launch_kernel(swiglu_act_kernel, dim3(grid_for(rows * inter, 256)), dim3(256), 0, stream, gate_up, static_cast<__nv_bfloat16*>(act), rows, inter);
   return check_cuda(cudaGetLastError(), "swiglu_act_kernel launch");
 }
 
@@ -198,9 +208,9 @@ int cast_launch(const void* in, int in_dtype, void* out, int out_dtype, long lon
   if (n == 0) return kOk;
   const int g = grid_for(n, 256);
   if (in_dtype == PTO_FP32 && out_dtype == PTO_BF16)
-    cast_kernel<float, __nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const float*>(in), static_cast<__nv_bfloat16*>(out), n);
+    launch_kernel(cast_kernel<float, __nv_bfloat16>, dim3(g), dim3(256), 0, stream, static_cast<const float*>(in), static_cast<__nv_bfloat16*>(out), n);
   else if (in_dtype == PTO_BF16 && out_dtype == PTO_FP32)
-    cast_kernel<__nv_bfloat16, float><<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(in), static_cast<float*>(out), n);
+    launch_kernel(cast_kernel<__nv_bfloat16, float>, dim3(g), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), static_cast<float*>(out), n);
   else
     return fail(kInvalidArgument, "cast: only fp32 <-> bf16");
   return check_cuda(cudaGetLastError(), "cast_kernel launch");
@@ -210,9 +220,9 @@ int pack_weight_launch(const void* src, int src_dtype, void* dst, int k, int n, 
   PTO_REQUIRE(src && dst && k > 0 && n > 0, "pack_weight: bad arguments");
   dim3 grid((n + 31) / 32, (k + 31) / 32);
   if (src_dtype == PTO_FP32)
-    pack_weight_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(src), static_cast<__nv_bfloat16*>(dst), k, n);
+    launch_kernel(pack_weight_kernel<float>, dim3(grid), dim3(256), 0, stream, static_cast<const float*>(src), static_cast<__nv_bfloat16*>(dst), k, n);
   else if (src_dtype == PTO_BF16)
-    pack_weight_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), k, n);
+    launch_kernel(pack_weight_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), k, n);
   else
     return fail(kInvalidArgument, "pack_weight: source must be fp32 or bf16");
   return check_cuda(cudaGetLastError(), "pack_weight_kernel launch");

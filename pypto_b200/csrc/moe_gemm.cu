@@ -61,6 +61,7 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(kMoeThreads, 1)
 moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                     const MoeGemmParams p) {
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -94,6 +95,7 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     tma_prefetch_desc(&tm_x);
   }
   if (warp == 2) tmem_alloc(tmem_slot, tmem_cols);
+  pdl_wait();   // barrier set-up and TMEM allocation overlap the previous kernel; offsets are read next
   // chunk prefix over experts: prefix[e] = number of token chunks of experts before e
   for (int e = threadIdx.x; e < p.experts; e += kMoeThreads) {
     const int n = p.offsets[e + 1] - p.offsets[e];
@@ -344,8 +346,8 @@ int moe_gemm_fp8_launch(int swiglu, const void* w, const float* w_scale, int exp
     PTO_CUDA(cudaFuncSetAttribute(moe_gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
-  if (swiglu) moe_gemm_fp8_kernel<true><<<sm_count(), kMoeThreads, smem, stream>>>(tm_w, tm_x, p);
-  else moe_gemm_fp8_kernel<false><<<sm_count(), kMoeThreads, smem, stream>>>(tm_w, tm_x, p);
+  if (swiglu) launch_kernel(moe_gemm_fp8_kernel<true>, dim3(sm_count()), dim3(kMoeThreads), smem, stream, tm_w, tm_x, p);
+  else launch_kernel(moe_gemm_fp8_kernel<false>, dim3(sm_count()), dim3(kMoeThreads), smem, stream, tm_w, tm_x, p);
   return check_cuda(cudaGetLastError(), "moe_gemm_fp8_kernel launch");
 }
 

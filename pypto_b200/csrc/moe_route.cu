@@ -22,6 +22,8 @@ constexpr int kMaxExpertsPerLane = 32;  // up to 1024 experts per token row
 __global__ void __launch_bounds__(256)
 moe_topk_kernel(const float* __restrict__ scores_in, const float* __restrict__ bias, int is_logits, int tokens,
                 int experts, int topk, int32_t* __restrict__ idx_out, float* __restrict__ w_out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= tokens) return;
@@ -80,6 +82,8 @@ template <typename TI>
 __global__ void __launch_bounds__(256)
 quantize_rows_kernel(const TI* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale, long long rows,
                      int cols) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int groups = cols / 128;
   const long long total = rows * groups;
@@ -112,6 +116,8 @@ quantize_rows_kernel(const TI* __restrict__ x, uint8_t* __restrict__ q, float* _
 __global__ void __launch_bounds__(256)
 moe_count_rank_kernel(const int32_t* __restrict__ expert_of, int routes, int32_t* __restrict__ counts,
                       int32_t* __restrict__ rank) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ int warp_tot[8];
   __shared__ int running_s;
   const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -140,6 +146,8 @@ moe_count_rank_kernel(const int32_t* __restrict__ expert_of, int routes, int32_t
 // Single CTA: offsets[0..n] = exclusive scan of counts[0..n).
 __global__ void __launch_bounds__(1024) moe_offsets_kernel(const int32_t* __restrict__ counts, int n,
                                                            int32_t* __restrict__ offsets) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ int warp_sum_s[32];
   __shared__ int carry_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -170,6 +178,8 @@ __global__ void __launch_bounds__(1024) moe_offsets_kernel(const int32_t* __rest
 __global__ void moe_positions_kernel(const int32_t* __restrict__ expert_of, const int32_t* __restrict__ rank,
                                      const int32_t* __restrict__ offsets, int routes, int32_t* __restrict__ pos,
                                      int32_t* __restrict__ route_at) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= routes) return;
   const int p = offsets[expert_of[r]] + rank[r];
@@ -188,6 +198,8 @@ struct RowArrays {
 
 __global__ void __launch_bounds__(256)
 moe_gather_rows_kernel(RowArrays a, const int32_t* __restrict__ src_row_of, int div, long long rows) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   for (long long p = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); p < rows;
        p += static_cast<long long>(gridDim.x) * (blockDim.x >> 5)) {
@@ -208,6 +220,8 @@ moe_gather_rows_kernel(RowArrays a, const int32_t* __restrict__ src_row_of, int 
 // route_weight_sorted[p] = weights[route_at[p]]
 __global__ void moe_gather_f32_kernel(const float* __restrict__ src, const int32_t* __restrict__ index, long long n,
                                       float* __restrict__ dst) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < n) dst[i] = src[index[i]];
 }
@@ -217,6 +231,8 @@ __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __nv_bfloat16* __restrict__ rows, const int32_t* __restrict__ pos,
                    const __nv_bfloat16* __restrict__ shared, int topk, int hidden, __nv_bfloat16* __restrict__ y,
                    float* __restrict__ y32) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -267,7 +283,7 @@ int moe_topk_launch(const float* scores, const float* bias, int is_logits, int t
   PTO_REQUIRE(experts > 0 && experts <= 32 * kMaxExpertsPerLane, "moe_topk: at most 1024 experts");
   PTO_REQUIRE(topk > 0 && topk <= 32 && topk <= experts, "moe_topk: 1 <= topk <= min(32, experts)");
   if (tokens <= 0) return kOk;
-  moe_topk_kernel<<<(tokens + 7) / 8, 256, 0, stream>>>(scores, bias, is_logits, tokens, experts, topk, idx, weights);
+  launch_kernel(moe_topk_kernel, dim3((tokens + 7) / 8), dim3(256), 0, stream, scores, bias, is_logits, tokens, experts, topk, idx, weights);
   return check_cuda(cudaGetLastError(), "moe_topk_kernel launch");
 }
 
@@ -278,9 +294,9 @@ int quantize_rows_launch(const void* x, int x_dtype, void* q, float* scale, long
   if (rows <= 0) return kOk;
   const int g = grid_rows(rows * (cols / 128), 8);
   if (x_dtype == PTO_BF16)
-    quantize_rows_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scale, rows, cols);
+    launch_kernel(quantize_rows_kernel<__nv_bfloat16>, dim3(g), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scale, rows, cols);
   else if (x_dtype == PTO_FP32)
-    quantize_rows_kernel<float><<<g, 256, 0, stream>>>(static_cast<const float*>(x), static_cast<uint8_t*>(q), scale, rows, cols);
+    launch_kernel(quantize_rows_kernel<float>, dim3(g), dim3(256), 0, stream, static_cast<const float*>(x), static_cast<uint8_t*>(q), scale, rows, cols);
   else
     return fail(kInvalidArgument, "quantize_rows: input must be bf16 or fp32");
   return check_cuda(cudaGetLastError(), "quantize_rows_kernel launch");
@@ -292,12 +308,12 @@ int moe_dispatch_plan_launch(const int32_t* expert_of, int routes, int buckets, 
                              int32_t* pos, int32_t* route_at, int32_t* rank_tmp, cudaStream_t stream) {
   PTO_REQUIRE(expert_of && counts && offsets && pos && route_at && rank_tmp, "moe_dispatch_plan: NULL tensor");
   PTO_REQUIRE(buckets > 0 && routes >= 0, "moe_dispatch_plan: bad sizes");
-  moe_count_rank_kernel<<<buckets, 256, 0, stream>>>(expert_of, routes, counts, rank_tmp);
+  launch_kernel(moe_count_rank_kernel, dim3(buckets), dim3(256), 0, stream, expert_of, routes, counts, rank_tmp);
   PTO_CUDA(cudaGetLastError());
-  moe_offsets_kernel<<<1, 1024, 0, stream>>>(counts, buckets, offsets);
+  launch_kernel(moe_offsets_kernel, dim3(1), dim3(1024), 0, stream, counts, buckets, offsets);
   PTO_CUDA(cudaGetLastError());
   if (routes > 0) {
-    moe_positions_kernel<<<(routes + 255) / 256, 256, 0, stream>>>(expert_of, rank_tmp, offsets, routes, pos, route_at);
+    launch_kernel(moe_positions_kernel, dim3((routes + 255) / 256), dim3(256), 0, stream, expert_of, rank_tmp, offsets, routes, pos, route_at);
     PTO_CUDA(cudaGetLastError());
   }
   return kOk;
@@ -315,14 +331,14 @@ int moe_gather_rows_launch(const void* const* src, void* const* dst, const int* 
     a.dst[i] = static_cast<uint8_t*>(dst[i]);
     a.row_bytes[i] = row_bytes[i];
   }
-  moe_gather_rows_kernel<<<grid_rows(rows, 8), 256, 0, stream>>>(a, src_row_of, div, rows);
+  launch_kernel(moe_gather_rows_kernel, dim3(grid_rows(rows, 8)), dim3(256), 0, stream, a, src_row_of, div, rows);
   return check_cuda(cudaGetLastError(), "moe_gather_rows_kernel launch");
 }
 
 int moe_gather_f32_launch(const float* src, const int32_t* index, long long n, float* dst, cudaStream_t stream) {
   PTO_REQUIRE(src && index && dst, "moe_gather_f32: NULL tensor");
   if (n <= 0) return kOk;
-  moe_gather_f32_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(src, index, n, dst);
+  launch_kernel(moe_gather_f32_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, stream, src, index, n, dst);
   return check_cuda(cudaGetLastError(), "moe_gather_f32_kernel launch");
 }
 
@@ -331,7 +347,7 @@ int moe_combine_launch(const void* rows, const int32_t* pos, const void* shared,
   PTO_REQUIRE(rows && pos && (y_bf16 || y_f32), "moe_combine: NULL tensor");
   PTO_REQUIRE(hidden > 0 && hidden % 8 == 0 && topk > 0, "moe_combine: hidden must be a multiple of 8");
   if (tokens <= 0) return kOk;
-  moe_combine_kernel<<<tokens, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(rows), pos,
+  launch_kernel(moe_combine_kernel, dim3(tokens), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(rows), pos,
                                                  static_cast<const __nv_bfloat16*>(shared), topk, hidden,
                                                  static_cast<__nv_bfloat16*>(y_bf16), y_f32);
   return check_cuda(cudaGetLastError(), "moe_combine_kernel launch");

@@ -128,6 +128,7 @@ template <int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                  const PAParams p) {
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -158,6 +159,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     for (int i = tid; i < kNBuf * kBuf / 16; i += kThreads) b4[i] = z;
     fence_proxy_async_smem();
   }
+  pdl_wait();   // everything above is CTA-local; from here on global memory is read and written
   for (int b = tid; b < p.batch; b += kThreads) prefix[b + 1] = tiles_of(p.context_lens[b], p);
   if (tid == 0) prefix[0] = 0;
   __syncthreads();
@@ -476,6 +478,8 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 
 // One warp per (item, row): combine the partials of all covering CTAs and warps.
 __global__ void __launch_bounds__(128) pa_merge_kernel(const PAParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int item = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.y * 4 + warp;
@@ -550,6 +554,8 @@ pa_generic_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                   const int* __restrict__ context_lens, void* out, int out_fp32, int num_heads,
                   int kv_heads, int q_len, int head_dim, int block_size, int max_blocks,
                   int pool_blocks, float scale, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float q_f[kGenMaxD];
   __shared__ float s_f[kGenMaxBlock];
   __shared__ float red[kGenThreads / 32];
@@ -678,7 +684,7 @@ int pa_launch(const void* q, const void* kc, const void* vc, const int32_t* bloc
   if (!pa_fast_path_ok(head_dim, block_size)) {
     PTO_REQUIRE(head_dim <= kGenMaxD && block_size <= kGenMaxBlock,
                 "paged_attention: head_dim <= 256 and block_size <= 1024 required");
-    pa_generic_kernel<<<batch * q_len * num_heads, kGenThreads, 0, stream>>>(
+    launch_kernel(pa_generic_kernel, dim3(batch * q_len * num_heads), dim3(kGenThreads), 0, stream, 
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kc),
         static_cast<const __nv_bfloat16*>(vc), block_table, context_lens, out, out_fp32, num_heads,
         kv_heads, q_len, head_dim, block_size, max_blocks, static_cast<int>(pool_blocks), scale, err);
@@ -732,14 +738,14 @@ int pa_launch(const void* q, const void* kc, const void* vc, const int32_t* bloc
   const size_t smem = smem_bytes(mt);
   if (mt == 1) {
     PTO_CUDA(cudaFuncSetAttribute(pa_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    pa_decode_kernel<1><<<grid, kThreads, smem, stream>>>(tm_k, tm_v, p);
+    launch_kernel(pa_decode_kernel<1>, dim3(grid), dim3(kThreads), smem, stream, tm_k, tm_v, p);
   } else {
     PTO_CUDA(cudaFuncSetAttribute(pa_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    pa_decode_kernel<2><<<grid, kThreads, smem, stream>>>(tm_k, tm_v, p);
+    launch_kernel(pa_decode_kernel<2>, dim3(grid), dim3(kThreads), smem, stream, tm_k, tm_v, p);
   }
   PTO_CUDA(cudaGetLastError());
   dim3 mgrid(batch * lay.subs, (lay.rows_per_item + 3) / 4);
-  pa_merge_kernel<<<mgrid, 128, 0, stream>>>(p);
+  launch_kernel(pa_merge_kernel, dim3(mgrid), dim3(128), 0, stream, p);
   return check_cuda(cudaGetLastError(), "pa_merge_kernel launch");
 }
 

@@ -15,6 +15,8 @@ paged_gather_kernel(const uint8_t* __restrict__ src, int64_t src_rows, int64_t r
                     const int32_t* __restrict__ indices, int64_t n_indices,
                     const int32_t* __restrict__ block_table, int64_t table_len, int block_size,
                     int64_t off_bytes, int64_t copy_bytes, uint8_t* __restrict__ out, int32_t* err) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -55,7 +57,7 @@ int paged_gather_launch(const void* src, int64_t src_rows, int64_t src_cols, int
   int64_t ctas = (n_indices + warps_per_cta - 1) / warps_per_cta;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   if (ctas > cap) ctas = cap;
-  paged_gather_kernel<<<static_cast<unsigned>(ctas), warps_per_cta * 32, 0, stream>>>(
+  launch_kernel(paged_gather_kernel, dim3(static_cast<unsigned>(ctas)), dim3(warps_per_cta * 32), 0, stream, 
       static_cast<const uint8_t*>(src), src_rows, src_cols * elem_bytes, indices, n_indices,
       block_table, table_len, block_size, col_off * elem_bytes, size * elem_bytes,
       static_cast<uint8_t*>(out), err);

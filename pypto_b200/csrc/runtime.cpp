@@ -5,6 +5,7 @@
 #include "runtime.h"
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -28,6 +29,14 @@ int check_cuda(cudaError_t e, const char* what) {
   if (e == cudaSuccess) return kOk;
   g_last_error = std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
   return e == cudaErrorMemoryAllocation ? kOutOfMemory : kCudaError;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("PTO_PDL");
+    return v == nullptr || v[0] != '0';
+  }();
+  return on;
 }
 
 int sm_count() {

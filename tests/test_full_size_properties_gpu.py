@@ -1,0 +1,70 @@
+"""GPU: the benchmark workloads at their full sizes, checked through size-independent properties
+(the CPU oracle cannot run these sizes in seconds) plus an oracle comparison on a sample."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_verify_attention_full_size_sample_and_value_linearity():
+    """Speculative-verify attention at batch 256, q_len 4, 64/8 heads, ctx U[8192, 32768] (about
+    24 GB of KV): (a) the first two sequences agree with the oracle; (b) doubling V doubles the
+    output exactly (scaling by 2 is exact in bf16 and in every fp32 partial sum)."""
+    import bench
+    from pypto_b200 import ops
+    if torch.cuda.mem_get_info()[0] < 60 << 30:
+        pytest.skip("needs about 50 GB of free device memory")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = bench.paged_inputs_device(dev, 7, **bench.VERIFY)
+    kw = dict(num_heads=g["num_heads"], kv_heads=g["kv_heads"], head_dim=g["head_dim"], block_size=g["block_size"],
+              scale=g["scale"], q_len=g["q_len"])
+    out = ops.paged_attention(g["query"], g["key_cache"], g["value_cache"], g["block_table"], g["context_lens"], **kw)
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    assert torch.isfinite(out.float()).all()
+    sub = bench.host_subproblem(g, 2)
+    from oracle import paged_attention as opa
+    exp = opa.paged_attention(sub["query"], sub["key_cache"], sub["value_cache"], sub["block_table"],
+                              sub["context_lens"], num_heads=g["num_heads"], head_dim=128, block_size=128,
+                              scale=g["scale"], kv_heads=g["kv_heads"], q_len=g["q_len"]).bfloat16()
+    got = out[: exp.shape[0]].cpu()
+    assert torch.allclose(got.float(), exp.float(), rtol=2e-2, atol=4e-3)
+    g["value_cache"].mul_(2)
+    out2 = ops.paged_attention(g["query"], g["key_cache"], g["value_cache"], g["block_table"], g["context_lens"], **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(out2.float(), out.float() * 2)
+
+
+def test_moe_full_size_token_permutation_equivariance():
+    """The 256 + 1 expert FP8 layer at 4096 tokens: quantisation and every dot product are per
+    token, so with the routing held fixed, permuting the tokens permutes the output rows bit for
+    bit (the gate logits themselves come from a stream-K GEMM whose fp32 atomics may flip a
+    near-tie between runs, hence the fixed routing); the routing indices match the oracle's top-k
+    on the device's own gate scores."""
+    import bench
+    from oracle import moe as omoe
+    from pypto_b200 import ops
+    from pypto_b200.moe import MoELayer
+    if torch.cuda.mem_get_info()[0] < 40 << 30:
+        pytest.skip("needs about 30 GB of free device memory")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    m = bench.MOE
+    gen = torch.Generator(device=dev).manual_seed(3)
+    gate_w = (torch.randn(m["hidden"], m["n_experts"], device=dev, generator=gen) * 0.02).bfloat16()
+    bias = torch.rand(m["n_experts"], device=dev, generator=gen) * 0.2 - 0.1
+    layer = MoELayer.from_packed(ops.pack_weight(gate_w), bias,
+                                 bench.synthetic_experts(dev, gen, m["n_experts"], m["hidden"], m["inter"]),
+                                 bench.synthetic_experts(dev, gen, 1, m["hidden"], m["inter"]), m["topk"])
+    x = torch.randn(m["tokens"], m["hidden"], device=dev, generator=gen).bfloat16()
+    y, idx, w = layer.forward(x)
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    assert torch.isfinite(y.float()).all() and y.float().abs().max() > 0
+    perm = torch.randperm(m["tokens"], device=dev, generator=gen)
+    y2, _, _ = layer.forward(x[perm].contiguous(), routing=(idx[perm].contiguous(), w[perm].contiguous()))
+    torch.cuda.synchronize()
+    assert torch.equal(y2.view(torch.int16), y[perm].view(torch.int16))
+    scores = torch.sigmoid(ops.linear(x, layer.gate_packed)).cpu()
+    exp_idx, _ = omoe.topk_from_scores(scores, bias.cpu(), m["topk"])
+    assert (idx.cpu() == exp_idx).all(dim=1).float().mean() > 0.999   # sigmoid rounding may flip a near-tie
