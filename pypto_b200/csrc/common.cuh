@@ -50,6 +50,10 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType d
 
 int sm_count();
 
+// True the first time it is called for (key, current device): function attributes such as the
+// dynamic shared-memory limit are per device and have to be set once on each.
+bool first_use_on_device(int key);
+
 // Device error word layout (first 16 ints of every scratch buffer).
 //   [0] error code (0 = none), [1] where (site id), [2] blockIdx.x, [3] extra
 constexpr int kErrWords = 16;

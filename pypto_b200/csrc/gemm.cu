@@ -353,11 +353,8 @@ int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total,
   st = make_tensor_map_2d(&tm_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_rows_total, k,
                           static_cast<uint64_t>(k) * 2, kBK, bn, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != kOk) return st;
-  static bool attr_set = false;
-  if (!attr_set) {
+  if (first_use_on_device(0))
     PTO_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr_set = true;
-  }
   launch_kernel(gemm_bf16_kernel, dim3(grid), dim3(kGemmThreads), smem, stream, tm_a, tm_b, p);
   return check_cuda(cudaGetLastError(), "gemm_bf16_kernel launch");
 }

@@ -340,11 +340,9 @@ int moe_gemm_fp8_launch(int swiglu, const void* w, const float* w_scale, int exp
   st = make_tensor_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, total_rows, k, k, 128, kTN,
                           CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != kOk) return st;
-  static bool attr_set = false;
-  if (!attr_set) {
+  if (first_use_on_device(1)) {
     PTO_CUDA(cudaFuncSetAttribute(moe_gemm_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     PTO_CUDA(cudaFuncSetAttribute(moe_gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr_set = true;
   }
   if (swiglu) launch_kernel(moe_gemm_fp8_kernel<true>, dim3(sm_count()), dim3(kMoeThreads), smem, stream, tm_w, tm_x, p);
   else launch_kernel(moe_gemm_fp8_kernel<false>, dim3(sm_count()), dim3(kMoeThreads), smem, stream, tm_w, tm_x, p);
