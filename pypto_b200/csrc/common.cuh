@@ -373,6 +373,13 @@ __device__ __forceinline__ void fma_f32x2(unsigned long long& acc, unsigned long
   asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
 }
 
+// 16-byte shared-memory load from a shared-space address (constant offsets fold into the instruction).
+__device__ __forceinline__ ulonglong2 lds_u64x2(uint32_t saddr) {
+  ulonglong2 r;
+  asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(r.x), "=l"(r.y) : "r"(saddr));
+  return r;
+}
+
 __device__ __forceinline__ void red_add_f32(float* addr, float v) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
 }

@@ -37,6 +37,7 @@ constexpr int kPromoWarps = 16;
 constexpr int kRoleWarps = 4;      // two TMA producers and two MMA issuers, alternating K blocks
 constexpr int kMoeThreads = (kRoleWarps + kPromoWarps) * 32;
 constexpr int kNumPartial = 4;    // TMEM partial buffers of 128 token columns
+constexpr int kTabStride = kTN + 4;   // padded row of the scale table: the fill hits 8 banks, reads stay 16-byte aligned
 constexpr int kMoeMaxStages = 8;
 
 struct MoeGemmParams {
@@ -51,6 +52,12 @@ struct MoeGemmParams {
   int total_rows, stages;
   int* err;
 };
+
+__host__ __device__ inline int scale_region_floats(bool swiglu, int kblocks) {
+  const int comb = (swiglu ? 2 : 1) * kblocks * kTabStride;
+  const int exch = swiglu ? 64 * kTN : 0;
+  return comb > exch ? comb : exch;
+}
 
 // A unit = (expert, weight tile, chunk of 128 tokens).
 //   plain mode:  the tile is 128 consecutive output features.
@@ -68,10 +75,11 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const uint32_t tile_bytes = 128 * 128;
   const uint32_t stage_bytes = 2 * tile_bytes;   // weight tile, token tile
   uint8_t* after = smem + static_cast<size_t>(p.stages) * stage_bytes;
-  float* xs_s = reinterpret_cast<float*>(after);                       // [kblocks][kTN]
-  float* ws_s = xs_s + static_cast<size_t>(p.kblocks) * kTN;           // [2][kblocks]
-  float* exch = ws_s + 2 * p.kblocks;                                  // SwiGLU: [kTN][64] up values
-  int* prefix = reinterpret_cast<int*>(exch + (SWIGLU ? 64 * kTN : 0)); // [experts + 1] chunk prefix
+  // comb[a][kb][kTabStride]: weight-block scale x token scale, a = 0 gate (or plain) rows, 1 up rows.
+  // SwiGLU overlays the [kTN][64] exchange buffer of the epilogue on the same bytes.
+  float* comb = reinterpret_cast<float*>(after);
+  float* exch = comb;
+  int* prefix = reinterpret_cast<int*>(comb + scale_region_floats(SWIGLU, p.kblocks)); // [experts + 1] chunk prefix
   uint64_t* full = reinterpret_cast<uint64_t*>(prefix + ((p.experts + 2) & ~1));
   uint64_t* empty = full + kMoeMaxStages;
   uint64_t* pfull = empty + kMoeMaxStages;
@@ -216,18 +224,31 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const int row0 = p.offsets[e] + chunk * kTN;
       const int row_end = min(p.offsets[e + 1], p.total_rows);
       named_bar_sync(1, kPromoWarps * 32);  // previous unit's scales / exchange buffer no longer in use
-      for (int i = ptid; i < kTN * p.kblocks; i += kPromoWarps * 32) {
-        const int kb = i / kTN, col = i - kb * kTN;
-        const int row = row0 + col;
-        xs_s[i] = row < row_end ? p.x_scale[static_cast<size_t>(row) * p.kblocks + kb] : 0.f;
-      }
-      for (int i = ptid; i < 2 * p.kblocks; i += kPromoWarps * 32) {
-        const int a = i / p.kblocks, kb = i - a * p.kblocks;
-        const int wrow = e * p.w_rows_per_expert + (SWIGLU ? tile * 64 + a * p.up_row_off : tile * 128);
-        ws_s[i] = p.w_scale[static_cast<size_t>(wrow / 128) * p.kblocks + kb];
+      {
+        // the chunk's token scales are one contiguous run of x_scale: row-major [token][kb]
+        const int valid = max(0, min(row_end - row0, kTN)) * p.kblocks;
+        const float* xsrc = p.x_scale + static_cast<size_t>(row0) * p.kblocks;
+        const int wrow = e * p.w_rows_per_expert + (SWIGLU ? tile * 64 : tile * 128);
+        const float* w0 = p.w_scale + static_cast<size_t>(wrow / 128) * p.kblocks;
+        const float* w1 = p.w_scale + static_cast<size_t>((wrow + p.up_row_off) / 128) * p.kblocks;
+        const int step_col = (kPromoWarps * 32) / p.kblocks, step_kb = (kPromoWarps * 32) % p.kblocks;
+        int col = ptid / p.kblocks, kb = ptid % p.kblocks;
+        for (int i = ptid; i < kTN * p.kblocks; i += kPromoWarps * 32) {
+          const float x = i < valid ? __ldg(xsrc + i) : 0.f;
+          const int at = kb * kTabStride + col;
+          comb[at] = x * __ldg(w0 + kb);
+          if (SWIGLU) comb[p.kblocks * kTabStride + at] = x * __ldg(w1 + kb);
+          col += step_col;
+          kb += step_kb;
+          if (kb >= p.kblocks) {
+            kb -= p.kblocks;
+            ++col;
+          }
+        }
       }
       named_bar_sync(1, kPromoWarps * 32);
-      const float* ws = ws_s + ((SWIGLU && q >= 2) ? p.kblocks : 0);   // lanes 64-127 hold up rows
+      // lanes 64-127 hold up rows; shared-space address of this warp's 32 token columns
+      uint32_t xs = smem_u32(comb + ((SWIGLU && q >= 2) ? p.kblocks * kTabStride : 0) + col0);
 
       unsigned long long acc2[16];   // 32 fp32 accumulators as packed pairs (FFMA2)
 #pragma unroll
@@ -248,16 +269,13 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&pempty[pb]);
-        const float sw = ws[kb];
-        const unsigned long long sw2 = pack_f32x2(sw, sw);
-        const float* xs = xs_s + kb * kTN + col0;
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
-          const ulonglong2 x4 = *reinterpret_cast<const ulonglong2*>(xs + j);   // four token scales
-          fma_f32x2(acc2[j / 2], pack_f32x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), mul_f32x2(sw2, x4.x));
-          fma_f32x2(acc2[j / 2 + 1], pack_f32x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])),
-                    mul_f32x2(sw2, x4.y));
+          const ulonglong2 x4 = lds_u64x2(xs + j * 4);   // four combined scales
+          fma_f32x2(acc2[j / 2], pack_f32x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), x4.x);
+          fma_f32x2(acc2[j / 2 + 1], pack_f32x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), x4.y);
         }
+        xs += kTabStride * 4;
       }
       float acc[32];
 #pragma unroll
@@ -266,6 +284,7 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
       if constexpr (SWIGLU) {
         // lanes 64-127 (up rows) hand their values to lanes 0-63 (gate rows) of the same feature
+        named_bar_sync(2, kPromoWarps * 32);   // every warp is done with the scale table under exch
         if (q >= 2 && !dead) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) exch[(col0 + j) * 64 + (q - 2) * 32 + lane] = acc[j];
@@ -324,7 +343,7 @@ int moe_gemm_fp8_launch(int swiglu, const void* w, const float* w_scale, int exp
   p.w_scale = w_scale; p.x_scale = x_scale; p.route_w = route_w; p.out = static_cast<__nv_bfloat16*>(out);
   p.total_rows = total_rows; p.err = err;
   const size_t stage_bytes = static_cast<size_t>(2) * 128 * 128;
-  const size_t fixed = 1024 + sizeof(float) * (static_cast<size_t>(p.kblocks) * kTN + 2 * p.kblocks + (swiglu ? 64 * kTN : 0)) +
+  const size_t fixed = 1024 + sizeof(float) * static_cast<size_t>(scale_region_floats(swiglu != 0, p.kblocks)) +
                        sizeof(int) * (experts + 2) + 8 * (2 * kMoeMaxStages + 2 * kNumPartial) + 16;
   int stages = static_cast<int>((227 * 1024 - fixed) / stage_bytes);
   if (stages > kMoeMaxStages) stages = kMoeMaxStages;
