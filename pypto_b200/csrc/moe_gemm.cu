@@ -29,6 +29,8 @@
 #include "common.cuh"
 #include "kernels.h"
 
+#include <type_traits>
+
 namespace pto {
 namespace {
 
@@ -39,6 +41,7 @@ constexpr int kMoeThreads = (kRoleWarps + kPromoWarps) * 32;
 constexpr int kNumPartial = 4;    // TMEM partial buffers of 128 token columns
 constexpr int kTabStride = kTN + 4;   // padded row of the scale table: the fill hits 8 banks, reads stay 16-byte aligned
 constexpr int kMoeMaxStages = 8;
+constexpr int kMoeMaxKBlocks = 64;   // K <= 8192
 
 struct MoeGemmParams {
   const int32_t* offsets;   // [experts + 1]
@@ -231,20 +234,37 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const int wrow = e * p.w_rows_per_expert + (SWIGLU ? tile * 64 : tile * 128);
         const float* w0 = p.w_scale + static_cast<size_t>(wrow / 128) * p.kblocks;
         const float* w1 = p.w_scale + static_cast<size_t>((wrow + p.up_row_off) / 128) * p.kblocks;
+        // Loads of a batch are all issued before their first use, so a batch costs one memory latency.
+        const int total = kTN * p.kblocks;
         const int step_col = (kPromoWarps * 32) / p.kblocks, step_kb = (kPromoWarps * 32) % p.kblocks;
         int col = ptid / p.kblocks, kb = ptid % p.kblocks;
-        for (int i = ptid; i < kTN * p.kblocks; i += kPromoWarps * 32) {
-          const float x = i < valid ? __ldg(xsrc + i) : 0.f;
-          const int at = kb * kTabStride + col;
-          comb[at] = x * __ldg(w0 + kb);
-          if (SWIGLU) comb[p.kblocks * kTabStride + at] = x * __ldg(w1 + kb);
-          col += step_col;
-          kb += step_kb;
-          if (kb >= p.kblocks) {
-            kb -= p.kblocks;
-            ++col;
+        auto fill = [&](auto batch_tag) {
+          constexpr int kBatch = decltype(batch_tag)::value;
+          for (int base = ptid; base < total; base += kBatch * kPromoWarps * 32) {
+            float xv[kBatch];
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+              const int i = base + r * kPromoWarps * 32;
+              xv[r] = i < valid ? __ldg(xsrc + i) : 0.f;
+            }
+#pragma unroll
+            for (int r = 0; r < kBatch; ++r) {
+              if (base + r * kPromoWarps * 32 < total) {
+                const int at = kb * kTabStride + col;
+                comb[at] = xv[r] * __ldg(w0 + kb);
+                if (SWIGLU) comb[p.kblocks * kTabStride + at] = xv[r] * __ldg(w1 + kb);
+              }
+              col += step_col;
+              kb += step_kb;
+              if (kb >= p.kblocks) {
+                kb -= p.kblocks;
+                ++col;
+              }
+            }
           }
-        }
+        };
+        if (p.kblocks > 32) fill(std::integral_constant<int, 8>{});
+        else fill(std::integral_constant<int, 4>{});
       }
       named_bar_sync(1, kPromoWarps * 32);
       // lanes 64-127 hold up rows; shared-space address of this warp's 32 token columns
@@ -283,23 +303,43 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       // a warp that timed out keeps walking the units so that the named barriers stay matched
 
       if constexpr (SWIGLU) {
-        // lanes 64-127 (up rows) hand their values to lanes 0-63 (gate rows) of the same feature
+        // Gate rows sit in lanes 0-63, the matching up rows in lanes 64-127.  The two threads of a feature
+        // swap half of their 32 token columns through shared memory and each finishes 16 outputs.
         named_bar_sync(2, kPromoWarps * 32);   // every warp is done with the scale table under exch
-        if (q >= 2 && !dead) {
+        const bool is_up = q >= 2;
+        const int f = (q & 1) * 32 + lane;     // feature within the tile
+        float* mine = exch + col0 * 64 + f;
+        if (!dead) {
+          if (is_up) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) exch[(col0 + j) * 64 + (q - 2) * 32 + lane] = acc[j];
+            for (int j = 0; j < 16; ++j) mine[j * 64] = acc[j];
+          } else {
+#pragma unroll
+            for (int j = 16; j < 32; ++j) mine[j * 64] = acc[j];
+          }
         }
-        named_bar_sync(2, kPromoWarps * 32);
-        if (q < 2 && !dead) {
-          const int feat = tile * 64 + q * 32 + lane;
-          const float* up = exch + col0 * 64 + q * 32 + lane;
+        named_bar_sync(3 + (pw >> 2) * 2 + (q & 1), 64);   // the gate warp and the up warp of these features
+        if (!dead) {
+          const int feat = tile * 64 + f;
+          if (is_up) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int row = row0 + col0 + j;
-            if (row < row_end) {
-              const float g = acc[j];
-              p.out[static_cast<size_t>(row) * p.n_out + feat] =
-                  __float2bfloat16_rn(g * (1.f / (1.f + __expf(-g))) * up[j * 64]);
+            for (int j = 16; j < 32; ++j) {
+              const int row = row0 + col0 + j;
+              if (row < row_end) {
+                const float g = mine[j * 64];
+                p.out[static_cast<size_t>(row) * p.n_out + feat] =
+                    __float2bfloat16_rn(g * (1.f / (1.f + __expf(-g))) * acc[j]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int row = row0 + col0 + j;
+              if (row < row_end) {
+                const float g = acc[j];
+                p.out[static_cast<size_t>(row) * p.n_out + feat] =
+                    __float2bfloat16_rn(g * (1.f / (1.f + __expf(-g))) * mine[j * 64]);
+              }
             }
           }
         }
@@ -332,7 +372,7 @@ int moe_gemm_fp8_launch(int swiglu, const void* w, const float* w_scale, int exp
                         int total_rows, const float* route_w, void* out, int* err, cudaStream_t stream) {
   PTO_REQUIRE(w && w_scale && x && x_scale && offsets && out, "moe_gemm: NULL tensor");
   PTO_REQUIRE(experts > 0 && experts <= 4096, "moe_gemm: 1..4096 experts");
-  PTO_REQUIRE(k > 0 && k % 128 == 0 && k <= 64 * 128, "moe_gemm: K must be a multiple of 128, at most 8192");
+  PTO_REQUIRE(k > 0 && k % 128 == 0 && k <= kMoeMaxKBlocks * 128, "moe_gemm: K must be a multiple of 128, at most 8192");
   PTO_REQUIRE(n_out > 0 && n_out % 128 == 0, "moe_gemm: output features must be a multiple of 128");
   PTO_REQUIRE(w_rows_per_expert == (swiglu ? 2 * n_out : n_out), "moe_gemm: weight rows per expert mismatch");
   if (total_rows <= 0) return kOk;
