@@ -59,6 +59,7 @@ bool first_use_on_device(int key);
 constexpr int kErrWords = 16;
 constexpr int kErrBarrierTimeout = 1;
 constexpr int kErrBadBlockId = 2;
+constexpr int kErrBadIndex = 3;   // a kernel's own bounds check refused an access
 
 // Programmatic dependent launch: every kernel of this library is launched with the
 // programmatic-stream-serialization attribute (unless PTO_PDL=0) so that its prologue (barrier
@@ -186,6 +187,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
       if (mbar_try_wait(bar, parity)) return true;
     if (global_timer_ns() - t0 > kWaitTimeoutNs) return false;
   }
+}
+
+// Whole-warp wait.  Lanes can see the phase complete on different polls and leave the polling loop at
+// different times; the vote brings them back together (and makes the result warp-uniform) so that
+// .sync.aligned instructions (tcgen05.ld, ldmatrix, mma.sync) may follow.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity) {
+  const bool ok = mbar_wait(bar, parity);
+  return __all_sync(0xffffffffu, ok) != 0;
 }
 
 // 2-D tiled TMA load into this CTA's shared memory; completion is signalled on

@@ -214,7 +214,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     for (; next_seg(cur, it_hi, p.kblocks_total, stride, sg); ++ui) {
       const int at = sg.tile / p.b_tiles, bt = sg.tile - at * p.b_tiles;
       const uint32_t ab = ui % p.nbuf;
-      if (!mbar_wait(&tmem_full[ab], (ui / p.nbuf) & 1u)) {
+      if (!mbar_wait_warp(&tmem_full[ab], (ui / p.nbuf) & 1u)) {
         report_error(p.err, kErrBarrierTimeout, 43, static_cast<int>(ui));
         break;
       }

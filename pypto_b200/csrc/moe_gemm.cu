@@ -276,7 +276,7 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
       for (int kb = 0; kb < p.kblocks && !dead; ++kb, ++it) {
         const uint32_t pb = it % kNumPartial;
-        if (!mbar_wait(&pfull[pb], (it / kNumPartial) & 1u)) {
+        if (!mbar_wait_warp(&pfull[pb], (it / kNumPartial) & 1u)) {
           report_error(p.err, kErrBarrierTimeout, 52, static_cast<int>(it));
           dead = true;
           break;

@@ -316,7 +316,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       const uint32_t qk = 2 * nt_done, qv = qk + 1;
       const uint32_t buf_k = qk % kNBuf, buf_v = qv % kNBuf;
 
-      if (!mbar_wait(&full[buf_k], (qk / kNBuf) & 1u)) {
+      if (!mbar_wait_warp(&full[buf_k], (qk / kNBuf) & 1u)) {
         report_error(p.err, kErrBarrierTimeout, 20 + warp, static_cast<int>(nt_done));
         dead = true;
         break;
@@ -397,7 +397,7 @@ pa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
           }
         }
 
-      if (!mbar_wait(&full[buf_v], (qv / kNBuf) & 1u)) {
+      if (!mbar_wait_warp(&full[buf_v], (qv / kNBuf) & 1u)) {
         report_error(p.err, kErrBarrierTimeout, 30 + warp, static_cast<int>(nt_done));
         dead = true;
         break;
