@@ -107,6 +107,24 @@ PTO_API int pto_run(pto_worker* w, int32_t cid, const pto_task_args* args);
 /* NUL-separated, double-NUL-terminated list of operator names. */
 PTO_API const char* pto_op_list(void);
 
+/* External kernels: the reference's plugin hook for hand-written device code,
+ * `@pl.function(type=AIV, external_source=...)` / `@pl.jit.extern(source=...)`
+ * (python/pypto/jit/decorator.py:2669-2738; the backend references the file instead of
+ * generating code, python/pypto/backend/pto_backend.py:1181-1191, 1884-1897; example kernel
+ * tests/st/runtime/external_kernel/kernels/aiv/spmd_write.cpp:59-69).
+ *   image   a cubin or PTX image for sm_100a (copied; need not outlive the call) that defines
+ *           `extern "C" __global__ void <entry>(const int64_t* args)`
+ *   launch  `block_num` CTAs (the reference's SPMD blocks: blockIdx.x is the block index) of
+ *           `threads_per_block` threads on the worker's stream
+ *   args    in device memory, the reference's kernel_entry order: args[0..T-1] are pointers to
+ *           one pto_chip_tensor per tensor, args[T..] the scalars bit-cast to 64 bits
+ *           (include/pypto_b200_device.h has the accessors).
+ * Ids share the space of pto_register_callable and are released by pto_unregister_callable. */
+PTO_API int pto_register_kernel_image(pto_worker* w, const void* image, size_t nbytes, const char* entry,
+                                      int32_t* cid);
+PTO_API int pto_run_kernel(pto_worker* w, int32_t cid, const pto_task_args* args, uint32_t block_num,
+                           uint32_t threads_per_block);
+
 /* ---- direct launchers ---- */
 
 /* Paged-attention decode.  Replaces the orchestration `paged_attention` and its four

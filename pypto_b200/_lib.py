@@ -58,6 +58,8 @@ SIGNATURES = {
     "pto_unregister_callable": (_i, [_p, C.c_int32]),
     "pto_run": (_i, [_p, C.c_int32, C.POINTER(TaskArgs)]),
     "pto_op_list": (C.POINTER(C.c_char), []),
+    "pto_register_kernel_image": (_i, [_p, _p, _sz, C.c_char_p, _i32p]),
+    "pto_run_kernel": (_i, [_p, C.c_int32, C.POINTER(TaskArgs), C.c_uint32, C.c_uint32]),
     "pto_paged_attention_scratch_bytes": (_sz, [_i, _i, _i, _i]),
     "pto_paged_attention": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _f, _p, _sz, _p]),
     "pto_paged_attention_static": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _f, _p, _p]),

@@ -111,6 +111,11 @@ Worker::~Worker() {
   cudaSetDevice(device);
   for (auto& kv : allocs) cudaFree(reinterpret_cast<void*>(kv.first));
   allocs.clear();
+  for (auto& kv : kernels) {
+    if (kv.second.args_dev) cudaFree(kv.second.args_dev);
+    if (kv.second.library) cudaLibraryUnload(kv.second.library);
+  }
+  kernels.clear();
   if (scratch) cudaFree(scratch);
   if (stream) cudaStreamDestroy(stream);
 }
@@ -271,7 +276,80 @@ int pto_register_callable(pto_worker* h, const char* op_name, int32_t* cid) {
 int pto_unregister_callable(pto_worker* h, int32_t cid) {
   PTO_WORKER(h);
   std::lock_guard<std::mutex> g(w->mu);
+  auto k = w->kernels.find(cid);
+  if (k != w->kernels.end()) {
+    PTO_CUDA(cudaStreamSynchronize(w->stream));   // a launch may still read its argument block
+    if (k->second.args_dev) cudaFree(k->second.args_dev);
+    if (k->second.library) cudaLibraryUnload(k->second.library);
+    w->kernels.erase(k);
+    return pto::kOk;
+  }
   if (w->callables.erase(cid) == 0) return pto::fail(pto::kNotFound, "unregister: unknown callable id");
+  return pto::kOk;
+}
+
+int pto_register_kernel_image(pto_worker* h, const void* image, size_t nbytes, const char* entry, int32_t* cid) {
+  PTO_WORKER(h);
+  if (image == nullptr || nbytes == 0 || entry == nullptr || cid == nullptr)
+    return pto::fail(pto::kInvalidArgument, "register_kernel_image: NULL or empty argument");
+  pto::ExternKernel k;
+  // The image is copied by the loader; it need not outlive this call.
+  cudaError_t e = cudaLibraryLoadData(&k.library, image, nullptr, nullptr, 0, nullptr, nullptr, 0);
+  if (e != cudaSuccess) return pto::check_cuda(e, "cudaLibraryLoadData (is the image built for sm_100a?)");
+  e = cudaLibraryGetKernel(&k.kernel, k.library, entry);
+  if (e != cudaSuccess) {
+    cudaLibraryUnload(k.library);
+    cudaGetLastError();
+    return pto::fail(pto::kNotFound, std::string("kernel image has no extern \"C\" __global__ entry '") + entry + "'");
+  }
+  e = cudaMalloc(&k.args_dev, pto::kExternArgSlots * pto::kExternArgSlotBytes);
+  if (e != cudaSuccess) {
+    cudaLibraryUnload(k.library);
+    return pto::check_cuda(e, "cudaMalloc(kernel argument ring)");
+  }
+  std::lock_guard<std::mutex> g(w->mu);
+  int32_t id = w->next_cid++;
+  w->kernels[id] = k;
+  *cid = id;
+  return pto::kOk;
+}
+
+int pto_run_kernel(pto_worker* h, int32_t cid, const pto_task_args* args, uint32_t block_num,
+                   uint32_t threads_per_block) {
+  PTO_WORKER(h);
+  if (args == nullptr) return pto::fail(pto::kInvalidArgument, "run_kernel: args is NULL");
+  if (block_num == 0 || threads_per_block == 0 || threads_per_block > 1024)
+    return pto::fail(pto::kInvalidArgument, "run_kernel: block_num >= 1 and 1 <= threads_per_block <= 1024");
+  if ((args->n_tensors && !args->tensors) || (args->n_scalars && !args->scalars))
+    return pto::fail(pto::kInvalidArgument, "run_kernel: NULL tensor or scalar array");
+  // block layout: int64 args[n_tensors + n_scalars], padded to 16 bytes, then the tensor descriptors
+  const size_t n = static_cast<size_t>(args->n_tensors) + args->n_scalars;
+  const size_t desc_off = (n * sizeof(int64_t) + 15) & ~static_cast<size_t>(15);
+  const size_t total = desc_off + args->n_tensors * sizeof(pto_chip_tensor);
+  if (total > pto::kExternArgSlotBytes) return pto::fail(pto::kInvalidArgument, "run_kernel: too many arguments");
+  cudaKernel_t kernel = nullptr;
+  uint8_t* slot = nullptr;
+  {
+    std::lock_guard<std::mutex> g(w->mu);
+    auto it = w->kernels.find(cid);
+    if (it == w->kernels.end()) return pto::fail(pto::kNotFound, "run_kernel: unknown kernel id");
+    kernel = it->second.kernel;
+    slot = static_cast<uint8_t*>(it->second.args_dev) +
+           (it->second.next_slot++ % pto::kExternArgSlots) * pto::kExternArgSlotBytes;
+  }
+  alignas(16) uint8_t block[pto::kExternArgSlotBytes];
+  int64_t* a = reinterpret_cast<int64_t*>(block);
+  for (uint32_t i = 0; i < args->n_tensors; ++i)
+    a[i] = static_cast<int64_t>(reinterpret_cast<uintptr_t>(slot + desc_off + i * sizeof(pto_chip_tensor)));
+  for (uint32_t i = 0; i < args->n_scalars; ++i) a[args->n_tensors + i] = static_cast<int64_t>(args->scalars[i]);
+  if (args->n_tensors) memcpy(block + desc_off, args->tensors, args->n_tensors * sizeof(pto_chip_tensor));
+  // Pageable source: the runtime stages it before returning, so `block` may go out of scope.  The ring slot is
+  // reused only after kExternArgSlots later launches on the same stream, i.e. after this launch has finished.
+  PTO_CUDA(cudaMemcpyAsync(slot, block, total, cudaMemcpyHostToDevice, w->stream));
+  void* dev_args = slot;
+  void* params[] = {&dev_args};
+  PTO_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(kernel), dim3(block_num), dim3(threads_per_block), params, 0,
+                            w->stream));
   return pto::kOk;
 }
 

@@ -14,12 +14,23 @@ namespace pto {
 struct Worker;
 using OpFn = int (*)(Worker*, const pto_task_args*);
 
+// A user kernel loaded from a cubin / PTX image (pto_register_kernel_image).
+struct ExternKernel {
+  cudaLibrary_t library = nullptr;
+  cudaKernel_t kernel = nullptr;
+  void* args_dev = nullptr;   // ring of argument blocks: the launch reads its block from device memory
+  uint32_t next_slot = 0;
+};
+constexpr uint32_t kExternArgSlots = 32;
+constexpr size_t kExternArgSlotBytes = 4096;
+
 struct Worker {
   int device = 0;
   cudaStream_t stream = nullptr;
   std::mutex mu;
   std::map<uint64_t, size_t> allocs;  // device pointers handed out by pto_malloc
   std::map<int32_t, OpFn> callables;
+  std::map<int32_t, ExternKernel> kernels;   // share the id space of `callables`
   int32_t next_cid = 1;
   void* scratch = nullptr;
   size_t scratch_bytes = 0;

@@ -171,5 +171,12 @@ def compile(program, *, output_dir=None, strategy=OptimizationStrategy.Default, 
         raise TypeError(f"compile() expects a @pl.program class or a pl.function, got {type(program).__name__}")
     if entry is None:
         raise ValueError("program has no functions")
-    fused = fused_programs.lookup(entry)
+    try:
+        fused = fused_programs.lookup(entry)
+    except NotImplementedError:
+        # the reference's plugin hook: an orchestration that only dispatches external kernels
+        from ..runtime import extern_kernel
+        fused = extern_kernel.match(entry, program if isinstance(program, Program) else None)
+        if fused is None:
+            raise
     return CompiledProgram(entry, fused, platform, bt, program)

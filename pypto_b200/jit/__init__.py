@@ -66,10 +66,30 @@ class _Jit:
     host = staticmethod(_sub(FunctionType.Opaque))
 
     @staticmethod
-    def extern(source=None, core_type=None, **attrs):
+    def extern(func=None, *, core_type="aiv", source=None, aic_source=None, aiv_source=None,
+               dual_aiv_dispatch=False, include_dirs=None):
+        """Signature-only stub backed by a hand-written kernel source
+        (python/pypto/jit/decorator.py:2669-2738).  Here the source is CUDA for sm_100a; the
+        AIC+AIV ``mixed`` form is recorded but has no single-kernel meaning on a GPU and is
+        refused when the program is compiled."""
+        if core_type not in ("aic", "aiv", "mixed"):
+            raise ValueError(f"@pl.jit.extern core_type must be 'aic', 'aiv', or 'mixed', got {core_type!r}")
+        if dual_aiv_dispatch and core_type != "mixed":
+            raise ValueError("@pl.jit.extern dual_aiv_dispatch=True requires core_type='mixed'")
+
         def wrap(f):
-            return Function(f, FunctionType.AIV, dict(attrs, external_source=source, core_type=core_type))
-        return wrap
+            if core_type == "mixed":
+                if aic_source is None or aiv_source is None:
+                    raise ValueError("@pl.jit.extern(core_type='mixed') requires both aic_source= and aiv_source=")
+                single = aiv_source
+            else:
+                single = source if source is not None else (aic_source or aiv_source)
+                if single is None:
+                    raise ValueError(f"@pl.jit.extern(core_type={core_type!r}) requires source=")
+            return Function(f, FunctionType.AIC if core_type == "aic" else FunctionType.AIV,
+                            dict(external_source=single, core_type=core_type, include_dirs=list(include_dirs or ()),
+                                 dual_aiv_dispatch=dual_aiv_dispatch))
+        return wrap(func) if func is not None else wrap
 
 
 jit = _Jit()

@@ -5,6 +5,7 @@ from __future__ import annotations
 
 import contextvars
 import ctypes as C
+import hashlib
 import weakref
 
 import torch
@@ -36,6 +37,7 @@ class ChipWorker:
         self._live_ptrs: dict[int, int] = {}
         self._pool: dict[int, list[int]] = {}   # freed staging blocks by size, reused by one-shot calls
         self._cid_cache: dict[str, int] = {}
+        self._kernel_ids: dict[tuple, int] = {}
         self._handles: "weakref.WeakSet[RegistrationHandle]" = weakref.WeakSet()
         self._token = None
         if auto_init is None or auto_init:
@@ -64,7 +66,7 @@ class ChipWorker:
         lib = _lib.load()
         _lib.check(lib.pto_worker_destroy(self._handle))   # frees everything the worker still owns
         self._handle, self._initialized = None, False
-        self._owned.clear(); self._live_ptrs.clear(); self._pool.clear(); self._cid_cache.clear()
+        self._owned.clear(); self._live_ptrs.clear(); self._pool.clear(); self._cid_cache.clear(); self._kernel_ids.clear()
 
     def __enter__(self):
         self.init()
@@ -198,11 +200,8 @@ class ChipWorker:
             cid = self._cid_cache[op_name] = out.value
         return cid
 
-    def launch(self, op_name: str, tensors: list[DeviceTensor], scalars: list[int]) -> None:
-        """Run one fused operator: tensors first, then uint64 scalars (the kernel_entry order,
-        python/pypto/backend/pto_backend.py:541-629)."""
+    def _task_args(self, tensors: list[DeviceTensor], scalars: list[int]):
         from ..ops import dtype_code
-        self._require_ready("launch")
         arr = (_lib.ChipTensor * max(1, len(tensors)))()
         for i, t in enumerate(tensors):
             arr[i].addr, arr[i].start_offset, arr[i].ndims = t.data_ptr, 0, len(t.shape)
@@ -212,8 +211,37 @@ class ChipWorker:
                 arr[i].shapes[j] = s
             arr[i].dtype = dtype_code(t.dtype)
         sc = (C.c_uint64 * max(1, len(scalars)))(*[int(s) & 0xFFFFFFFFFFFFFFFF for s in scalars])
-        args = _lib.TaskArgs(arr, len(tensors), sc, len(scalars))
+        return _lib.TaskArgs(arr, len(tensors), sc, len(scalars)), (arr, sc)
+
+    def launch(self, op_name: str, tensors: list[DeviceTensor], scalars: list[int]) -> None:
+        """Run one fused operator: tensors first, then uint64 scalars (the kernel_entry order,
+        python/pypto/backend/pto_backend.py:541-629)."""
+        self._require_ready("launch")
+        args, _keep = self._task_args(tensors, scalars)
         _lib.check(_lib.load().pto_run(self._handle, self._cid(op_name), C.byref(args)))
+
+    # ---- external kernels (the reference's external_source / jit.extern hook) ----
+    def register_kernel_image(self, image: bytes, entry: str = "kernel_entry") -> int:
+        """Load a cubin/PTX image built for sm_100a and return the id of its entry kernel.
+        Images are cached per worker by content, so registering the same kernel twice is free."""
+        self._require_ready("register_kernel_image")
+        key = (hashlib.sha256(image).digest(), entry)
+        cid = self._kernel_ids.get(key)
+        if cid is None:
+            out = C.c_int32()
+            buf = C.create_string_buffer(image, len(image))
+            _lib.check(_lib.load().pto_register_kernel_image(self._handle, buf, len(image), entry.encode(),
+                                                             C.byref(out)))
+            cid = self._kernel_ids[key] = out.value
+        return cid
+
+    def launch_kernel(self, cid: int, tensors: list[DeviceTensor], scalars: list[int], *, block_num: int = 1,
+                      threads_per_block: int = 128) -> None:
+        """One launch of an external kernel: `block_num` SPMD blocks (CTAs) of `threads_per_block`
+        threads; arguments in the kernel_entry order (tensors, then scalars bit-cast to 64 bits)."""
+        self._require_ready("launch_kernel")
+        args, _keep = self._task_args(tensors, scalars)
+        _lib.check(_lib.load().pto_run_kernel(self._handle, cid, C.byref(args), block_num, threads_per_block))
 
     def _check_binding(self, compiled) -> None:
         if compiled.platform != self.platform:
