@@ -72,7 +72,7 @@ class ClockSampler:
     _NAMES = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
               0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, index: int, period: float = 0.01):
+    def __init__(self, index: int, period: float = 0.002):
         self.index, self.period = index, period
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop, self._thread, self.active = threading.Event(), None, False
@@ -90,16 +90,23 @@ class ClockSampler:
         self._thread.start()
         return self
 
+    def sample_now(self):
+        """One sample from the calling thread (the timed region of a short run can be shorter than the
+        sampling period; the caller takes this sample while the queued steps are still executing)."""
+        if self._thread is None:
+            return
+        try:
+            nv = self.nv
+            self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+            mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            self.reasons.update(n for b, n in self._NAMES.items() if mask & b)
+        except Exception:
+            pass
+
     def _run(self):
-        nv = self.nv
         while not self._stop.is_set():
             if self.active:
-                try:
-                    self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
-                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
-                    self.reasons.update(n for b, n in self._NAMES.items() if mask & b)
-                except Exception:
-                    pass
+                self.sample_now()
             time.sleep(self.period)
 
     def stop(self):
@@ -158,6 +165,7 @@ def timed(step, d: Dist, steps: int, warmup: int):
     for _ in range(steps):
         step()
     e1.record()
+    sampler.sample_now()           # the steps above are queued and still running
     torch.cuda.synchronize()
     sampler.active = False
     d.barrier()
