@@ -322,8 +322,14 @@ int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total,
   p.b_tiles = (b_rows + bn - 1) / bn;
   const int stage_atom_bytes = p.mt * kBM * 128 + (dual ? 2 : 1) * bn * 128;
   p.katoms = (stage_atom_bytes <= 24 * 1024 && k > kBK) ? 2 : 1;   // small stages: two K atoms per barrier round
-  p.kblocks_total = (k + kBK * p.katoms - 1) / (kBK * p.katoms);
   const int tiles = p.a_tiles * p.b_tiles;
+  // Decode-shaped problems (weights as A, a few dozen tokens as the MMA N) with a long stream per CTA: four atoms
+  // per round.  Each round costs a fixed ~0.3 us of barrier hand-offs next to 0.4 us per atom of loading and
+  // MMA issue, so longer rounds pay as long as every CTA still gets ten or more of them.
+  if (swap && epi == kGemmEpiAtomic && p.katoms == 2 &&
+      static_cast<long long>(tiles) * ((k + 4 * kBK - 1) / (4 * kBK)) >= 10ll * sm_count())
+    p.katoms = 4;
+  p.kblocks_total = (k + kBK * p.katoms - 1) / (kBK * p.katoms);
   PTO_REQUIRE(static_cast<long long>(tiles) * p.kblocks_total < (1ll << 31), "gemm: problem too large");
   p.iters_total = tiles * p.kblocks_total;
   int grid = sm_count();
