@@ -101,7 +101,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   uint64_t* empty = full + kMaxStages;
   uint64_t* tmem_full = empty + kMaxStages;
   uint64_t* tmem_empty = tmem_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* drain = tmem_empty + 2;   // every MMA of the issuer has completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t acc_cols = nacc * p.bn;                // columns of one 128-row accumulator
@@ -118,6 +119,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       mbar_init(&tmem_full[i], 1);
       mbar_init(&tmem_empty[i], 4);
     }
+    mbar_init(drain, 1);
     fence_barrier_init();
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b);
@@ -203,6 +205,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         if (ok) umma_commit(&tmem_full[ab]);
       }
+      // TMEM is released only after every MMA has completed, also when a wait gave up
+      umma_commit(drain);
+      if (!mbar_wait(drain, 0)) report_error(p.err, kErrBarrierTimeout, 44, static_cast<int>(it));
     }
     __syncwarp();
   } else {
@@ -350,7 +355,7 @@ int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total,
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) stages = 2;
   p.stages = stages;
-  const size_t smem = 1024 + static_cast<size_t>(stages) * stage_bytes + (2 * kMaxStages + 4) * 8 + 16;
+  const size_t smem = 1024 + static_cast<size_t>(stages) * stage_bytes + (2 * kMaxStages + 5) * 8 + 16;
 
   CUtensorMap tm_a, tm_b;
   int st = make_tensor_map_2d(&tm_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_rows, k, static_cast<uint64_t>(k) * 2,

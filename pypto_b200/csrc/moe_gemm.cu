@@ -87,7 +87,8 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   uint64_t* empty = full + kMoeMaxStages;
   uint64_t* pfull = empty + kMoeMaxStages;
   uint64_t* pempty = pfull + kNumPartial;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pempty + kNumPartial);
+  uint64_t* drain = pempty + kNumPartial;   // one per MMA issuer: all of its MMAs have completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr uint32_t tmem_cols = kNumPartial * kTN;  // 512
@@ -101,6 +102,8 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       mbar_init(&pfull[i], 1);
       mbar_init(&pempty[i], kPromoWarps);
     }
+    mbar_init(&drain[0], 1);
+    mbar_init(&drain[1], 1);
     fence_barrier_init();
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_x);
@@ -211,6 +214,10 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           umma_commit(&pfull[pb]);
         }
       }
+      // TMEM is released only after every MMA of this thread has completed, also when a wait gave up:
+      // a CTA that exits with tensor-core work in flight ends the whole launch with an error.
+      umma_commit(&drain[me]);
+      if (!mbar_wait(&drain[me], 0)) report_error(p.err, kErrBarrierTimeout, 53, static_cast<int>(it));
     }
     __syncwarp();
   } else {
@@ -384,9 +391,15 @@ int moe_gemm_fp8_launch(int swiglu, const void* w, const float* w_scale, int exp
   p.total_rows = total_rows; p.err = err;
   const size_t stage_bytes = static_cast<size_t>(2) * 128 * 128;
   const size_t fixed = 1024 + sizeof(float) * static_cast<size_t>(scale_region_floats(swiglu != 0, p.kblocks)) +
-                       sizeof(int) * (experts + 2) + 8 * (2 * kMoeMaxStages + 2 * kNumPartial) + 16;
+                       sizeof(int) * (experts + 2) + 8 * (2 * kMoeMaxStages + 2 * kNumPartial + 2) + 16;
   int stages = static_cast<int>((227 * 1024 - fixed) / stage_bytes);
   if (stages > kMoeMaxStages) stages = kMoeMaxStages;
+  // The two producers (and the two issuers) take alternate K blocks.  With an even number of stages every stage
+  // belongs to one producer and one issuer, so each stage is an ordinary in-order ring.  With an odd number a
+  // stage alternates between the two producers, and a producer that is ten K blocks ahead of a lagging issuer
+  // would find the stage's `empty` barrier in a phase of the parity it waits for (zero completed phases look
+  // like two) and overwrite operands that have not been consumed.
+  stages &= ~1;
   PTO_REQUIRE(stages >= 2, "moe_gemm: shared memory does not fit two pipeline stages");
   p.stages = stages;
   const size_t smem = fixed + stages * stage_bytes;
