@@ -38,3 +38,23 @@ def test_cpu_tensors_are_refused_not_computed():
     with pytest.raises(BackendUnavailable):
         ops.paged_gather(torch.zeros(4, 4), torch.zeros(1, dtype=torch.int32),
                          torch.zeros(1, dtype=torch.int32), 4)
+
+
+def test_header_is_plain_c_and_the_library_serves_a_c_host(tmp_path):
+    """gcc (C, not C++) compiles a host that includes the public header, dlopens the library and
+    makes the first calls of a foreign-language binding.  Without a GPU pto_worker_create must fail
+    with a status and a message instead of crashing."""
+    import shutil
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    lib = root / "pypto_b200" / "lib" / "libpypto_b200.so"
+    assert lib.exists(), "build the library first (python -m pypto_b200.build)"
+    gcc = shutil.which("gcc")
+    assert gcc, "gcc is part of this image"
+    exe = tmp_path / "c_abi_host"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-I", str(root / "include"), str(root / "tests" / "c_abi_host.c"),
+                    "-ldl", "-o", str(exe)], check=True)
+    r = subprocess.run([str(exe), str(lib)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "version=" in r.stdout and "op=paged_attention" in r.stdout and "worker_create=" in r.stdout
