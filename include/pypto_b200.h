@@ -215,6 +215,13 @@ PTO_API int pto_ffn_swiglu(const void* x, const void* w_gate_up, const void* w_d
  * examples/models/08_llama_mini.py:94-118 is the gamma-free form). */
 PTO_API int pto_rms_norm(const void* x, int x_dtype, const float* gamma, void* out, int out_dtype, int64_t rows,
                          int hidden, float eps, void* stream);
+/* The same with two optional side jobs that save a decoder layer two launches
+ * (examples/models/qwen3_jit/qwen3_decode.py:50-112 runs the norm right before the QKV projection and keeps
+ * the un-normalised rows as the residual): copy_f32 (or NULL) receives x as fp32 [rows, hidden];
+ * zero (or NULL; 16-byte aligned, zero_bytes a multiple of 16) is cleared, e.g. the fp32 accumulator of the
+ * projection that follows. */
+PTO_API int pto_rms_norm_ex(const void* x, int x_dtype, const float* gamma, void* out, int out_dtype, int64_t rows,
+                            int hidden, float eps, float* copy_f32, void* zero, size_t zero_bytes, void* stream);
 
 /* RoPE (rotate-half) on Q and K at pos = seq_len - 1 and append of the rotated K row and the
  * V row to the paged cache (examples/models/qwen3_jit/kernels/attention.py:40-111).

@@ -42,19 +42,26 @@ __device__ __forceinline__ float block_sum_256(float v, float* red) {
   return r;
 }
 
-// One CTA (256 threads) per row.
+// One CTA (256 threads) per row.  Two optional side jobs let a decoder layer drop two launches: `copy`
+// receives the row as fp32 (the residual that the next projection accumulates onto), and `zero`
+// (16-byte vectors) is cleared by the whole grid (the accumulator of the next stream-K GEMM).
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 rms_norm_kernel(const TI* __restrict__ x, const float* __restrict__ gamma, TO* __restrict__ out, int hidden,
-                float eps) {
+                float eps, float* __restrict__ copy, uint4* __restrict__ zero, long long zero_vecs) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[8];
   const TI* xr = x + static_cast<size_t>(blockIdx.x) * hidden;
   TO* orow = out + static_cast<size_t>(blockIdx.x) * hidden;
+  float* crow = copy ? copy + static_cast<size_t>(blockIdx.x) * hidden : nullptr;
+  for (long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; i < zero_vecs;
+       i += static_cast<long long>(gridDim.x) * 256)
+    zero[i] = make_uint4(0u, 0u, 0u, 0u);
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden; i += 256) {
     const float v = to_f32(xr[i]);
+    if (crow) crow[i] = v;
     ss += v * v;
   }
   const float mean = block_sum_256(ss, red) / static_cast<float>(hidden);
@@ -164,18 +171,25 @@ int grid_for(long long n, int block) {
 }  // namespace
 
 int rms_norm_launch(const void* x, int x_dtype, const float* gamma, void* out, int out_dtype, long long rows,
-                    int hidden, float eps, cudaStream_t stream) {
+                    int hidden, float eps, float* copy_f32, void* zero, size_t zero_bytes, cudaStream_t stream) {
   PTO_REQUIRE(x && out && rows >= 0 && hidden > 0, "rms_norm: bad arguments");
-  if (rows == 0) return kOk;
+  PTO_REQUIRE(zero_bytes == 0 || (zero && zero_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(zero) & 15) == 0),
+              "rms_norm: the buffer to clear must be 16-byte aligned and a multiple of 16 bytes");
+  if (rows == 0) {
+    if (zero_bytes) PTO_CUDA(cudaMemsetAsync(zero, 0, zero_bytes, stream));
+    return kOk;
+  }
   const unsigned g = static_cast<unsigned>(rows);
+  uint4* z = static_cast<uint4*>(zero);
+  const long long zv = static_cast<long long>(zero_bytes / 16);
   if (x_dtype == PTO_BF16 && out_dtype == PTO_BF16)
-    launch_kernel(rms_norm_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(g), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), gamma, static_cast<__nv_bfloat16*>(out), hidden, eps);
+    launch_kernel(rms_norm_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(g), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), gamma, static_cast<__nv_bfloat16*>(out), hidden, eps, copy_f32, z, zv);
   else if (x_dtype == PTO_FP32 && out_dtype == PTO_BF16)
-    launch_kernel(rms_norm_kernel<float, __nv_bfloat16>, dim3(g), dim3(256), 0, stream, static_cast<const float*>(x), gamma, static_cast<__nv_bfloat16*>(out), hidden, eps);
+    launch_kernel(rms_norm_kernel<float, __nv_bfloat16>, dim3(g), dim3(256), 0, stream, static_cast<const float*>(x), gamma, static_cast<__nv_bfloat16*>(out), hidden, eps, copy_f32, z, zv);
   else if (x_dtype == PTO_FP32 && out_dtype == PTO_FP32)
-    launch_kernel(rms_norm_kernel<float, float>, dim3(g), dim3(256), 0, stream, static_cast<const float*>(x), gamma, static_cast<float*>(out), hidden, eps);
+    launch_kernel(rms_norm_kernel<float, float>, dim3(g), dim3(256), 0, stream, static_cast<const float*>(x), gamma, static_cast<float*>(out), hidden, eps, copy_f32, z, zv);
   else if (x_dtype == PTO_BF16 && out_dtype == PTO_FP32)
-    launch_kernel(rms_norm_kernel<__nv_bfloat16, float>, dim3(g), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), gamma, static_cast<float*>(out), hidden, eps);
+    launch_kernel(rms_norm_kernel<__nv_bfloat16, float>, dim3(g), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), gamma, static_cast<float*>(out), hidden, eps, copy_f32, z, zv);
   else
     return fail(kInvalidArgument, "rms_norm: dtypes must be fp32 or bf16");
   return check_cuda(cudaGetLastError(), "rms_norm_kernel launch");

@@ -48,7 +48,7 @@ int ffn_swiglu_launch(const void* x, const void* w_gate_up, const void* w_down, 
 
 // glue.cu
 int rms_norm_launch(const void* x, int x_dtype, const float* gamma, void* out, int out_dtype, long long rows,
-                    int hidden, float eps, cudaStream_t stream);
+                    int hidden, float eps, float* copy_f32, void* zero, size_t zero_bytes, cudaStream_t stream);
 int rope_kv_append_launch(const float* qkv, const int32_t* seq_lens, const float* cos_t, const float* sin_t,
                           int table_rows, const int32_t* block_table, int max_blocks, void* k_cache, void* v_cache,
                           void* q_out, int batch, int num_heads, int kv_heads, int head_dim, int block_size,

@@ -107,7 +107,7 @@ int op_rms_norm(Worker* w, const pto_task_args* a) {
     return fail(kInvalidArgument, "rms_norm: gamma/out sizes do not match x");
   return rms_norm_launch(tptr(t[0], dtype_bytes(t[0].dtype)), (int)t[0].dtype, static_cast<const float*>(tptr(t[1], 4)),
                          tptr(t[2], dtype_bytes(t[2].dtype)), (int)t[2].dtype, numel(t[0]) / hidden, hidden,
-                         f32_from_bits(a->scalars[0]), w->stream);
+                         f32_from_bits(a->scalars[0]), nullptr, nullptr, 0, w->stream);
 }
 
 // The reference's ffn_swiglu signature (examples/models/01_ffn.py:112-131): all fp32,
@@ -250,7 +250,13 @@ int pto_ffn_swiglu(const void* x, const void* w_gate_up, const void* w_down, voi
 
 int pto_rms_norm(const void* x, int x_dtype, const float* gamma, void* out, int out_dtype, int64_t rows, int hidden,
                  float eps, void* stream) {
-  return pto::rms_norm_launch(x, x_dtype, gamma, out, out_dtype, rows, hidden, eps,
+  return pto::rms_norm_launch(x, x_dtype, gamma, out, out_dtype, rows, hidden, eps, nullptr, nullptr, 0,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int pto_rms_norm_ex(const void* x, int x_dtype, const float* gamma, void* out, int out_dtype, int64_t rows, int hidden,
+                    float eps, float* copy_f32, void* zero, size_t zero_bytes, void* stream) {
+  return pto::rms_norm_launch(x, x_dtype, gamma, out, out_dtype, rows, hidden, eps, copy_f32, zero, zero_bytes,
                               static_cast<cudaStream_t>(stream));
 }
 

@@ -60,15 +60,17 @@ class DecoderLayer:
         """One decode step for ``hidden`` bf16 [batch, H]; the caches are updated in place at
         position seq_len - 1 of every sequence.  Returns bf16 [batch, H]."""
         batch = hidden.shape[0]
-        normed = ops.rms_norm(hidden, self.gamma_in, self.eps, torch.bfloat16)
-        qkv = ops.linear(normed, self.w_qkv)
+        # the input norm also leaves fp32(hidden) as the residual and clears the QKV accumulator
+        resid = torch.empty(hidden.shape, dtype=torch.float32, device=hidden.device)
+        qkv = torch.empty(batch, self.w_qkv.shape[0], dtype=torch.float32, device=hidden.device)
+        normed = ops.rms_norm(hidden, self.gamma_in, self.eps, torch.bfloat16, copy_fp32=resid, zero=qkv)
+        ops.linear(normed, self.w_qkv, out=qkv, accumulate=True)
         q_rot = ops.rope_kv_append(qkv, seq_lens, self.cos, self.sin, block_table, k_cache, v_cache,
                                    num_heads=self.num_heads, kv_heads=self.kv_heads, head_dim=self.head_dim,
                                    block_size=self.block_size)
         attn = ops.paged_attention(q_rot, k_cache, v_cache, block_table, seq_lens, num_heads=self.num_heads,
                                    kv_heads=self.kv_heads, head_dim=self.head_dim, block_size=self.block_size,
                                    scale=self.scale, out_dtype=torch.bfloat16)
-        resid = ops.cast(hidden, torch.float32)
         ops.linear(attn.view(batch, self.num_heads * self.head_dim), self.w_o, out=resid, accumulate=True)
         post = ops.rms_norm(resid, self.gamma_post, self.eps, torch.bfloat16)
         self.ffn(post, out=resid, accumulate=True)   # resid now holds down + resid1

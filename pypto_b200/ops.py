@@ -244,16 +244,32 @@ def ffn_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, o
     return out
 
 
-def rms_norm(x: torch.Tensor, gamma: torch.Tensor | None, eps: float, out_dtype: torch.dtype = torch.bfloat16):
+def rms_norm(x: torch.Tensor, gamma: torch.Tensor | None, eps: float, out_dtype: torch.dtype = torch.bfloat16, *,
+             copy_fp32: torch.Tensor | None = None, zero: torch.Tensor | None = None):
+    """RMSNorm of the rows of x.  Optional side jobs of the same launch: ``copy_fp32`` (fp32, shape of x)
+    receives x unchanged as fp32, ``zero`` (any contiguous tensor whose byte size is a multiple of 16) is
+    cleared."""
     dev = _need_cuda(x) if gamma is None else _need_cuda(x, gamma)
     if gamma is not None and (gamma.dtype != torch.float32 or gamma.numel() != x.shape[-1]):
         raise ValueError("rms_norm: gamma must be fp32 with hidden elements")
     hidden = x.shape[-1]
+    if copy_fp32 is not None:
+        _need_cuda(copy_fp32)
+        if copy_fp32.dtype != torch.float32 or copy_fp32.shape != x.shape or not copy_fp32.is_contiguous():
+            raise ValueError("rms_norm: copy_fp32 must be a contiguous fp32 tensor of the shape of x")
+    zero_bytes = 0
+    if zero is not None:
+        _need_cuda(zero)
+        zero_bytes = zero.numel() * zero.element_size()
+        if not zero.is_contiguous() or zero_bytes % 16 or zero.data_ptr() % 16:
+            raise ValueError("rms_norm: the tensor to clear must be contiguous, 16-byte aligned, a multiple of 16 bytes")
     out = torch.empty(x.shape, dtype=out_dtype, device=dev)
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().pto_rms_norm(x.data_ptr(), dtype_code(x.dtype), gamma.data_ptr() if gamma is not None else None,
-                                            out.data_ptr(), dtype_code(out_dtype), x.numel() // hidden, hidden,
-                                            float(eps), _stream_ptr(dev)))
+        _lib.check(_lib.load().pto_rms_norm_ex(
+            x.data_ptr(), dtype_code(x.dtype), gamma.data_ptr() if gamma is not None else None, out.data_ptr(),
+            dtype_code(out_dtype), x.numel() // hidden, hidden, float(eps),
+            copy_fp32.data_ptr() if copy_fp32 is not None else None, zero.data_ptr() if zero is not None else None,
+            zero_bytes, _stream_ptr(dev)))
     return out
 
 

@@ -80,3 +80,22 @@ def test_decoder_layer_full_size():
     rel = ((got.float() - exp.float()).norm() / exp.float().norm()).item()
     err = (got.float() - exp.float()).abs().max().item()
     assert rel < 1e-2 and err <= 2e-2 * exp.float().abs().max().item(), (rel, err)
+
+
+def test_rms_norm_side_jobs_copy_and_clear():
+    """The fused form gives the same rows as the plain one, leaves x as fp32 in `copy_fp32` and clears `zero`."""
+    ops = _ops()
+    torch.manual_seed(1)
+    x = torch.randn(32, 4096).bfloat16().cuda()
+    gamma = (torch.rand(4096) + 0.5).cuda()
+    plain = ops.rms_norm(x, gamma, 1e-5, torch.bfloat16)
+    copy = torch.full((32, 4096), float("nan"), device="cuda")
+    acc = torch.full((32, 6144), 3.0, device="cuda")
+    fused = ops.rms_norm(x, gamma, 1e-5, torch.bfloat16, copy_fp32=copy, zero=acc)
+    assert torch.equal(fused, plain)
+    assert torch.equal(copy, x.float())
+    assert not acc.any()
+    with pytest.raises(ValueError):
+        ops.rms_norm(x, gamma, 1e-5, torch.bfloat16, copy_fp32=torch.empty(32, 4096, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(ValueError):
+        ops.rms_norm(x, gamma, 1e-5, torch.bfloat16, zero=torch.empty(3, device="cuda"))
