@@ -155,6 +155,42 @@ def test_grouped_fp8_gemms_match_oracle(experts, hidden, inter, rows_per):
         assert (got - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-6
 
 
+def test_expert_gemm_is_reproducible_under_stream_concurrency():
+    """The grouped GEMM has no atomics: repeated launches on the same operands must give identical bits, also
+    while a second stream runs the same kernel (the shared expert does in the layer).  Long K (7168, the
+    four-stage pipeline), many units per CTA and ragged token counts: a pipeline stage recycled too early
+    shows up here as a changed output."""
+    ops = _ops()
+    experts, hidden, inter = 24, 7168, 512
+    g = torch.Generator(device="cuda").manual_seed(7)
+    counts = torch.tensor([0, 481, 3, 128, 129, 257, 64, 0, 300, 17, 255, 1] * 2, dtype=torch.int32)
+    off = torch.cat([torch.zeros(1, dtype=torch.int32), counts.cumsum(0).int()]).cuda()
+    rows = int(counts.sum())
+    w_gu = torch.randn(experts, 2 * inter, hidden, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    s_gu = torch.rand(experts, 2 * inter // 128, hidden // 128, device="cuda", generator=g) * 0.01 + 0.001
+    w_d = torch.randn(experts, hidden, inter, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    s_d = torch.rand(experts, hidden // 128, inter // 128, device="cuda", generator=g) * 0.01 + 0.001
+    x = torch.randn(rows, hidden, device="cuda", generator=g).bfloat16()
+    xq, xs = ops.quantize_rows(x)
+    side = torch.cuda.Stream()
+    first_a = first_y = None
+    for _ in range(12):
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ops.moe_expert_gemm(True, w_gu[:1], s_gu[:1], xq, xs, torch.tensor([0, rows], dtype=torch.int32, device="cuda"))
+        a = ops.moe_expert_gemm(True, w_gu, s_gu, xq, xs, off)
+        aq, asc = ops.quantize_rows(a)
+        y = ops.moe_expert_gemm(False, w_d, s_d, aq, asc, off, None)
+        torch.cuda.current_stream().wait_stream(side)
+        if first_a is None:
+            first_a, first_y = a.clone(), y.clone()
+        else:
+            assert torch.equal(a, first_a) and torch.equal(y, first_y)
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    assert torch.isfinite(first_y.float()).all()
+
+
 def _layer_vs_oracle(tokens, hidden, inter, experts, topk, seed):
     from pypto_b200.moe import MoELayer
     m = oracle.inputs.moe_inputs(tokens=tokens, hidden=hidden, inter=inter, n_experts=experts, topk=topk, seed=seed)
