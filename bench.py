@@ -49,10 +49,15 @@ MOE = dict(tokens=4096, hidden=7168, inter=2048, n_experts=256, topk=8)
 # dram bytes (read + write) of one launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None where no capture exists yet)
 NCU_TRAFFIC = {"decode": 1406460304,   # pa_decode_kernel<1>, profiles/pa_decode_kernel_decode_batch64_ctx1k-8k.md
-               "verify": None,
-               "ffn": None,
+               "verify": None,         # scaled from a batch-16 capture, see VERIFY_TRAFFIC_PER_KV_BYTE
+               "ffn": 17104384 + 10026752,   # the two gemm_bf16_kernel launches of a step (gate/up + SwiGLU 17.1 MB, down 10.0 MB)
                "layer": 243135232,     # gate/up gemm_bf16_kernel launch (235.4 MB read + 7.7 MB written), profiles/gemm_bf16_*.md
                "moe": 499609856 * 16}  # gate/up moe_gemm_fp8_kernel: 489.7 MB read + 9.9 MB written on the 16-expert capture, x16 for 256 experts
+
+
+# pa_decode_kernel<2> on `--workload verify --small` (batch 16): 1.2221 GB read + 12.4 MB written for 1.2157 GB of
+# K/V that the step must read; traffic grows in proportion to the K/V bytes, so a full launch is scaled by them.
+VERIFY_TRAFFIC_PER_KV_BYTE = (1222118000 + 12380416) / 1215746048
 
 
 def peaks():
@@ -375,7 +380,9 @@ def run_attention(args, d: Dist, which: str):
              config={"workload": desc, "l2": "inputs larger than L2", "kv_bytes_per_step_per_gpu": kv_b},
              launches=2 * args.steps, clocks=clocks,
              roofline={"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
-                       "frac": achieved / pk["hbm"], "traffic": NCU_TRAFFIC[which], "peak_source": pk["source"],
+                       "frac": achieved / pk["hbm"],
+                       "traffic": NCU_TRAFFIC[which] if which == "decode" else int(VERIFY_TRAFFIC_PER_KV_BYTE * kv_b),
+                       "peak_source": pk["source"],
                        "note": "algorithmic bytes of one step / CUDA-event time of the step (pa_decode_kernel + "
                                "pa_merge_kernel), rank 0"},
              cpu_baseline=cpu, e2e=e2e, extra={"tokens_per_s": tot_seq * g["q_len"] / sec})
