@@ -15,8 +15,10 @@ includes, loaded into the worker (``pto_register_kernel_image``) and launched wi
 SPMD block (``pto_run_kernel``).
 
 The orchestration that calls the stubs is not lowered: its body must be a plain sequence of
-calls to external functions, each optionally under ``with pl.spmd(core_num=N):``, with entry
-parameters, results of earlier calls or constants as arguments.  Anything else is refused.
+calls, each optionally under ``with pl.spmd(core_num=N):``, with entry parameters, results of
+earlier calls or constants as arguments.  A callee is either an external function or a function
+whose name and parameter list are in the fused-operator table (``fused_programs``), so one
+orchestration can chain hand-written kernels and fused operators.  Anything else is refused.
 """
 
 from __future__ import annotations
@@ -129,19 +131,23 @@ def encode_scalar(value, ptype) -> int:
 
 
 class _Step:
-    def __init__(self, fn: Function, block_num: int, bindings: list):
+    def __init__(self, fn: Function, block_num: int, bindings: list, fused=None):
         self.fn, self.block_num, self.bindings = fn, block_num, bindings   # ("param", name) | ("const", value)
         self.threads = int(fn.attrs.get("threads_per_block", 128))
+        self.fused = fused            # a FusedOp when the callee is in the fused-operator table, else None
+
+    def bind(self, values: dict) -> dict:
+        """The callee's view of a {entry parameter: value} mapping."""
+        return {p.name: (values[v] if kind == "param" else v) for p, (kind, v) in zip(self.fn.params, self.bindings)}
 
 
 class ExternProgramOp(FusedOp):
-    """A program whose orchestration only dispatches external kernels."""
-
-    op_names: tuple[str, ...] = ()
+    """A program whose orchestration is a sequence of external kernels and fused operators."""
 
     def __init__(self, entry: Function, steps: list[_Step]):
         self.entry, self.steps = entry, steps
         self._images: dict[int, bytes] = {}
+        self.op_names = tuple(dict.fromkeys(n for s in steps if s.fused is not None for n in s.fused.op_names))
 
     def matches(self, entry) -> bool:
         return entry is self.entry
@@ -153,17 +159,34 @@ class ExternProgramOp(FusedOp):
         return img
 
     def plan(self, compiled, host, worker):
-        return dict(cids=[worker.register_kernel_image(self.image(s), ENTRY_SYMBOL) for s in self.steps])
+        plans, replace, host_only = [], {}, []
+        for s in self.steps:
+            if s.fused is None:
+                plans.append(worker.register_kernel_image(self.image(s), ENTRY_SYMBOL))
+                continue
+            sub = s.fused.plan(compiled, s.bind(host), worker)
+            to_entry = {p.name: v for p, (kind, v) in zip(s.fn.params, s.bindings) if kind == "param"}
+            for name, value in sub.get("replace", {}).items():
+                replace[to_entry[name]] = value
+            host_only += [to_entry[n] for n in sub.get("host_only", ()) if n in to_entry]
+            plans.append(sub)
+        # a tensor that one step only reads on the host may still be a device operand of another step
+        used_on_device = {v for s in self.steps if s.fused is None
+                          for p, (kind, v) in zip(s.fn.params, s.bindings) if p.is_tensor}
+        return dict(steps=plans, replace=replace, host_only=tuple(n for n in host_only if n not in used_on_device))
 
     def launch(self, worker, dev, host, plan):
-        for step, cid in zip(self.steps, plan["cids"]):
+        for step, sp in zip(self.steps, plan["steps"]):
+            if step.fused is not None:
+                step.fused.launch(worker, step.bind(dev), step.bind(host), sp)
+                continue
             tensors, scalars = [], []
             for p, (kind, v) in zip(step.fn.params, step.bindings):
                 if p.is_tensor:
                     tensors.append(dev[v])
                 else:
                     scalars.append(encode_scalar(host[v] if kind == "param" else v, p.type))
-            worker.launch_kernel(cid, tensors, scalars, block_num=step.block_num, threads_per_block=step.threads)
+            worker.launch_kernel(sp, tensors, scalars, block_num=step.block_num, threads_per_block=step.threads)
 
 
 class _Refused(Exception):
@@ -220,11 +243,19 @@ def match(entry: Function, program=None) -> ExternProgramOp | None:
     def call(node, block_num, target):
         nonlocal saw_extern
         fn = callee(node.func)
-        if fn is None or not (fn.attrs.get("external_source") or fn.attrs.get("external_aiv_source")):
-            raise _Refused(f"call to '{ast.unparse(node.func)}' is not an external kernel")
+        if fn is None:
+            raise _Refused(f"call to '{ast.unparse(node.func)}' is neither an external kernel nor a fused operator")
+        fused = None
+        if fn.attrs.get("external_source") or fn.attrs.get("external_aiv_source"):
+            if fn.attrs.get("core_type") not in (None, "aiv", "aic"):
+                raise _Refused(f"core_type {fn.attrs.get('core_type')!r}: only single-kernel stubs are supported")
+        else:
+            from . import fused_programs
+            try:
+                fused = fused_programs.lookup(fn)
+            except NotImplementedError:
+                raise _Refused(f"call to '{fn.name}' is neither an external kernel nor a fused operator") from None
         saw_extern = True
-        if fn.attrs.get("core_type") not in (None, "aiv", "aic"):
-            raise _Refused(f"core_type {fn.attrs.get('core_type')!r}: only single-kernel stubs are supported")
         if node.keywords or len(node.args) != len(fn.params):
             raise _Refused(f"'{fn.name}' takes {len(fn.params)} positional arguments")
         bindings, result = [], None
@@ -244,7 +275,7 @@ def match(entry: Function, program=None) -> ExternProgramOp | None:
             if result is None:
                 raise _Refused(f"'{fn.name}' has no output tensor to bind '{target}' to")
             alias[target] = result
-        steps.append(_Step(fn, block_num, bindings))
+        steps.append(_Step(fn, block_num, bindings, fused))
 
     def statement(st, block_num):
         if isinstance(st, ast.Expr) and isinstance(st.value, ast.Constant):
@@ -277,7 +308,8 @@ def match(entry: Function, program=None) -> ExternProgramOp | None:
     except _Refused as e:
         if saw_extern or any(f.attrs.get("external_source") for f in functions.values()):
             raise NotImplementedError(f"program entry '{entry.name}' uses external kernels, but {e}; this front end "
-                                      "follows orchestrations that are plain sequences of external-kernel calls") from None
+                                      "follows orchestrations that are plain sequences of external-kernel calls "
+                                      "and fused-operator calls") from None
         return None
     if not steps:
         return None

@@ -89,6 +89,36 @@ def test_compile_errors_carry_the_compiler_output(tmp_path, monkeypatch):
         ek.compile_cuda(tmp_path / "missing.cu")
 
 
+@pl.program
+class NormThenAxpy:
+    """A fused operator of the table (rms_norm(x, gamma, output)) followed by an external kernel."""
+
+    @pl.function(type=pl.FunctionType.InCore)
+    def rms_norm(self, x: pl.Tensor[[32, 64], pl.FP32], gamma: pl.Tensor[[1, 64], pl.FP32],
+                 output: pl.Out[pl.Tensor[[32, 64], pl.FP32]]) -> pl.Tensor[[32, 64], pl.FP32]: ...
+
+    @pl.function(type=pl.FunctionType.AIV, external_source=KERNELS / "axpy.cu")
+    def axpy(self, x: pl.Tensor[[32, 64], pl.FP32], y: pl.InOut[pl.Tensor[[32, 64], pl.FP32]],
+             alpha: pl.Scalar[pl.FP32]) -> pl.Tensor[[32, 64], pl.FP32]: ...
+
+    @pl.function(type=pl.FunctionType.Orchestration)
+    def main(self, x: pl.Tensor[[32, 64], pl.FP32], gamma: pl.Tensor[[1, 64], pl.FP32],
+             normed: pl.Out[pl.Tensor[[32, 64], pl.FP32]], y: pl.InOut[pl.Tensor[[32, 64], pl.FP32]]):
+        normed = self.rms_norm(x, gamma, normed)
+        with pl.spmd(core_num=4):
+            y = self.axpy(normed, y, 2.0)
+        return y
+
+
+def test_fused_operators_and_external_kernels_chain_in_one_orchestration():
+    compiled = ir.compile(NormThenAxpy, platform="b200")
+    first, second = compiled.fused.steps
+    assert first.fused is not None and first.fused.op_names == ("rms_norm",) and second.fused is None
+    assert first.bindings == [("param", "x"), ("param", "gamma"), ("param", "normed")]
+    assert second.bindings == [("param", "normed"), ("param", "y"), ("const", 2.0)] and second.block_num == 4
+    assert compiled.op_names == ("rms_norm",)
+
+
 def test_orchestrations_the_front_end_does_not_follow_are_refused():
     @pl.program
     class Mixed:

@@ -12,7 +12,7 @@ import pypto_b200.language as pl
 from pypto_b200 import _lib, ir
 from pypto_b200.runtime import ChipWorker, RunConfig, run
 from pypto_b200.runtime import extern_kernel as ek
-from test_extern_kernel import (_BASE_CL, _CORE_NUM, _FLOATS_PER_CACHE_LINE, _KERNEL, _TOTAL,
+from test_extern_kernel import (_BASE_CL, _CORE_NUM, _FLOATS_PER_CACHE_LINE, _KERNEL, _TOTAL, NormThenAxpy,
                                 SpmdWriteExternProgram)
 
 pytestmark = pytest.mark.gpu
@@ -50,6 +50,18 @@ def test_jit_extern_with_two_tensors_and_a_float_scalar():
     entry(x, y, 2.5, config=RunConfig(platform="b200"))
     assert torch.equal(y, want)                 # the fixture rounds product and sum separately, as torch does
     assert len(entry._cache) == 1
+
+
+def test_fused_operator_then_external_kernel_in_one_program():
+    from oracle import layer as olayer
+    g = torch.Generator().manual_seed(2)
+    x, gamma = torch.randn(32, 64, generator=g), torch.rand(1, 64, generator=g) + 0.5
+    y0 = torch.randn(32, 64, generator=g)
+    normed, y = torch.zeros(32, 64), y0.clone()
+    run(NormThenAxpy, x, gamma, normed, y, config=RunConfig(platform="b200"))
+    want_norm = olayer.rms_norm_sqrt_div(x, gamma, 1e-5)
+    assert torch.allclose(normed, want_norm, rtol=1e-5, atol=1e-5)
+    assert torch.equal(y, 2.0 * normed + y0)
 
 
 def test_resident_tensors_and_registered_handle():
