@@ -17,7 +17,9 @@ import struct
 
 import torch
 
-REFERENCE_ROOT = os.environ.get("PYPTO_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: $PYPTO_REFERENCE_ROOT, else a directory named "reference" beside this repository
+REFERENCE_ROOT = os.environ.get("PYPTO_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))), "reference")
 
 
 def available() -> bool:
