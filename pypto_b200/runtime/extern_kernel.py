@@ -178,7 +178,7 @@ class ExternProgramOp(FusedOp):
     def launch(self, worker, dev, host, plan):
         for step, sp in zip(self.steps, plan["steps"]):
             if step.fused is not None:
-                step.fused.launch(worker, step.bind(dev), step.bind(host), sp)
+                step.fused.launch(worker, step.bind({**host, **dev}), step.bind(host), sp)   # scalars come from the host side
                 continue
             tensors, scalars = [], []
             for p, (kind, v) in zip(step.fn.params, step.bindings):
