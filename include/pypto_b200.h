@@ -91,8 +91,10 @@ PTO_API int pto_copy_from(pto_worker* w, void* dst_host, uint64_t src_dev, size_
 PTO_API int pto_synchronize(pto_worker* w);
 PTO_API void* pto_worker_stream(pto_worker* w);
 /* Reads and clears the device error word of the worker's scratch arena:
- * out[0] code (0 none, 1 barrier timeout, 2 block id outside the pool), out[1] site,
- * out[2] CTA, out[3] detail.  Synchronises the worker's stream. */
+ * out[0] code (0 none, 1 a bounded wait ran out, 2 block id outside the pool, 3 an index or row count
+ * outside its array: the kernel skipped the access), out[1] site, out[2] CTA, out[3] detail.
+ * Synchronises the worker's stream.  Returns PTO_DEVICE_TIMEOUT for code 1 and PTO_INVALID_ARGUMENT
+ * for codes 2 and 3 (out is filled either way). */
 PTO_API int pto_device_status(pto_worker* w, int32_t out[4]);
 /* The worker's scratch arena (grown on demand, never shrunk). */
 PTO_API int pto_worker_scratch(pto_worker* w, size_t min_bytes, uint64_t* dev_ptr, size_t* nbytes);
@@ -255,16 +257,42 @@ PTO_API int pto_quantize_rows(const void* x, int x_dtype, void* q, float* scale,
 /* Dispatch plan (dispatch_step, tests/st/distributed/test_l3_ep_dispatch_combine.py:104-299):
  * bucket of route r is expert_of[r]; inside a bucket routes keep ascending r = t * TOPK + k.
  * Outputs: counts [buckets], offsets [buckets + 1], pos [routes] (slot of each route in the
- * bucket-sorted order), route_at [routes] (inverse).  rank_tmp: int32 [routes] work array. */
+ * bucket-sorted order), route_at [routes] (inverse).  rank_tmp: int32 [routes] work array.
+ * An expert id outside [0, buckets) is not dereferenced: the route gets pos = -1, the unused
+ * tail of route_at is set to -1 and `err` (device int32[4], may be NULL) receives code 3. */
 PTO_API int pto_moe_dispatch_plan(const int32_t* expert_of, int routes, int buckets, int32_t* counts,
                                   int32_t* offsets, int32_t* pos, int32_t* route_at, int32_t* rank_tmp,
-                                  void* stream);
+                                  int32_t* err, void* stream);
+
+/* Receiver side of dispatch_step (:184-218): rows arrive source-major and, inside a source, ordered
+ * by local expert; recv_counts int32 [world, local_experts] says how many.  Outputs: counts
+ * [local_experts]; offsets [local_experts + 1] (dense when slot_stride = 0, e * slot_stride for the
+ * reference's padded [L, R] receive layout); arrival_of [capacity] (grouped row -> arrival row, -1
+ * where nothing arrives); grouped_of [capacity] (arrival row -> grouped row).  Inside an expert rows
+ * are ordered by source rank, then arrival order -- the reference's slot order. */
+PTO_API int pto_moe_recv_plan(const int32_t* recv_counts, int world, int local_experts, int slot_stride,
+                              int capacity, int32_t* counts, int32_t* offsets, int32_t* arrival_of,
+                              int32_t* grouped_of, int32_t* err, void* stream);
 
 /* dst_i[p, :] = src_i[index[p] / div, :] for up to 3 byte arrays with row sizes row_bytes[i]
- * (index NULL: identity).  Bit-exact row copies (the payload move of dispatch_step). */
+ * (index NULL: identity).  Bit-exact row copies (the payload move of dispatch_step).  index -1 clears
+ * the destination row; any other source row outside [0, src_rows) clears it and sets code 3 in `err`.
+ * pto_moe_move_rows is the same with a row stride per source and destination array (NULL = packed),
+ * which packs several arrays side by side into one payload row and takes them apart again. */
 PTO_API int pto_moe_gather_rows(const void* const* src, void* const* dst, const int* row_bytes, int n_arrays,
-                                const int32_t* index, int div, int64_t rows, void* stream);
-PTO_API int pto_moe_gather_f32(const float* src, const int32_t* index, int64_t n, float* dst, void* stream);
+                                const int32_t* index, int div, int64_t rows, int64_t src_rows, int32_t* err,
+                                void* stream);
+PTO_API int pto_moe_move_rows(const void* const* src, const int64_t* src_stride, void* const* dst,
+                              const int64_t* dst_stride, const int* row_bytes, int n_arrays, const int32_t* index,
+                              int div, int64_t rows, int64_t src_rows, int32_t* err, void* stream);
+PTO_API int pto_moe_gather_f32(const float* src, const int32_t* index, int64_t n, int64_t n_src, float* dst,
+                               int32_t* err, void* stream);
+
+/* y[r, :] = bf16(fp32(x[r, :]) * w[r * w_stride]) over bf16 rows: the stand-in expert of the reference's
+ * expert-parallel test (local_expert_step, test_l3_ep_dispatch_combine.py:309-327).  With `count`
+ * (int32 [rows / slot_stride]) only the first count[e] rows of each block of slot_stride rows are written. */
+PTO_API int pto_scale_rows(const void* x, const float* w, int w_stride, const int32_t* count, int slot_stride,
+                           int64_t rows, int cols, void* y, void* stream);
 
 /* Grouped FP8 expert GEMM over tokens sorted by expert (replaces local_expert_step,
  * test_l3_ep_dispatch_combine.py:309-327, by the SwiGLU expert FFN).
@@ -278,9 +306,56 @@ PTO_API int pto_moe_expert_gemm(int swiglu, const void* w, const float* w_scale,
                                 int rows, const float* route_w, void* out, int32_t* err, void* stream);
 
 /* Combine (combine_step, test_l3_ep_dispatch_combine.py:337-402): y[t] = sum_k fp32(rows[pos[t*topk+k]])
- * (+ fp32(shared[t]) if given), k ascending; written as bf16 (y_bf16) and/or fp32 (y_f32). */
+ * (+ fp32(shared[t]) if given), k ascending; written as bf16 (y_bf16) and/or fp32 (y_f32).  `rows` holds
+ * n_rows bf16 rows; a pos outside [0, n_rows) contributes nothing. */
 PTO_API int pto_moe_combine(const void* rows, const int32_t* pos, const void* shared, int tokens, int topk,
-                            int hidden, void* y_bf16, float* y_f32, void* stream);
+                            int hidden, int64_t n_rows, void* y_bf16, float* y_f32, void* stream);
+
+/* ---- MX block-scaled FP8 matmul ---- */
+
+/* out[m, n] = (acc_in[m, n] +) sum_k a[m, k] * 2^(sa[m, k/32] - 127) * b[k, n] * 2^(sb[k/32, n] - 127).
+ * Replaces tile.matmul_mx / tile.matmul_mx_acc (src/ir/op/tile_ops/matmul_mx.cpp:321-345; golden
+ * tests/st/runtime/ops/test_matmul_mx.py:119-131) on the hardware block-scaled path
+ * (tcgen05.mma kind::mxf8f6f4.block_scale, E8M0 scales staged in tensor memory).
+ *   a          e4m3 [m, k] row-major; k a multiple of 32
+ *   b_t        e4m3 [n, k]: the right operand with K contiguous (pto_transpose_u8 of the
+ *              reference's [k, n] tensor, done once for a resident weight)
+ *   a_scale    E8M0 codes, uint8 [m, k/32]; b_scale uint8 [k/32, n]
+ *   *_layout   PTO_MX_SCALE_LOGICAL (row-major as written above), PTO_MX_SCALE_A_ZZ / PTO_MX_SCALE_B_NN:
+ *              the physical orders the reference hands its kernel (test_matmul_mx.py:38-101;
+ *              these need m, n multiples of 16 and k/32 even)
+ *   acc_in     fp32 [m, n] added to the product (matmul_mx_acc), or NULL; may alias out
+ *   out        fp32 [m, n] */
+enum { PTO_MX_SCALE_LOGICAL = 0, PTO_MX_SCALE_A_ZZ = 1, PTO_MX_SCALE_B_NN = 2 };
+PTO_API int pto_matmul_mx(const void* a, const void* a_scale, int a_scale_layout, const void* b_t,
+                          const void* b_scale, int b_scale_layout, const float* acc_in, float* out, int m, int n,
+                          int k, int32_t* err, void* stream);
+/* dst[c, r] = src[r, c] for a byte matrix src [rows, cols] (operand re-layout for pto_matmul_mx). */
+PTO_API int pto_transpose_u8(const void* src, void* dst, int64_t rows, int64_t cols, void* stream);
+
+/* ---- communicator: one rank per GPU, NCCL over NVLink ---- */
+
+/* Replaces the communication-domain set-up of the reference's level-3 runtime and its all_to_all /
+ * all_to_all_v builtins (python/pypto/runtime/builtins/collectives/all_to_all_v/templates/
+ * kernel.cpp.in:96-160; DistributedWorker, python/pypto/runtime/distributed_runner.py:1442).
+ * One process (or thread) per GPU creates one communicator; rank 0 makes the 128-byte id with
+ * pto_comm_unique_id and hands it to the others by any host channel.  pto_comm_init is collective:
+ * every rank must call it.  NCCL is looked up at run time; without it these return PTO_UNSUPPORTED. */
+#define PTO_UNIQUE_ID_BYTES 128
+typedef struct pto_comm pto_comm;
+PTO_API int pto_comm_unique_id(void* id_out);
+PTO_API int pto_comm_init(int rank, int nranks, const void* unique_id, int device_id, pto_comm** out);
+PTO_API int pto_comm_destroy(pto_comm* c); /* idempotent on NULL */
+PTO_API int pto_comm_rank(const pto_comm* c);
+PTO_API int pto_comm_size(const pto_comm* c);
+PTO_API int pto_comm_nccl_version(void);   /* 0 when NCCL could not be loaded */
+/* Rank r's block p of `send` (bytes_per_rank each) lands in rank p's block r of `recv`. */
+PTO_API int pto_all_to_all(pto_comm* c, const void* send, void* recv, size_t bytes_per_rank, void* stream);
+/* This rank sends send_rows[p] consecutive rows of `send` to rank p and receives recv_rows[p] rows from
+ * rank p, stored in source-rank order in `recv`; exact counts (host arrays of nranks entries, typically
+ * from a pto_all_to_all of the counts).  Rows for this rank itself are a device copy. */
+PTO_API int pto_all_to_all_v(pto_comm* c, const void* send, const int64_t* send_rows, void* recv,
+                             const int64_t* recv_rows, size_t row_bytes, void* stream);
 
 #ifdef __cplusplus
 }

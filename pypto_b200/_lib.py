@@ -74,11 +74,25 @@ SIGNATURES = {
     "pto_swiglu_act": (_i, [_p, _p, _i64, _i, _p]),
     "pto_moe_topk": (_i, [_p, _p, _i, _i, _i, _i, _p, _p, _p]),
     "pto_quantize_rows": (_i, [_p, _i, _p, _p, _i64, _i, _p]),
-    "pto_moe_dispatch_plan": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p]),
-    "pto_moe_gather_rows": (_i, [C.POINTER(_p), C.POINTER(_p), C.POINTER(_i), _i, _p, _i, _i64, _p]),
-    "pto_moe_gather_f32": (_i, [_p, _p, _i64, _p, _p]),
+    "pto_moe_dispatch_plan": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p, _p]),
+    "pto_moe_recv_plan": (_i, [_p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
+    "pto_moe_gather_rows": (_i, [C.POINTER(_p), C.POINTER(_p), C.POINTER(_i), _i, _p, _i, _i64, _i64, _p, _p]),
+    "pto_moe_move_rows": (_i, [C.POINTER(_p), C.POINTER(_i64), C.POINTER(_p), C.POINTER(_i64), C.POINTER(_i), _i, _p,
+                               _i, _i64, _i64, _p, _p]),
+    "pto_moe_gather_f32": (_i, [_p, _p, _i64, _i64, _p, _p, _p]),
+    "pto_scale_rows": (_i, [_p, _p, _i, _p, _i, _i64, _i, _p, _p]),
     "pto_moe_expert_gemm": (_i, [_i, _p, _p, _i, _i, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p]),
-    "pto_moe_combine": (_i, [_p, _p, _p, _i, _i, _i, _p, _p, _p]),
+    "pto_moe_combine": (_i, [_p, _p, _p, _i, _i, _i, _i64, _p, _p, _p]),
+    "pto_matmul_mx": (_i, [_p, _p, _i, _p, _p, _i, _p, _p, _i, _i, _i, _p, _p]),
+    "pto_transpose_u8": (_i, [_p, _p, _i64, _i64, _p]),
+    "pto_comm_unique_id": (_i, [_p]),
+    "pto_comm_init": (_i, [_i, _i, _p, _i, C.POINTER(_p)]),
+    "pto_comm_destroy": (_i, [_p]),
+    "pto_comm_rank": (_i, [_p]),
+    "pto_comm_size": (_i, [_p]),
+    "pto_comm_nccl_version": (_i, []),
+    "pto_all_to_all": (_i, [_p, _p, _p, _sz, _p]),
+    "pto_all_to_all_v": (_i, [_p, _p, C.POINTER(_i64), _p, C.POINTER(_i64), _sz, _p]),
     "pto_paged_gather": (_i, [_p, _i64, _i64, _i, _p, _i64, _p, _i64, _i, _i64, _i64, _p, _p, _p]),
 }
 

@@ -63,16 +63,29 @@ int moe_topk_launch(const float* scores, const float* bias, int is_logits, int t
 int quantize_rows_launch(const void* x, int x_dtype, void* q, float* scale, long long rows, int cols,
                          cudaStream_t stream);
 int moe_dispatch_plan_launch(const int32_t* expert_of, int routes, int buckets, int32_t* counts, int32_t* offsets,
-                             int32_t* pos, int32_t* route_at, int32_t* rank_tmp, cudaStream_t stream);
-int moe_gather_rows_launch(const void* const* src, void* const* dst, const int* row_bytes, int n_arrays,
-                           const int32_t* src_row_of, int div, long long rows, cudaStream_t stream);
-int moe_gather_f32_launch(const float* src, const int32_t* index, long long n, float* dst, cudaStream_t stream);
+                             int32_t* pos, int32_t* route_at, int32_t* rank_tmp, int* err, cudaStream_t stream);
+int moe_recv_plan_launch(const int32_t* recv_counts, int world, int local_experts, int slot_stride, int capacity,
+                         int32_t* counts, int32_t* offsets, int32_t* arrival_of, int32_t* grouped_of, int* err,
+                         cudaStream_t stream);
+int moe_move_rows_launch(const void* const* src, const long long* src_stride, void* const* dst,
+                         const long long* dst_stride, const int* row_bytes, int n_arrays, const int32_t* src_row_of,
+                         int div, long long rows, long long src_rows, int* err, cudaStream_t stream);
+int scale_rows_launch(const void* x, const float* w, int w_stride, const int32_t* count, int slot_stride,
+                      long long rows, int cols, void* y, cudaStream_t stream);
+int moe_gather_f32_launch(const float* src, const int32_t* index, long long n, long long n_src, float* dst, int* err,
+                          cudaStream_t stream);
 int moe_combine_launch(const void* rows, const int32_t* pos, const void* shared, int tokens, int topk, int hidden,
-                       void* y_bf16, float* y_f32, cudaStream_t stream);
+                       long long n_rows, void* y_bf16, float* y_f32, cudaStream_t stream);
 
 // moe_gemm.cu
 int moe_gemm_fp8_launch(int swiglu, const void* w, const float* w_scale, int experts, int w_rows_per_expert,
                         int n_out, int k, const void* x, const float* x_scale, const int32_t* offsets,
                         int total_rows, const float* route_w, void* out, int* err, cudaStream_t stream);
+
+// matmul_mx.cu
+int matmul_mx_launch(const void* a, const void* a_scale, int a_scale_layout, const void* b_t, const void* b_scale,
+                     int b_scale_layout, const float* acc_in, float* out, int m, int n, int k, int* err,
+                     cudaStream_t stream);
+int transpose_u8_launch(const void* src, void* dst, long long rows, long long cols, cudaStream_t stream);
 
 }  // namespace pto

@@ -1,0 +1,367 @@
+// MX block-scaled FP8 matmul on the hardware block-scaling path of the 5th-generation tensor cores.
+//
+//   out[m, n] = (acc_in[m, n] +) sum_k a[m, k] * 2^(sa[m, k/32] - 127) * b[k, n] * 2^(sb[k/32, n] - 127)
+//
+// It stands where the reference lowers tile.matmul_mx / tile.matmul_mx_acc to the MX cube
+// instruction of its 950 target (src/ir/op/tile_ops/matmul_mx.cpp:321-345; numerics
+// tests/st/runtime/ops/test_matmul_mx.py:119-131: dequantise per 32-wide K group, exact product).
+// The same format is native here: `tcgen05.mma.kind::mxf8f6f4.block_scale` multiplies every 32-wide
+// K group by one E8M0 scale per operand row, read from tensor memory, so no scale arithmetic runs on
+// the CUDA cores.
+//
+// Operands: a e4m3 [m, k] and b_t e4m3 [n, k], both K-major, brought in by TMA with the 128-byte
+// swizzle, 128 K bytes per pipeline stage (four MMAs of K = 32).  Scales: one byte per (row, K group).
+// The tensor core wants the four scale bytes of a row for one stage in one 32-bit tensor-memory cell,
+// rows 32 apart in neighbouring columns:
+//     chunk byte offset of (row r, group g of the stage) = (r % 32) * 16 + (r / 32) * 4 + g
+// for every 128 rows (512 bytes).  Scale-loader warps build those chunks in shared memory from the
+// caller's layout (row-major, or the reference's MX_A_ZZ / MX_B_NN physical orders,
+// test_matmul_mx.py:38-101); the MMA thread moves a chunk to tensor memory with
+// `tcgen05.cp.32x128b.warpx4` and selects the byte with the scale-id field of the instruction.
+//
+// CTA = warp 0 TMA producer, warp 1 MMA issuer (owns tensor memory), warps 2-5 epilogue (one
+// TMEM lane quarter each), warps 6-9 scale loaders.  Tiles of 128 x bn outputs (bn = 128 with two
+// accumulator buffers, or 256 with one) are taken round-robin by persistent CTAs.  Every wait is bounded.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace pto {
+namespace {
+
+constexpr int kMxThreads = 320;
+constexpr int kMxScaleWarps = 4;
+constexpr int kMxMaxStages = 8;
+constexpr int kMxBK = 128;           // K bytes per stage = 4 scale groups
+
+struct MxParams {
+  int m, n, k;
+  int m_tiles, n_tiles, kblocks, kgroups;
+  int bn, nbuf, stages;
+  const uint8_t* a_scale;
+  const uint8_t* b_scale;
+  int a_layout, b_layout;
+  const float* acc_in;
+  float* out;
+  int* err;
+};
+
+// E8M0 code of (row, K group) of the left operand; 127 (= 1.0) outside the matrix.
+__device__ __forceinline__ uint32_t a_scale_code(const MxParams& p, int row, int g) {
+  if (row >= p.m || g >= p.kgroups) return 127u;
+  if (p.a_layout == PTO_MX_SCALE_A_ZZ)   // [m/16][kg/2][16][2]
+    return p.a_scale[(static_cast<size_t>(row >> 4) * (p.kgroups >> 1) + (g >> 1)) * 32 + (row & 15) * 2 + (g & 1)];
+  return p.a_scale[static_cast<size_t>(row) * p.kgroups + g];
+}
+// E8M0 code of (K group, column) of the right operand.
+__device__ __forceinline__ uint32_t b_scale_code(const MxParams& p, int col, int g) {
+  if (col >= p.n || g >= p.kgroups) return 127u;
+  if (p.b_layout == PTO_MX_SCALE_B_NN)   // [n/16][kg/2][16][2]
+    return p.b_scale[(static_cast<size_t>(col >> 4) * (p.kgroups >> 1) + (g >> 1)) * 32 + (col & 15) * 2 + (g & 1)];
+  return p.b_scale[static_cast<size_t>(g) * p.n + col];
+}
+
+// Shared-memory descriptor of one 512-byte scale chunk for tcgen05.cp: 32 rows of 16 bytes, no swizzle,
+// 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;   // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;          // descriptor version (sm_100)
+  return d;
+}
+
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+
+// Block-scaled instruction descriptor: e4m3 x e4m3, K-major, E8M0 scales, M x N, scale byte ids.
+__device__ __forceinline__ uint32_t mx_idesc(uint32_t m, uint32_t n, uint32_t a_sf_id, uint32_t b_sf_id) {
+  return (b_sf_id << 4) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (a_sf_id << 29);
+}
+
+__device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate, uint32_t tsfa, uint32_t tsfb) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kMxThreads, 1)
+matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const MxParams p) {
+  pdl_launch_dependents();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t a_bytes = 128 * kMxBK, b_bytes = static_cast<uint32_t>(p.bn) * kMxBK;
+  const uint32_t sfb_chunks = p.bn / 128;
+  const uint32_t sf_bytes = 512 * (1 + sfb_chunks);
+  const uint32_t stage_bytes = a_bytes + b_bytes + 1024 * ((sf_bytes + 1023) / 1024);   // keeps stages 1024-aligned
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
+  uint64_t* empty = full + kMxMaxStages;
+  uint64_t* tmem_full = empty + kMxMaxStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint64_t* drain = tmem_empty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t tmem_cols = 512;
+  // accumulators in columns [0, nbuf * bn); two sets of scale columns after them (K blocks alternate)
+  const uint32_t sf_col0 = static_cast<uint32_t>(p.nbuf * p.bn);
+  const uint32_t sf_set = 4 + 4 * sfb_chunks;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < p.stages; ++i) {
+      mbar_init(&full[i], 1 + kMxScaleWarps);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);
+    }
+    mbar_init(drain, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+  const int tiles = p.m_tiles * p.n_tiles;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const uint32_t s = it % p.stages, round = it / p.stages;
+          if (!mbar_wait(&empty[s], (round & 1u) ^ 1u)) {
+            report_error(p.err, kErrBarrierTimeout, 70, static_cast<int>(it));
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
+          mbar_arrive_expect_tx(&full[s], a_bytes + b_bytes);
+          tma_load_2d(st, &tm_a, kb * kMxBK, mt * 128, &full[s]);          // past m or k the box is zero filled
+          for (uint32_t c = 0; c < sfb_chunks; ++c)
+            tma_load_2d(st + a_bytes + c * (128 * kMxBK), &tm_b, kb * kMxBK, nt * p.bn + c * 128, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      uint32_t it = 0, ui = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++ui) {
+        const uint32_t ab = ui % p.nbuf;
+        if (!mbar_wait(&tmem_empty[ab], ((ui / p.nbuf) & 1u) ^ 1u)) {
+          report_error(p.err, kErrBarrierTimeout, 71, static_cast<int>(ui));
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d0 = tmem_base + ab * p.bn;
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const uint32_t s = it % p.stages, round = it / p.stages;
+          if (!mbar_wait(&full[s], round & 1u)) {
+            report_error(p.err, kErrBarrierTimeout, 72, static_cast<int>(it));
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
+          const uint32_t b_addr = a_addr + a_bytes;
+          const uint32_t sf_addr = b_addr + b_bytes;
+          const uint32_t tsfa = tmem_base + sf_col0 + (it & 1u) * sf_set;
+          const uint32_t tsfb = tsfa + 4;
+          tmem_cp_32x128b_warpx4(tsfa, sf_desc(sf_addr));
+          for (uint32_t c = 0; c < sfb_chunks; ++c) tmem_cp_32x128b_warpx4(tsfb + 4 * c, sf_desc(sf_addr + 512 * (1 + c)));
+#pragma unroll
+          for (uint32_t g = 0; g < 4; ++g)
+            umma_mxf8(d0, umma_desc_sw128(a_addr + g * 32), umma_desc_sw128(b_addr + g * 32),
+                      mx_idesc(128, static_cast<uint32_t>(p.bn), g, g), (kb > 0 || g > 0) ? 1u : 0u, tsfa, tsfb);
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&tmem_full[ab]);
+      }
+      umma_commit(drain);   // tensor memory is released only after every MMA has completed
+      if (!mbar_wait(drain, 0)) report_error(p.err, kErrBarrierTimeout, 74, static_cast<int>(it));
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // -------------------------------- epilogue --------------------------------
+    const int q = warp & 3;   // TMEM lane quarter this warp may read
+    uint32_t ui = 0;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++ui) {
+      const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
+      const uint32_t ab = ui % p.nbuf;
+      if (!mbar_wait_warp(&tmem_full[ab], (ui / p.nbuf) & 1u)) {
+        report_error(p.err, kErrBarrierTimeout, 73, static_cast<int>(ui));
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = mt * 128 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * p.bn;
+      for (int c0 = 0; c0 < p.bn; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c0, v);
+        tmem_ld_wait();
+        const int col0 = nt * p.bn + c0;
+        if (row < p.m && col0 < p.n) {
+          const size_t o = static_cast<size_t>(row) * p.n + col0;
+          const bool vec = col0 + 32 <= p.n && (p.n & 3) == 0;
+          if (p.acc_in != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.n) v[j] = __float_as_uint(__uint_as_float(v[j]) + p.acc_in[o + j]);
+          }
+          if (vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<uint4*>(p.out + o + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.n) p.out[o + j] = __uint_as_float(v[j]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[ab]);
+    }
+  } else {
+    // ------------------------------ scale loaders ------------------------------
+    // Per stage: 128 left-operand rows and bn right-operand columns, four scale bytes each, packed into one
+    // 32-bit word at its place in the 512-byte chunk of its 128 rows.
+    const int t = threadIdx.x - 6 * 32;   // 0 .. 127
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
+      for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+        const uint32_t s = it % p.stages, round = it / p.stages;
+        if (!mbar_wait_warp(&empty[s], (round & 1u) ^ 1u)) {
+          report_error(p.err, kErrBarrierTimeout, 75, static_cast<int>(it));
+          ok = false;
+          break;
+        }
+        uint8_t* sf = smem + static_cast<size_t>(s) * stage_bytes + a_bytes + b_bytes;
+        const int g0 = kb * 4;
+        {
+          const int row = mt * 128 + t;
+          uint32_t w = 0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) w |= a_scale_code(p, row, g0 + g) << (8 * g);
+          *reinterpret_cast<uint32_t*>(sf + (t & 31) * 16 + (t >> 5) * 4) = w;
+        }
+        for (uint32_t c = 0; c < sfb_chunks; ++c) {
+          const int col = nt * p.bn + static_cast<int>(c) * 128 + t;
+          uint32_t w = 0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) w |= b_scale_code(p, col, g0 + g) << (8 * g);
+          *reinterpret_cast<uint32_t*>(sf + 512 * (1 + c) + (t & 31) * 16 + (t >> 5) * 4) = w;
+        }
+        fence_proxy_async_smem();   // the chunk is read by tcgen05.cp (async proxy)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[s]);
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// dst[c, r] = src[r, c], bytes; 32 x 32 tiles through shared memory.
+__global__ void __launch_bounds__(256)
+transpose_u8_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, long long rows, long long cols) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ uint8_t tile[32][33];
+  const long long tiles_c = (cols + 31) / 32, tiles_r = (rows + 31) / 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+  for (long long t = blockIdx.x; t < tiles_r * tiles_c; t += gridDim.x) {
+    const long long r0 = (t / tiles_c) * 32, c0 = (t % tiles_c) * 32;
+    for (int i = ty; i < 32; i += 8)
+      if (r0 + i < rows && c0 + tx < cols) tile[i][tx] = src[(r0 + i) * cols + c0 + tx];
+    __syncthreads();
+    for (int i = ty; i < 32; i += 8)
+      if (c0 + i < cols && r0 + tx < rows) dst[(c0 + i) * rows + r0 + tx] = tile[tx][i];
+    __syncthreads();
+  }
+}
+
+}  // namespace
+
+int transpose_u8_launch(const void* src, void* dst, long long rows, long long cols, cudaStream_t stream) {
+  PTO_REQUIRE(src && dst, "transpose_u8: NULL tensor");
+  PTO_REQUIRE(rows >= 0 && cols >= 0, "transpose_u8: negative size");
+  if (rows == 0 || cols == 0) return kOk;
+  const long long tiles = ((rows + 31) / 32) * ((cols + 31) / 32);
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  launch_kernel(transpose_u8_kernel, dim3(static_cast<unsigned>(tiles < cap ? tiles : cap)), dim3(256), 0, stream,
+                static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), rows, cols);
+  return check_cuda(cudaGetLastError(), "transpose_u8_kernel launch");
+}
+
+int matmul_mx_launch(const void* a, const void* a_scale, int a_scale_layout, const void* b_t, const void* b_scale,
+                     int b_scale_layout, const float* acc_in, float* out, int m, int n, int k, int* err,
+                     cudaStream_t stream) {
+  PTO_REQUIRE(a && a_scale && b_t && b_scale && out, "matmul_mx: NULL tensor");
+  PTO_REQUIRE(m > 0 && n > 0 && k > 0, "matmul_mx: empty problem");
+  PTO_REQUIRE(k % 32 == 0, "matmul_mx: K must be a multiple of the 32-element scale group");
+  PTO_REQUIRE(a_scale_layout == PTO_MX_SCALE_LOGICAL || a_scale_layout == PTO_MX_SCALE_A_ZZ,
+              "matmul_mx: a_scale layout must be PTO_MX_SCALE_LOGICAL or PTO_MX_SCALE_A_ZZ");
+  PTO_REQUIRE(b_scale_layout == PTO_MX_SCALE_LOGICAL || b_scale_layout == PTO_MX_SCALE_B_NN,
+              "matmul_mx: b_scale layout must be PTO_MX_SCALE_LOGICAL or PTO_MX_SCALE_B_NN");
+  const int kgroups = k / 32;
+  PTO_REQUIRE(a_scale_layout == PTO_MX_SCALE_LOGICAL || (m % 16 == 0 && kgroups % 2 == 0),
+              "matmul_mx: the MX_A_ZZ scale layout needs m a multiple of 16 and an even number of K groups");
+  PTO_REQUIRE(b_scale_layout == PTO_MX_SCALE_LOGICAL || (n % 16 == 0 && kgroups % 2 == 0),
+              "matmul_mx: the MX_B_NN scale layout needs n a multiple of 16 and an even number of K groups");
+  MxParams p;
+  p.m = m; p.n = n; p.k = k; p.kgroups = kgroups;
+  p.kblocks = (k + kMxBK - 1) / kMxBK;
+  // 256-column tiles halve the left-operand traffic per FLOP; they pay once the problem has many tiles
+  const long long tiles128 = static_cast<long long>((m + 127) / 128) * ((n + 127) / 128);
+  p.bn = (n >= 256 && tiles128 >= 4ll * sm_count()) ? 256 : 128;
+  p.nbuf = p.bn == 128 ? 2 : 1;
+  p.m_tiles = (m + 127) / 128;
+  p.n_tiles = (n + p.bn - 1) / p.bn;
+  p.a_scale = static_cast<const uint8_t*>(a_scale); p.b_scale = static_cast<const uint8_t*>(b_scale);
+  p.a_layout = a_scale_layout; p.b_layout = b_scale_layout;
+  p.acc_in = acc_in; p.out = out; p.err = err;
+  const size_t sf_bytes = 512 * (1 + p.bn / 128);
+  const size_t stage_bytes = static_cast<size_t>(128 + p.bn) * kMxBK + 1024 * ((sf_bytes + 1023) / 1024);
+  int stages = static_cast<int>((210 * 1024) / stage_bytes);
+  if (stages > kMxMaxStages) stages = kMxMaxStages;
+  PTO_REQUIRE(stages >= 2, "matmul_mx: shared memory does not fit two pipeline stages");
+  p.stages = stages;
+  const size_t smem = 1024 + stages * stage_bytes + (2 * kMxMaxStages + 5) * 8 + 16;
+  const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
+  PTO_REQUIRE(tiles < (1ll << 31), "matmul_mx: problem too large");
+
+  CUtensorMap tm_a, tm_b;
+  int st = make_tensor_map_2d(&tm_a, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, m, k, k, kMxBK, 128,
+                              CU_TENSOR_MAP_SWIZZLE_128B);
+  if (st != kOk) return st;
+  st = make_tensor_map_2d(&tm_b, b_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k, k, kMxBK, 128,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+  if (st != kOk) return st;
+  if (first_use_on_device(2))
+    PTO_CUDA(cudaFuncSetAttribute(matmul_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  launch_kernel(matmul_mx_kernel, dim3(grid), dim3(kMxThreads), smem, stream, tm_a, tm_b, p);
+  return check_cuda(cudaGetLastError(), "matmul_mx_kernel launch");
+}
+
+}  // namespace pto

@@ -175,41 +175,127 @@ __global__ void __launch_bounds__(1024) moe_offsets_kernel(const int32_t* __rest
 }
 
 // pos[r] = offsets[expert_of[r]] + rank[r]; route_at[pos[r]] = r.
+// A route whose expert id lies outside [0, buckets) belongs to no bucket: it is reported through the error
+// word (kErrBadIndex), gets pos = -1 (the combine skips it) and nothing is read or written at an address
+// derived from the id.  Such routes leave the last slots of route_at unused; those are set to -1.
 __global__ void moe_positions_kernel(const int32_t* __restrict__ expert_of, const int32_t* __restrict__ rank,
-                                     const int32_t* __restrict__ offsets, int routes, int32_t* __restrict__ pos,
-                                     int32_t* __restrict__ route_at) {
+                                     const int32_t* __restrict__ offsets, int routes, int buckets,
+                                     int32_t* __restrict__ pos, int32_t* __restrict__ route_at, int* err) {
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= routes) return;
-  const int p = offsets[expert_of[r]] + rank[r];
+  if (r >= offsets[buckets]) route_at[r] = -1;   // slots [total valid routes, routes) have no route
+  const int e = expert_of[r];
+  if (e < 0 || e >= buckets) {
+    report_error(err, kErrBadIndex, 60, r);
+    pos[r] = -1;
+    return;
+  }
+  const int p = offsets[e] + rank[r];
   pos[r] = p;
   route_at[p] = r;
 }
 
-// dst row p = src row (route_at[p] / topk) for each of `n_arrays` row-major byte arrays.
-// One warp per destination row; 16-byte copies (row sizes are multiples of 16 bytes or small).
+// Arrival plan of the expert-parallel receiver.  Rows arrive source-major, and inside a source ordered by
+// local expert: recv_counts[s][e] rows from source s for local expert e.  The expert GEMM wants them grouped
+// by expert, inside an expert by source and then arrival order (the bucket order of the reference's
+// dispatch_step, tests/st/distributed/test_l3_ep_dispatch_combine.py:184-218).  One CTA:
+//   counts[e]         rows of expert e
+//   offsets[e]        first grouped row of expert e: dense (running sum, offsets[L] = number of rows) when
+//                     slot_stride == 0, else e * slot_stride (the reference's padded [L, R] receive layout)
+//   arrival_of[g]     arrival row that goes to grouped row g (-1 for a grouped row nothing arrives at)
+//   grouped_of[a]     grouped row of arrival row a
+// Rows that do not fit (more than `capacity` arrival or grouped rows, or more than slot_stride rows for one
+// expert) are dropped and reported through the error word.
+__global__ void __launch_bounds__(1024)
+moe_recv_plan_kernel(const int32_t* __restrict__ recv_counts, int world, int local_experts, int slot_stride,
+                     int capacity, int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
+                     int32_t* __restrict__ arrival_of, int32_t* __restrict__ grouped_of, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ int plan_smem[];
+  const int cells = world * local_experts;
+  int* arr0 = plan_smem;             // [cells] first arrival row of cell (s, e)
+  int* grp0 = plan_smem + cells;     // [cells] first grouped row of cell (s, e)
+  int* eoff = grp0 + cells;          // [local_experts + 1]
+  for (int g = threadIdx.x; g < capacity; g += blockDim.x) arrival_of[g] = -1;
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int c = 0; c < cells; ++c) {            // arrival order: s major, e minor
+      arr0[c] = run;
+      run += max(recv_counts[c], 0);
+    }
+    if (run > capacity) report_error(err, kErrBadIndex, 61, run);
+    run = 0;
+    for (int e = 0; e < local_experts; ++e) {    // grouped order: e major, s minor
+      const int first = slot_stride > 0 ? e * slot_stride : run;
+      eoff[e] = first;
+      int in_e = 0;
+      for (int s = 0; s < world; ++s) {
+        grp0[s * local_experts + e] = first + in_e;
+        in_e += max(recv_counts[s * local_experts + e], 0);
+      }
+      if (slot_stride > 0 && in_e > slot_stride) report_error(err, kErrBadIndex, 64, e);
+      counts[e] = in_e;
+      run = first + in_e;
+    }
+    eoff[local_experts] = slot_stride > 0 ? local_experts * slot_stride : run;
+    if (eoff[local_experts] > capacity) report_error(err, kErrBadIndex, 61, eoff[local_experts]);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= local_experts; e += blockDim.x) offsets[e] = min(eoff[e], capacity);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int c = warp; c < cells; c += warps) {
+    const int e = c % local_experts;
+    const int n = max(recv_counts[c], 0), a0 = arr0[c], g0 = grp0[c];
+    const int g_end = slot_stride > 0 ? min((e + 1) * slot_stride, capacity) : capacity;
+    for (int i = lane; i < n; i += 32) {
+      if (a0 + i < capacity) {
+        const bool fits = g0 + i < g_end;
+        grouped_of[a0 + i] = fits ? g0 + i : -1;
+        if (fits) arrival_of[g0 + i] = a0 + i;
+      }
+    }
+  }
+}
+
+// dst row p = src row (src_row_of[p] / div) for each of `n` row-major byte arrays; each array has its own
+// source and destination row stride, so that several arrays can be packed side by side into one payload row
+// (and unpacked again).  One warp per destination row; 16-byte copies where both rows are 16-byte aligned.
+// An index of -1 marks a destination row that nothing maps to (an unused slot of a padded layout, a route the
+// plan refused): the row is cleared.  Any other source row outside [0, src_rows) is cleared too and reported
+// through the error word (kErrBadIndex).
 struct RowArrays {
   const uint8_t* src[3];
   uint8_t* dst[3];
+  long long src_stride[3], dst_stride[3];
   int row_bytes[3];
   int n;
 };
 
 __global__ void __launch_bounds__(256)
-moe_gather_rows_kernel(RowArrays a, const int32_t* __restrict__ src_row_of, int div, long long rows) {
+moe_gather_rows_kernel(RowArrays a, const int32_t* __restrict__ src_row_of, int div, long long rows,
+                       long long src_rows, int* err) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
   for (long long p = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); p < rows;
        p += static_cast<long long>(gridDim.x) * (blockDim.x >> 5)) {
-    const long long s = src_row_of ? src_row_of[p] / div : p;
+    const long long raw = src_row_of ? src_row_of[p] : p;
+    const long long s = raw >= 0 ? raw / div : -1;
+    const bool ok = s >= 0 && s < src_rows;
+    if (!ok && raw != -1 && lane == 0) report_error(err, kErrBadIndex, 62, static_cast<int>(p));
     for (int i = 0; i < a.n; ++i) {
       const int rb = a.row_bytes[i];
-      const uint8_t* sp = a.src[i] + s * rb;
-      uint8_t* dp = a.dst[i] + p * rb;
-      if ((rb & 15) == 0 && ((reinterpret_cast<uintptr_t>(sp) | reinterpret_cast<uintptr_t>(dp)) & 15) == 0) {
+      const uint8_t* sp = a.src[i] + (ok ? s : 0) * a.src_stride[i];
+      uint8_t* dp = a.dst[i] + p * a.dst_stride[i];
+      if (!ok) {
+        for (int c = lane; c < rb; c += 32) dp[c] = 0;
+      } else if ((rb & 15) == 0 && ((reinterpret_cast<uintptr_t>(sp) | reinterpret_cast<uintptr_t>(dp)) & 15) == 0) {
         for (int c = lane; c < rb / 16; c += 32) reinterpret_cast<uint4*>(dp)[c] = reinterpret_cast<const uint4*>(sp)[c];
+      } else if ((rb & 3) == 0 && ((reinterpret_cast<uintptr_t>(sp) | reinterpret_cast<uintptr_t>(dp)) & 3) == 0) {
+        for (int c = lane; c < rb / 4; c += 32) reinterpret_cast<uint32_t*>(dp)[c] = reinterpret_cast<const uint32_t*>(sp)[c];
       } else {
         for (int c = lane; c < rb; c += 32) dp[c] = sp[c];
       }
@@ -219,18 +305,25 @@ moe_gather_rows_kernel(RowArrays a, const int32_t* __restrict__ src_row_of, int 
 
 // route_weight_sorted[p] = weights[route_at[p]]
 __global__ void moe_gather_f32_kernel(const float* __restrict__ src, const int32_t* __restrict__ index, long long n,
-                                      float* __restrict__ dst) {
+                                      long long n_src, float* __restrict__ dst, int* err) {
   pdl_launch_dependents();
   pdl_wait();
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i < n) dst[i] = src[index[i]];
+  if (i >= n) return;
+  const long long j = index[i];
+  if (j < 0 || j >= n_src) {
+    if (j != -1) report_error(err, kErrBadIndex, 63, static_cast<int>(i));
+    dst[i] = 0.f;
+  } else {
+    dst[i] = src[j];
+  }
 }
 
 // y[t] = bf16( sum_k fp32(rows[pos[t*topk + k]]) + fp32(shared[t]) ), k ascending.
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __nv_bfloat16* __restrict__ rows, const int32_t* __restrict__ pos,
-                   const __nv_bfloat16* __restrict__ shared, int topk, int hidden, __nv_bfloat16* __restrict__ y,
-                   float* __restrict__ y32) {
+                   const __nv_bfloat16* __restrict__ shared, int topk, int hidden, long long n_rows,
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ y32) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -238,7 +331,7 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ rows, const int32_t* __rest
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int k = 0; k < topk; ++k) {
       const int p = pos[static_cast<size_t>(t) * topk + k];
-      if (p < 0) continue;
+      if (p < 0 || p >= n_rows) continue;   // a route that was refused by the plan, or a slot outside `rows`
       const uint4 v = *reinterpret_cast<const uint4*>(rows + static_cast<size_t>(p) * hidden + c);
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -266,6 +359,24 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ rows, const int32_t* __rest
       o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
       *reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * hidden + c) = o;
     }
+  }
+}
+
+// y[r, :] = bf16(fp32(x[r, :]) * w[r * w_stride]): the stand-in expert of the reference's expert-parallel test
+// (local_expert_step, tests/st/distributed/test_l3_ep_dispatch_combine.py:309-327).  Rows r with
+// r % slot_stride >= count[r / slot_stride] (unused slots of a padded [experts, slots] layout) are skipped when
+// `count` is given.
+__global__ void __launch_bounds__(256)
+scale_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, int w_stride,
+                  const int32_t* __restrict__ count, int slot_stride, long long rows, int cols,
+                  __nv_bfloat16* __restrict__ y) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    if (count != nullptr && static_cast<int>(r % slot_stride) >= count[r / slot_stride]) continue;
+    const float wr = w[r * w_stride];
+    for (int c = threadIdx.x; c < cols; c += blockDim.x)
+      y[r * cols + c] = __float2bfloat16_rn(__bfloat162float(x[r * cols + c]) * wr);
   }
 }
 
@@ -305,7 +416,7 @@ int quantize_rows_launch(const void* x, int x_dtype, void* q, float* scale, long
 // expert_of int32 [routes] -> counts [buckets], offsets [buckets + 1], pos [routes], route_at [routes].
 // `rank_tmp` is an int32 [routes] work array.
 int moe_dispatch_plan_launch(const int32_t* expert_of, int routes, int buckets, int32_t* counts, int32_t* offsets,
-                             int32_t* pos, int32_t* route_at, int32_t* rank_tmp, cudaStream_t stream) {
+                             int32_t* pos, int32_t* route_at, int32_t* rank_tmp, int* err, cudaStream_t stream) {
   PTO_REQUIRE(expert_of && counts && offsets && pos && route_at && rank_tmp, "moe_dispatch_plan: NULL tensor");
   PTO_REQUIRE(buckets > 0 && routes >= 0, "moe_dispatch_plan: bad sizes");
   launch_kernel(moe_count_rank_kernel, dim3(buckets), dim3(256), 0, stream, expert_of, routes, counts, rank_tmp);
@@ -313,42 +424,74 @@ int moe_dispatch_plan_launch(const int32_t* expert_of, int routes, int buckets, 
   launch_kernel(moe_offsets_kernel, dim3(1), dim3(1024), 0, stream, counts, buckets, offsets);
   PTO_CUDA(cudaGetLastError());
   if (routes > 0) {
-    launch_kernel(moe_positions_kernel, dim3((routes + 255) / 256), dim3(256), 0, stream, expert_of, rank_tmp, offsets, routes, pos, route_at);
+    launch_kernel(moe_positions_kernel, dim3((routes + 255) / 256), dim3(256), 0, stream, expert_of, rank_tmp, offsets,
+                  routes, buckets, pos, route_at, err);
     PTO_CUDA(cudaGetLastError());
   }
   return kOk;
 }
 
-int moe_gather_rows_launch(const void* const* src, void* const* dst, const int* row_bytes, int n_arrays,
-                           const int32_t* src_row_of, int div, long long rows, cudaStream_t stream) {
-  PTO_REQUIRE(n_arrays >= 1 && n_arrays <= 3 && div >= 1, "moe_gather_rows: 1..3 arrays, div >= 1");
+int moe_recv_plan_launch(const int32_t* recv_counts, int world, int local_experts, int slot_stride, int capacity,
+                         int32_t* counts, int32_t* offsets, int32_t* arrival_of, int32_t* grouped_of, int* err,
+                         cudaStream_t stream) {
+  PTO_REQUIRE(recv_counts && counts && offsets && arrival_of && grouped_of, "moe_recv_plan: NULL tensor");
+  PTO_REQUIRE(world > 0 && local_experts > 0 && capacity >= 0 && slot_stride >= 0, "moe_recv_plan: bad sizes");
+  const size_t smem = sizeof(int) * (2 * static_cast<size_t>(world) * local_experts + local_experts + 1);
+  PTO_REQUIRE(smem <= 48 * 1024, "moe_recv_plan: world * local_experts too large");
+  launch_kernel(moe_recv_plan_kernel, dim3(1), dim3(1024), smem, stream, recv_counts, world, local_experts,
+                slot_stride, capacity, counts, offsets, arrival_of, grouped_of, err);
+  return check_cuda(cudaGetLastError(), "moe_recv_plan_kernel launch");
+}
+
+int moe_move_rows_launch(const void* const* src, const long long* src_stride, void* const* dst,
+                         const long long* dst_stride, const int* row_bytes, int n_arrays, const int32_t* src_row_of,
+                         int div, long long rows, long long src_rows, int* err, cudaStream_t stream) {
+  PTO_REQUIRE(n_arrays >= 1 && n_arrays <= 3 && div >= 1, "moe_move_rows: 1..3 arrays, div >= 1");
+  PTO_REQUIRE(src && dst && row_bytes, "moe_move_rows: NULL argument");
   if (rows <= 0) return kOk;
   RowArrays a;
   a.n = n_arrays;
   for (int i = 0; i < n_arrays; ++i) {
-    PTO_REQUIRE(src[i] && dst[i] && row_bytes[i] > 0, "moe_gather_rows: NULL array or empty row");
+    PTO_REQUIRE(src[i] && dst[i] && row_bytes[i] > 0, "moe_move_rows: NULL array or empty row");
     a.src[i] = static_cast<const uint8_t*>(src[i]);
     a.dst[i] = static_cast<uint8_t*>(dst[i]);
     a.row_bytes[i] = row_bytes[i];
+    a.src_stride[i] = src_stride ? src_stride[i] : row_bytes[i];
+    a.dst_stride[i] = dst_stride ? dst_stride[i] : row_bytes[i];
+    PTO_REQUIRE(a.src_stride[i] >= row_bytes[i] && a.dst_stride[i] >= row_bytes[i], "moe_move_rows: stride below row size");
   }
-  launch_kernel(moe_gather_rows_kernel, dim3(grid_rows(rows, 8)), dim3(256), 0, stream, a, src_row_of, div, rows);
+  launch_kernel(moe_gather_rows_kernel, dim3(grid_rows(rows, 8)), dim3(256), 0, stream, a, src_row_of, div, rows,
+                src_rows, err);
   return check_cuda(cudaGetLastError(), "moe_gather_rows_kernel launch");
 }
 
-int moe_gather_f32_launch(const float* src, const int32_t* index, long long n, float* dst, cudaStream_t stream) {
+int scale_rows_launch(const void* x, const float* w, int w_stride, const int32_t* count, int slot_stride,
+                      long long rows, int cols, void* y, cudaStream_t stream) {
+  PTO_REQUIRE(x && w && y, "scale_rows: NULL tensor");
+  PTO_REQUIRE(cols > 0 && w_stride >= 1 && (count == nullptr || slot_stride > 0), "scale_rows: bad sizes");
+  if (rows <= 0) return kOk;
+  launch_kernel(scale_rows_kernel, dim3(grid_rows(rows, 1)), dim3(256), 0, stream,
+                static_cast<const __nv_bfloat16*>(x), w, w_stride, count, slot_stride, rows, cols,
+                static_cast<__nv_bfloat16*>(y));
+  return check_cuda(cudaGetLastError(), "scale_rows_kernel launch");
+}
+
+int moe_gather_f32_launch(const float* src, const int32_t* index, long long n, long long n_src, float* dst, int* err,
+                          cudaStream_t stream) {
   PTO_REQUIRE(src && index && dst, "moe_gather_f32: NULL tensor");
   if (n <= 0) return kOk;
-  launch_kernel(moe_gather_f32_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, stream, src, index, n, dst);
+  launch_kernel(moe_gather_f32_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, stream, src, index, n,
+                n_src, dst, err);
   return check_cuda(cudaGetLastError(), "moe_gather_f32_kernel launch");
 }
 
 int moe_combine_launch(const void* rows, const int32_t* pos, const void* shared, int tokens, int topk, int hidden,
-                       void* y_bf16, float* y_f32, cudaStream_t stream) {
+                       long long n_rows, void* y_bf16, float* y_f32, cudaStream_t stream) {
   PTO_REQUIRE(rows && pos && (y_bf16 || y_f32), "moe_combine: NULL tensor");
   PTO_REQUIRE(hidden > 0 && hidden % 8 == 0 && topk > 0, "moe_combine: hidden must be a multiple of 8");
   if (tokens <= 0) return kOk;
   launch_kernel(moe_combine_kernel, dim3(tokens), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(rows), pos,
-                                                 static_cast<const __nv_bfloat16*>(shared), topk, hidden,
+                                                 static_cast<const __nv_bfloat16*>(shared), topk, hidden, n_rows,
                                                  static_cast<__nv_bfloat16*>(y_bf16), y_f32);
   return check_cuda(cudaGetLastError(), "moe_combine_kernel launch");
 }

@@ -284,20 +284,42 @@ int pto_quantize_rows(const void* x, int x_dtype, void* q, float* scale, int64_t
 }
 
 int pto_moe_dispatch_plan(const int32_t* expert_of, int routes, int buckets, int32_t* counts, int32_t* offsets,
-                          int32_t* pos, int32_t* route_at, int32_t* rank_tmp, void* stream) {
-  return pto::moe_dispatch_plan_launch(expert_of, routes, buckets, counts, offsets, pos, route_at, rank_tmp,
+                          int32_t* pos, int32_t* route_at, int32_t* rank_tmp, int32_t* err, void* stream) {
+  return pto::moe_dispatch_plan_launch(expert_of, routes, buckets, counts, offsets, pos, route_at, rank_tmp, err,
                                        static_cast<cudaStream_t>(stream));
 }
 
-int pto_moe_gather_rows(const void* const* src, void* const* dst, const int* row_bytes, int n_arrays,
-                        const int32_t* index, int div, int64_t rows, void* stream) {
-  if (!src || !dst || !row_bytes) return pto::fail(pto::kInvalidArgument, "moe_gather_rows: NULL argument");
-  return pto::moe_gather_rows_launch(src, dst, row_bytes, n_arrays, index, div, rows,
-                                     static_cast<cudaStream_t>(stream));
+int pto_moe_recv_plan(const int32_t* recv_counts, int world, int local_experts, int slot_stride, int capacity,
+                      int32_t* counts, int32_t* offsets, int32_t* arrival_of, int32_t* grouped_of, int32_t* err,
+                      void* stream) {
+  return pto::moe_recv_plan_launch(recv_counts, world, local_experts, slot_stride, capacity, counts, offsets,
+                                   arrival_of, grouped_of, err, static_cast<cudaStream_t>(stream));
 }
 
-int pto_moe_gather_f32(const float* src, const int32_t* index, int64_t n, float* dst, void* stream) {
-  return pto::moe_gather_f32_launch(src, index, n, dst, static_cast<cudaStream_t>(stream));
+int pto_moe_gather_rows(const void* const* src, void* const* dst, const int* row_bytes, int n_arrays,
+                        const int32_t* index, int div, int64_t rows, int64_t src_rows, int32_t* err, void* stream) {
+  if (!src || !dst || !row_bytes) return pto::fail(pto::kInvalidArgument, "moe_gather_rows: NULL argument");
+  return pto::moe_move_rows_launch(src, nullptr, dst, nullptr, row_bytes, n_arrays, index, div, rows, src_rows, err,
+                                   static_cast<cudaStream_t>(stream));
+}
+
+int pto_moe_move_rows(const void* const* src, const int64_t* src_stride, void* const* dst, const int64_t* dst_stride,
+                      const int* row_bytes, int n_arrays, const int32_t* index, int div, int64_t rows,
+                      int64_t src_rows, int32_t* err, void* stream) {
+  static_assert(sizeof(long long) == sizeof(int64_t), "stride arrays are passed through as 64-bit integers");
+  return pto::moe_move_rows_launch(src, reinterpret_cast<const long long*>(src_stride), dst,
+                                   reinterpret_cast<const long long*>(dst_stride), row_bytes, n_arrays, index, div,
+                                   rows, src_rows, err, static_cast<cudaStream_t>(stream));
+}
+
+int pto_moe_gather_f32(const float* src, const int32_t* index, int64_t n, int64_t n_src, float* dst, int32_t* err,
+                       void* stream) {
+  return pto::moe_gather_f32_launch(src, index, n, n_src, dst, err, static_cast<cudaStream_t>(stream));
+}
+
+int pto_scale_rows(const void* x, const float* w, int w_stride, const int32_t* count, int slot_stride, int64_t rows,
+                   int cols, void* y, void* stream) {
+  return pto::scale_rows_launch(x, w, w_stride, count, slot_stride, rows, cols, y, static_cast<cudaStream_t>(stream));
 }
 
 int pto_moe_expert_gemm(int swiglu, const void* w, const float* w_scale, int experts, int w_rows, int n_out, int k,
@@ -308,9 +330,20 @@ int pto_moe_expert_gemm(int swiglu, const void* w, const float* w_scale, int exp
 }
 
 int pto_moe_combine(const void* rows, const int32_t* pos, const void* shared, int tokens, int topk, int hidden,
-                    void* y_bf16, float* y_f32, void* stream) {
-  return pto::moe_combine_launch(rows, pos, shared, tokens, topk, hidden, y_bf16, y_f32,
+                    int64_t n_rows, void* y_bf16, float* y_f32, void* stream) {
+  return pto::moe_combine_launch(rows, pos, shared, tokens, topk, hidden, n_rows, y_bf16, y_f32,
                                  static_cast<cudaStream_t>(stream));
+}
+
+int pto_matmul_mx(const void* a, const void* a_scale, int a_scale_layout, const void* b_t, const void* b_scale,
+                  int b_scale_layout, const float* acc_in, float* out, int m, int n, int k, int32_t* err,
+                  void* stream) {
+  return pto::matmul_mx_launch(a, a_scale, a_scale_layout, b_t, b_scale, b_scale_layout, acc_in, out, m, n, k, err,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int pto_transpose_u8(const void* src, void* dst, int64_t rows, int64_t cols, void* stream) {
+  return pto::transpose_u8_launch(src, dst, rows, cols, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

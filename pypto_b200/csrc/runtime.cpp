@@ -258,6 +258,12 @@ int pto_device_status(pto_worker* h, int32_t out[4]) {
     snprintf(buf, sizeof buf, "block id or row outside the pool (site %d, CTA %d, value %d)", words[1], words[2], words[3]);
     return pto::fail(pto::kInvalidArgument, buf);
   }
+  if (words[0] == pto::kErrBadIndex) {
+    char buf[128];
+    snprintf(buf, sizeof buf, "index or row count outside its array, access skipped (site %d, CTA %d, value %d)",
+             words[1], words[2], words[3]);
+    return pto::fail(pto::kInvalidArgument, buf);
+  }
   return pto::kOk;
 }
 

@@ -81,6 +81,11 @@ def check_device_status(dev=None) -> None:
         raise _lib.PtoError(4, f"device wait timed out (site {site}, CTA {cta}, detail {extra})")
     if code == 2:
         raise _lib.PtoError(1, f"block id or row outside the pool (site {site}, CTA {cta}, value {extra})")
+    if code == 3:
+        raise _lib.PtoError(1, f"index or row count outside its array, access skipped (site {site}, CTA {cta}, "
+                               f"value {extra})")
+    if code != 0:
+        raise _lib.PtoError(2, f"device error word {code} (site {site}, CTA {cta}, value {extra})")
 
 
 def paged_attention(query, key_cache, value_cache, block_table, context_lens, *, num_heads: int,
@@ -347,7 +352,8 @@ def quantize_rows(x: torch.Tensor):
 
 
 def moe_dispatch_plan(expert_of: torch.Tensor, buckets: int):
-    """counts [buckets], offsets [buckets+1], pos [routes], route_at [routes] (all int32)."""
+    """counts [buckets], offsets [buckets+1], pos [routes], route_at [routes] (all int32).  An expert id
+    outside [0, buckets) is never dereferenced: it sets the device error word (``check_device_status``)."""
     dev = _need_cuda(expert_of)
     if expert_of.dtype != torch.int32:
         raise TypeError("moe_dispatch_plan: expert ids must be int32")
@@ -360,12 +366,35 @@ def moe_dispatch_plan(expert_of: torch.Tensor, buckets: int):
     with torch.cuda.device(dev):
         _lib.check(_lib.load().pto_moe_dispatch_plan(expert_of.data_ptr(), n, buckets, counts.data_ptr(),
                                                      offsets.data_ptr(), pos.data_ptr(), route_at.data_ptr(),
-                                                     tmp.data_ptr(), _stream_ptr(dev)))
+                                                     tmp.data_ptr(), _err_ptr(dev), _stream_ptr(dev)))
     return counts, offsets, pos, route_at
 
 
+def moe_recv_plan(recv_counts: torch.Tensor, capacity: int, slot_stride: int = 0):
+    """Receiver plan from recv_counts int32 [world, L]: (counts [L], offsets [L+1], arrival_of [capacity],
+    grouped_of [capacity]).  slot_stride > 0 lays expert e out at rows [e*slot_stride, (e+1)*slot_stride)."""
+    dev = _need_cuda(recv_counts)
+    if recv_counts.dtype != torch.int32 or recv_counts.dim() != 2:
+        raise TypeError("moe_recv_plan: recv_counts must be int32 [world, local_experts]")
+    world, L = recv_counts.shape
+    counts = torch.empty(L, dtype=torch.int32, device=dev)
+    offsets = torch.empty(L + 1, dtype=torch.int32, device=dev)
+    arrival_of = torch.empty(max(capacity, 1), dtype=torch.int32, device=dev)
+    grouped_of = torch.empty(max(capacity, 1), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_moe_recv_plan(recv_counts.data_ptr(), world, L, slot_stride, capacity,
+                                                 counts.data_ptr(), offsets.data_ptr(), arrival_of.data_ptr(),
+                                                 grouped_of.data_ptr(), _err_ptr(dev), _stream_ptr(dev)))
+    return counts, offsets, arrival_of, grouped_of
+
+
+def _row_bytes(t: torch.Tensor) -> int:
+    return (t.numel() // t.shape[0]) * t.element_size() if t.shape[0] else 0
+
+
 def gather_rows(sources: list, index: torch.Tensor | None, div: int = 1, rows: int | None = None):
-    """dst_i[p] = src_i[index[p] // div] for up to three 2-D (or 1-D) tensors; bit-exact copies."""
+    """dst_i[p] = src_i[index[p] // div] for up to three 2-D (or 1-D) tensors; bit-exact copies.  index -1
+    gives a zero row; any other index outside the source sets the device error word."""
     import ctypes as C
     dev = _need_cuda(*sources) if index is None else _need_cuda(*sources, index)
     n = len(sources)
@@ -373,7 +402,7 @@ def gather_rows(sources: list, index: torch.Tensor | None, div: int = 1, rows: i
         raise ValueError("gather_rows: 1..3 source tensors")
     rows = (index.numel() if index is not None else sources[0].shape[0]) if rows is None else rows
     outs = [torch.empty((rows,) + tuple(s.shape[1:]), dtype=s.dtype, device=dev) for s in sources]
-    rb = [(s.numel() // s.shape[0]) * s.element_size() if s.shape[0] else 0 for s in sources]
+    rb = [_row_bytes(s) for s in sources]
     if rows == 0 or any(b == 0 for b in rb):
         return outs
     src = (C.c_void_p * n)(*[s.data_ptr() for s in sources])
@@ -381,8 +410,44 @@ def gather_rows(sources: list, index: torch.Tensor | None, div: int = 1, rows: i
     rbs = (C.c_int * n)(*rb)
     with torch.cuda.device(dev):
         _lib.check(_lib.load().pto_moe_gather_rows(src, dst, rbs, n, index.data_ptr() if index is not None else None,
-                                                   div, rows, _stream_ptr(dev)))
+                                                   div, rows, min(s.shape[0] for s in sources), _err_ptr(dev),
+                                                   _stream_ptr(dev)))
     return outs
+
+
+def move_rows(parts: list, index: torch.Tensor | None, div: int, rows: int, src_rows: int):
+    """Strided row mover behind payload packing: ``parts`` is a list of up to three
+    (src_ptr, src_stride, dst_ptr, dst_stride, row_bytes) byte descriptions; dst row p of every part receives
+    src row index[p] // div (identity without an index)."""
+    import ctypes as C
+    n = len(parts)
+    if not 1 <= n <= 3:
+        raise ValueError("move_rows: 1..3 parts")
+    if rows == 0:
+        return
+    dev = torch.device("cuda", torch.cuda.current_device())
+    src = (C.c_void_p * n)(*[p[0] for p in parts])
+    sst = (C.c_int64 * n)(*[p[1] for p in parts])
+    dst = (C.c_void_p * n)(*[p[2] for p in parts])
+    dstr = (C.c_int64 * n)(*[p[3] for p in parts])
+    rbs = (C.c_int * n)(*[p[4] for p in parts])
+    _lib.check(_lib.load().pto_moe_move_rows(src, sst, dst, dstr, rbs, n, index.data_ptr() if index is not None else None,
+                                             div, rows, src_rows, _err_ptr(dev), _stream_ptr(dev)))
+
+
+def scale_rows(x: torch.Tensor, w: torch.Tensor, w_stride: int = 1, count: torch.Tensor | None = None,
+               slot_stride: int = 0, out: torch.Tensor | None = None):
+    """y[r] = bf16(fp32(x[r]) * w[r * w_stride]) (the reference's stand-in expert); with ``count`` only the first
+    count[e] rows of every block of slot_stride rows are written."""
+    dev = _need_cuda(x, w)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.float32 or x.dim() != 2:
+        raise TypeError("scale_rows: x must be bf16 [rows, cols], w fp32")
+    out = torch.zeros_like(x) if out is None else out
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_scale_rows(x.data_ptr(), w.data_ptr(), w_stride,
+                                              count.data_ptr() if count is not None else None, slot_stride,
+                                              x.shape[0], x.shape[1], out.data_ptr(), _stream_ptr(dev)))
+    return out
 
 
 def moe_expert_gemm(swiglu: bool, w: torch.Tensor, w_scale: torch.Tensor, x: torch.Tensor, x_scale: torch.Tensor,
@@ -417,5 +482,55 @@ def moe_combine(rows: torch.Tensor, pos: torch.Tensor, shared: torch.Tensor | No
     with torch.cuda.device(dev):
         _lib.check(_lib.load().pto_moe_combine(rows.data_ptr(), pos.data_ptr(),
                                                shared.data_ptr() if shared is not None else None, tokens, topk, hidden,
-                                               y.data_ptr(), y32.data_ptr() if want_f32 else None, _stream_ptr(dev)))
+                                               rows.shape[0], y.data_ptr(), y32.data_ptr() if want_f32 else None,
+                                               _stream_ptr(dev)))
     return (y, y32) if want_f32 else y
+
+
+# ---------------------------------------------------------------------------
+# MX block-scaled FP8 matmul
+# ---------------------------------------------------------------------------
+
+MX_SCALE_LOGICAL, MX_SCALE_A_ZZ, MX_SCALE_B_NN = 0, 1, 2
+
+
+def transpose_u8(x: torch.Tensor) -> torch.Tensor:
+    """[rows, cols] of one-byte elements -> [cols, rows] (operand re-layout for ``matmul_mx``)."""
+    dev = _need_cuda(x)
+    if x.dim() != 2 or x.element_size() != 1:
+        raise TypeError("transpose_u8: a 2-D tensor of one-byte elements is expected")
+    out = torch.empty(x.shape[1], x.shape[0], dtype=x.dtype, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_transpose_u8(x.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1], _stream_ptr(dev)))
+    return out
+
+
+def matmul_mx(a: torch.Tensor, a_scale: torch.Tensor, b_t: torch.Tensor, b_scale: torch.Tensor, *,
+              acc: torch.Tensor | None = None, out: torch.Tensor | None = None,
+              a_scale_layout: int = MX_SCALE_LOGICAL, b_scale_layout: int = MX_SCALE_LOGICAL) -> torch.Tensor:
+    """fp32 out[m, n] = (acc +) MX matmul of a e4m3 [m, k] and b_t e4m3 [n, k] (K contiguous) with E8M0 scale
+    codes a_scale uint8 [m, k/32], b_scale uint8 [k/32, n] (tile.matmul_mx / matmul_mx_acc,
+    src/ir/op/tile_ops/matmul_mx.cpp:321-345)."""
+    dev = _need_cuda(a, a_scale, b_t, b_scale)
+    if a.element_size() != 1 or b_t.element_size() != 1 or a_scale.element_size() != 1 or b_scale.element_size() != 1:
+        raise TypeError("matmul_mx: operands are e4m3 (one byte) and scales E8M0 codes (one byte)")
+    m, k = a.shape
+    n, k2 = b_t.shape
+    if k != k2 or k % 32:
+        raise ValueError("matmul_mx: both operands need the same K, a multiple of 32")
+    if a_scale.numel() != m * (k // 32) or b_scale.numel() != (k // 32) * n:
+        raise ValueError("matmul_mx: scale tensors must hold m*k/32 and (k/32)*n codes")
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.float32, device=dev)
+    elif out.dtype != torch.float32 or tuple(out.shape) != (m, n) or not out.is_contiguous():
+        raise ValueError("matmul_mx: out must be a contiguous fp32 [m, n] tensor")
+    if acc is not None:
+        _need_cuda(acc)
+        if acc.dtype != torch.float32 or tuple(acc.shape) != (m, n):
+            raise ValueError("matmul_mx: acc must be fp32 [m, n]")
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_matmul_mx(a.data_ptr(), a_scale.data_ptr(), a_scale_layout, b_t.data_ptr(),
+                                             b_scale.data_ptr(), b_scale_layout,
+                                             acc.data_ptr() if acc is not None else None, out.data_ptr(), m, n, k,
+                                             _err_ptr(dev), _stream_ptr(dev)))
+    return out

@@ -25,6 +25,8 @@ GATHER = "tests/st/runtime/ops/test_paged_gather.py"
 EP = "tests/st/distributed/test_l3_ep_dispatch_combine.py"
 SCOPE3 = "tests/st/runtime/framework_and_models/test_qwen3_decode_scope3_mixed.py"
 SORT = "tests/st/runtime/ops/test_sort.py"
+LLAMA = "tests/st/examples/03_llm_models/test_llama_7b_mini_1h.py"
+MX = "tests/st/runtime/ops/test_matmul_mx.py"
 
 EP_SMALL = dict(T=16, TOPK=3, D=32, L=4, R=40, N_ROUTES=48)
 
@@ -40,6 +42,36 @@ def pa04_case(batch, heads, head_dim, block, max_blocks, ctx, scale, seed, ctx_l
              config=cfg)
     ns["golden"](t)
     return t
+
+
+def rope_case():
+    """RoPE tables and rotate-half from the reference's llama test (helpers nested in
+    define_tensors / compute_expected, test_llama_7b_mini_1h.py:83-95, 146-159)."""
+    tab = ref_extract.extract(LLAMA, ["make_cos_emb", "make_sin_emb"], overrides={"head_dim": 64}, nested=True)
+    cos, sin = tab["make_cos_emb"](), tab["make_sin_emb"]()
+    rot = ref_extract.extract(LLAMA, ["apply_rope"], overrides={"cos_emb": cos, "sin_emb": sin}, nested=True)
+    x = torch.randn(16, 64, generator=torch.Generator().manual_seed(11))
+    return dict(cos_emb=cos, sin_emb=sin, x=x, rotated=rot["apply_rope"](x), head_dim=64, theta=10000.0)
+
+
+def matmul_mx_case():
+    """The reference's MXFP8 x MXFP8 case (test_matmul_mx.py:146-168): integer-valued e4m3 data in
+    [-2, 2], E8M0 scale codes 126..129, scales in the packed MX_A_ZZ / MX_B_NN layouts it hands to the
+    kernel, and the golden of :119-131 (dequantise per 32-wide K group, fp64 matmul, fp32 result)."""
+    names = ["_pack_a_scale", "_unpack_a_scale", "_pack_b_scale", "_unpack_b_scale", "_matmul_mx_golden",
+             "M", "K", "N", "MX_GROUP_SIZE", "SCALE_BLOCK_SIZE", "SCALE_C0_SIZE"]
+    ns = ref_extract.extract(MX, names)
+    m, k, n = ns["M"], ns["K"], ns["N"]
+    g = torch.Generator().manual_seed(23)                       # _make_case_inputs(lhs_fp4=False), :156-168
+    a = torch.randint(-2, 3, (m, k), generator=g).to(torch.float8_e4m3fn)
+    b = torch.randint(-2, 3, (k, n), generator=g).to(torch.float8_e4m3fn)
+    a_codes = torch.randint(126, 130, (m, k // 32), generator=g).to(torch.uint8)
+    b_codes = torch.randint(126, 130, (k // 32, n), generator=g).to(torch.uint8)
+    a_packed, b_packed = ns["_pack_a_scale"](a_codes), ns["_pack_b_scale"](b_codes)
+    assert torch.equal(ns["_unpack_a_scale"](a_packed), a_codes) and torch.equal(ns["_unpack_b_scale"](b_packed), b_codes)
+    out = ns["_matmul_mx_golden"](a.to(torch.float64), a_codes, b.to(torch.float64), b_codes)
+    return dict(a=a.view(torch.uint8), b=b.view(torch.uint8), a_scale_codes=a_codes, b_scale_codes=b_codes,
+                a_scale_packed=a_packed, b_scale_packed=b_packed, out=out, out_acc=2 * out, m=m, k=k, n=n)
 
 
 def main():
@@ -101,6 +133,9 @@ def main():
 
     ns = ref_extract.extract(SORT, ["_make_unique_fp32_values"])
     fx["sort_unique_2048"] = dict(src=ns["_make_unique_fp32_values"](2048))
+
+    fx["rope"] = rope_case()
+    fx["matmul_mx"] = matmul_mx_case()
 
     for name, data in fx.items():
         torch.save(data, os.path.join(HERE, name + ".pt"))

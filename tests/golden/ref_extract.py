@@ -3,8 +3,11 @@
 The reference's example and test modules import ``pypto`` at the top, which
 cannot be imported without its compiled core.  Their ``golden`` / helper
 functions, however, use only ``torch`` and ``struct``.  This helper parses a
-reference file, picks named top-level functions (and simple constant
-assignments) and executes just those in a namespace holding torch and struct.
+reference file, picks named functions (top-level ones and simple constant
+assignments by default; with ``nested=True`` functions defined anywhere, e.g.
+helpers local to a test method) and executes just those in a namespace holding
+torch and struct.  A nested function's free variables become globals of that
+namespace: supply them through ``overrides``.
 Used by ``make_golden.py`` (fixture generation) and by the CPU test that pins
 the oracle whenever the reference tree is present.
 """
@@ -26,23 +29,39 @@ def available() -> bool:
     return os.path.isdir(os.path.join(REFERENCE_ROOT, "examples", "models"))
 
 
-def extract(rel_path: str, names: list[str], overrides: dict | None = None) -> dict:
-    """Return a namespace with the requested top-level functions / constants of
-    ``rel_path`` (relative to the reference root).  ``overrides`` replaces module
-    constants (e.g. to shrink problem sizes) after the definitions have run."""
+def _assigned(node: ast.Assign) -> set:
+    """Names bound by a simple assignment (``A = ...`` or ``A, B = ...``); empty if it binds anything else."""
+    out = set()
+    for t in node.targets:
+        elts = t.elts if isinstance(t, ast.Tuple) else [t]
+        if not all(isinstance(e, ast.Name) for e in elts):
+            return set()
+        out |= {e.id for e in elts}
+    return out
+
+
+def extract(rel_path: str, names: list[str], overrides: dict | None = None, nested: bool = False) -> dict:
+    """Return a namespace with the requested functions / constants of ``rel_path``
+    (relative to the reference root).  ``overrides`` replaces module constants (e.g.
+    to shrink problem sizes) after the definitions have run, and supplies the free
+    variables of functions lifted out of an enclosing scope (``nested=True``)."""
     path = os.path.join(REFERENCE_ROOT, rel_path)
     with open(path, encoding="utf-8") as fh:
         tree = ast.parse(fh.read(), filename=path)
     wanted = []
-    for node in tree.body:
+    seen = set()
+    for node in (ast.walk(tree) if nested else tree.body):
         if isinstance(node, ast.FunctionDef) and node.name in names:
+            if node.name in seen:
+                continue
+            seen.add(node.name)
             node.decorator_list = []
             wanted.append(node)
-        elif isinstance(node, ast.Assign) and all(
-            isinstance(t, ast.Name) and t.id in names for t in node.targets
-        ):
+        elif not nested and isinstance(node, ast.Assign) and _assigned(node) and _assigned(node) <= set(names):
             wanted.append(node)
-    found = {getattr(n, "name", None) or n.targets[0].id for n in wanted}
+    found = set()
+    for n in wanted:
+        found |= {n.name} if isinstance(n, ast.FunctionDef) else _assigned(n)
     missing = set(names) - found
     if missing:
         raise KeyError(f"{rel_path}: not found: {sorted(missing)}")

@@ -68,3 +68,41 @@ def test_moe_full_size_token_permutation_equivariance():
     scores = torch.sigmoid(ops.linear(x, layer.gate_packed)).cpu()
     exp_idx, _ = omoe.topk_from_scores(scores, bias.cpu(), m["topk"])
     assert (idx.cpu() == exp_idx).all(dim=1).float().mean() > 0.999   # sigmoid rounding may flip a near-tie
+
+    # Oracle on a sample at the layer's own geometry (H = 7168 through the four-stage pipeline of the gate/up
+    # GEMM, I = 2048 through the six-stage one of the down GEMM): 8 tokens spread over the batch, each through
+    # its eight routed experts and the shared expert, with the device's routing.
+    H, I = m["hidden"], m["inter"]
+    sample = torch.arange(0, m["tokens"], m["tokens"] // 8)[:8] + 3
+    xq, xs = omoe.quantize_rows(x[sample].cpu())
+    idx_h, w_h = idx.cpu(), w.cpu()
+
+    def oracle_expert(weights, e):
+        """Expert e of a K-major device weight dict in the oracle's x @ W layout."""
+        def t8(v):
+            return v.cpu().view(torch.uint8).t().contiguous().view(torch.float8_e4m3fn)
+        gu, s_gu = t8(weights["w_gu"][e]), weights["s_gu"][e].cpu().t().contiguous()
+        return dict(wg=gu[:, :I], wu=gu[:, I:], sg=s_gu[:, :I // 128], su=s_gu[:, I // 128:],
+                    wd=t8(weights["w_d"][e]), sd=weights["s_d"][e].cpu().t().contiguous())
+
+    contrib = torch.zeros(len(sample), m["topk"], H)
+    by_expert: dict = {}
+    for i, t in enumerate(sample.tolist()):
+        for k in range(m["topk"]):
+            by_expert.setdefault(int(idx_h[t, k]), []).append((i, t, k))
+    for e, uses in by_expert.items():
+        ex = oracle_expert(layer.routed, e)
+        rows = torch.tensor([i for i, _t, _k in uses])
+        o = omoe.expert_ffn(xq[rows], xs[rows], ex)
+        for j, (i, t, k) in enumerate(uses):
+            contrib[i, k] = (o[j] * w_h[t, k]).bfloat16().float()
+    y_exp = torch.zeros(len(sample), H)
+    for k in range(m["topk"]):
+        y_exp += contrib[:, k]
+    y_exp += omoe.expert_ffn(xq, xs, oracle_expert(layer.shared, 0)).bfloat16().float()
+    y_exp = y_exp.bfloat16().float()
+    got = y[sample.to(dev)].cpu().float()
+    rel = ((got - y_exp).norm() / y_exp.norm()).item()
+    assert rel < 2e-2, rel
+    per_row = (got - y_exp).norm(dim=1) / y_exp.norm(dim=1)
+    assert per_row.max() < 5e-2, per_row

@@ -1,9 +1,11 @@
-"""Expert-parallel MoE on 2 GPUs (one process per GPU, NCCL all-to-all for dispatch and
-combine): every rank's output must equal the oracle's single-process result for its token
-slice.  Skipped when fewer than 2 GPUs are visible."""
+"""Expert-parallel MoE on 2, 4 and 8 GPUs (one process per GPU; dispatch and combine through the library's
+NCCL communicator): every rank's output must equal the oracle's single-process result for its token slice.
+Each world size is skipped when fewer GPUs are visible."""
 
 import os
-import socket
+import queue
+import sys
+import traceback
 
 import pytest
 import torch
@@ -12,61 +14,90 @@ pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-
-def _free_port():
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
+# 7168 hidden channels: the gate/up GEMM of the benchmark layer (56 K blocks, four-stage pipeline)
+SHAPE = dict(tokens=256, hidden=7168, inter=256, experts=16, topk=4)
 
 
-def _worker(rank, world, port, q):
-    import sys
-    sys.path.insert(0, ROOT)
-    import torch.distributed as dist
-
-    import oracle
-    from oracle import moe as omoe
-    from pypto_b200.moe import MoELayer
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+def _worker(rank, world, uid, q):
     try:
-        tokens, hidden, inter, experts, topk = 256, 1024, 512, 16, 4
+        sys.path.insert(0, ROOT)
+        import oracle
+        from oracle import moe as omoe
+        from pypto_b200 import ops
+        from pypto_b200.comm import Communicator
+        from pypto_b200.moe import MoELayer, PhaseTimer
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        torch.cuda.set_device(rank)
+        tokens, hidden, inter, experts, topk = (SHAPE[k] for k in ("tokens", "hidden", "inter", "experts", "topk"))
         m = oracle.inputs.moe_inputs(tokens=tokens, hidden=hidden, inter=inter, n_experts=experts, topk=topk, seed=9)
         y_exp, idx_exp, w_exp = omoe.moe_layer(m["x"], m["gate_w"], m["bias"], m["routed"], m["shared"], topk)
         L, tl = experts // world, tokens // world
         mine = {k: v[rank * L:(rank + 1) * L].cuda() for k, v in m["routed"].items()}
-        layer = MoELayer(m["gate_w"].cuda(), m["bias"].cuda(), mine, {k: v.cuda() for k, v in m["shared"].items()},
-                         topk, n_experts=experts, group=dist.group.WORLD)
-        sl = slice(rank * tl, (rank + 1) * tl)
-        y, _, _ = layer.forward(m["x"][sl].cuda(), routing=(idx_exp[sl].cuda(), w_exp[sl].cuda()))
-        torch.cuda.synchronize()
-        from pypto_b200 import ops
-        status = ops.device_status()
-        rel = ((y.cpu().float() - y_exp[sl].float()).norm() / y_exp[sl].float().norm()).item()
-        y2, idx2, _ = layer.forward(m["x"][sl].cuda())        # own routing, a second pass over the exchange
-        same = (idx2.cpu() == idx_exp[sl]).all(dim=1)
-        rel2 = ((y2.cpu().float()[same] - y_exp[sl].float()[same]).norm() / y_exp[sl].float()[same].norm()).item()
-        q.put((rank, rel, rel2, float(same.float().mean()), status[0]))
-    finally:
-        dist.destroy_process_group()
+        comm = Communicator(rank, world, uid, rank)          # collective: after everything that can fail alone
+        try:
+            layer = MoELayer(m["gate_w"].cuda(), m["bias"].cuda(), mine, {k: v.cuda() for k, v in m["shared"].items()},
+                             topk, n_experts=experts, comm=comm)
+            sl = slice(rank * tl, (rank + 1) * tl)
+            y, _, _ = layer.forward(m["x"][sl].cuda(), routing=(idx_exp[sl].cuda(), w_exp[sl].cuda()))
+            torch.cuda.synchronize()
+            status = ops.device_status()
+            with torch.cuda.stream(layer._side_stream(y.device)):
+                side_status = ops.device_status()
+            rel = ((y.cpu().float() - y_exp[sl].float()).norm() / y_exp[sl].float().norm()).item()
+            timer = PhaseTimer()
+            y2, idx2, _ = layer.forward(m["x"][sl].cuda(), timer=timer)     # own routing, a second pass over the exchange
+            phases = timer.result()
+            same = (idx2.cpu() == idx_exp[sl]).all(dim=1)
+            rel2 = ((y2.cpu().float()[same] - y_exp[sl].float()[same]).norm() / y_exp[sl].float()[same].norm()).item()
+            q.put((rank, "ok", rel, rel2, float(same.float().mean()), status[0] or side_status[0], sorted(phases)))
+        finally:
+            comm.close()
+    except BaseException:
+        q.put((rank, "error", traceback.format_exc()))
+        os._exit(1)         # leave at once: a peer may be blocked in a collective that will never complete
 
 
-@pytest.mark.parametrize("world", [2])
-def test_expert_parallel_layer_matches_oracle(world):
-    if torch.cuda.device_count() < world:
-        pytest.skip(f"needs {world} GPUs")
+def run_ranks(target, world, args=(), timeout=420):
+    """Start one child per rank, collect one message from each, and never leave a child behind: on a failure
+    or a timeout every child still alive is terminated, then killed."""
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    for p in procs:
-        p.join(timeout=300)
-        assert p.exitcode == 0
-    for _ in range(world):
-        rank, rel, rel2, frac_same, status = q.get(timeout=5)
+    procs = [ctx.Process(target=target, args=(r, world) + tuple(args) + (q,)) for r in range(world)]
+    results = []
+    try:
+        for p in procs:
+            p.start()
+        for _ in range(world):
+            try:
+                msg = q.get(timeout=timeout)
+            except queue.Empty:
+                raise AssertionError(f"a rank did not report within {timeout} s; got {results}") from None
+            results.append(msg)
+            if msg[1] != "ok":
+                raise AssertionError(f"rank {msg[0]} failed:\n{msg[2]}")
+        for p in procs:
+            p.join(timeout=60)
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        for p in procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=10)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    return results
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_layer_matches_oracle(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    from pypto_b200 import comm
+    results = run_ranks(_worker, world, args=(comm.unique_id(),))
+    for rank, _ok, rel, rel2, frac_same, status, phases in results:
         assert status == 0
         assert rel < 2e-2 and rel2 < 2e-2 and frac_same > 0.97, (rank, rel, rel2, frac_same)
+        assert {"plan", "pack", "exchange_out", "unpack", "experts", "exchange_back", "combine"} <= set(phases)

@@ -82,22 +82,64 @@ def test_dispatch_plan_matches_reference_protocol(golden, n_ranks):
         x_s, = ops.gather_rows([t["x"][s].cuda()], route_at, div=K)
         w_s, = ops.gather_rows([t["weights"][s].reshape(-1, 1).cuda()], route_at, div=1)
         plans.append((counts.cpu(), offsets.cpu(), route_at.cpu(), x_s.cpu(), w_s.cpu()))
+    R = t["r"]
     for d in range(n_ranks):
-        rows_x, rows_w, rows_id, rows_e = [], [], [], []
+        rows_x, rows_w, rows_id = [], [], []
         for s in range(n_ranks):
             counts, offsets, route_at, x_s, w_s = plans[s]
             lo, hi = int(offsets[d * L]), int(offsets[(d + 1) * L])
             rows_x.append(x_s[lo:hi]); rows_w.append(w_s[lo:hi]); rows_id.append(route_at[lo:hi])
-            rows_e.append(torch.repeat_interleave(torch.arange(L, dtype=torch.int32), counts[d * L:(d + 1) * L].long()))
-        x_r, w_r, id_r, e_r = (torch.cat(v) for v in (rows_x, rows_w, rows_id, rows_e))
-        c2, off2, _pos2, route_at2 = ops.moe_dispatch_plan(e_r.cuda(), L)
-        x_g, w_g, id_g = ops.gather_rows([x_r.cuda(), w_r.cuda(), id_r.reshape(-1, 1).cuda()], route_at2, div=1)
+        x_r, w_r, id_r = (torch.cat(v) for v in (rows_x, rows_w, rows_id))        # arrival order: source-major
+        recv_counts = torch.stack([plans[s][0][d * L:(d + 1) * L] for s in range(n_ranks)]).contiguous().cuda()
+        arrived = x_r.shape[0]
+        # dense grouping (what the expert GEMM consumes)
+        c2, off2, arrival_of, grouped_of = ops.moe_recv_plan(recv_counts, arrived)
+        x_g, w_g, id_g = ops.gather_rows([x_r.cuda(), w_r.cuda(), id_r.reshape(-1, 1).cuda()], arrival_of[:arrived], div=1)
         assert torch.equal(c2.cpu(), t["count"][d])
+        assert torch.equal(arrival_of[:arrived][grouped_of[:arrived].long()].cpu(), torch.arange(arrived, dtype=torch.int32))
         for e in range(L):
             n, o = int(c2[e]), int(off2[e])
             assert torch.equal(x_g[o:o + n].cpu().view(torch.int16), t["recv_x"][d, e, :n].view(torch.int16))
             assert torch.equal(w_g[o:o + n, 0].cpu(), t["recv_w"][d, e, :n])
             assert torch.equal(id_g[o:o + n, 0].cpu(), t["recv_idx"][d, e, :n])
+        # the reference's padded [L, R] receive layout: unused slots stay zero, as in its zero-initialised outputs
+        c3, off3, arrival_pad, _g3 = ops.moe_recv_plan(recv_counts, L * R, slot_stride=R)
+        x_p, w_p, id_p = ops.gather_rows([x_r.cuda(), w_r.cuda(), id_r.reshape(-1, 1).cuda()], arrival_pad, div=1)
+        assert torch.equal(c3.cpu(), t["count"][d]) and off3.cpu().tolist() == [e * R for e in range(L + 1)]
+        assert torch.equal(x_p.cpu().view(torch.int16).reshape(L, R, -1), t["recv_x"][d].view(torch.int16))
+        assert torch.equal(w_p.cpu().reshape(L, R), t["recv_w"][d])
+        assert torch.equal(id_p.cpu().reshape(L, R), t["recv_idx"][d])
+    torch.cuda.synchronize()
+    ops.check_device_status()
+
+
+def test_expert_id_outside_the_buckets_is_reported_not_dereferenced():
+    """A route whose expert id is not a bucket: no address is formed from it; the route gets pos -1, the tail
+    of route_at is -1, gathers through those entries give zero rows, the combine skips the route, and the
+    error word carries code 3."""
+    from pypto_b200 import _lib
+    ops = _ops()
+    torch.cuda.synchronize()
+    ops.device_status()                                    # start from a clear word
+    ids = torch.tensor([3, 1, 9999, 0, -7, 1], dtype=torch.int32, device="cuda")
+    counts, offsets, pos, route_at = ops.moe_dispatch_plan(ids, 4)
+    torch.cuda.synchronize()
+    assert counts.cpu().tolist() == [1, 2, 0, 1] and offsets.cpu().tolist() == [0, 1, 3, 3, 4]
+    assert pos.cpu().tolist() == [3, 1, -1, 0, -1, 2]
+    assert route_at.cpu().tolist() == [3, 1, 5, 0, -1, -1]
+    x = torch.arange(6 * 8, dtype=torch.float32, device="cuda").reshape(6, 8) + 1
+    rows, = ops.gather_rows([x], route_at, div=1)
+    assert torch.equal(rows[:4].cpu(), x.cpu()[[3, 1, 5, 0]]) and torch.count_nonzero(rows[4:]) == 0
+    y, y32 = ops.moe_combine(x[:4].bfloat16().repeat(1, 1).contiguous(), pos, None, 3, 2, want_f32=True)
+    xb = x[:4].bfloat16().float().cpu()
+    assert torch.equal(y32.cpu(), torch.stack([xb[3] + xb[1], xb[0], xb[2]]))   # routes (1,0) and (2,0) contribute nothing
+    code = ops.device_status()
+    assert code[0] == 3 and code[1] == 60
+    with pytest.raises(_lib.PtoError):
+        ops.moe_dispatch_plan(ids, 4)
+        torch.cuda.synchronize()
+        ops.check_device_status()
+    assert ops.device_status()[0] == 0                     # reading cleared it
 
 
 def test_combine_matches_reference_golden(golden):
@@ -155,6 +197,64 @@ def test_grouped_fp8_gemms_match_oracle(experts, hidden, inter, rows_per):
         assert (got - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-6
 
 
+def _pow2(shape, lo, hi, g):
+    """Random powers of two 2^lo .. 2^hi."""
+    return torch.pow(2.0, torch.randint(lo, hi + 1, shape, generator=g).float())
+
+
+@pytest.mark.parametrize("hidden,inter,rows_per", [(7168, 256, [130, 1, 0, 260]), (2048, 512, [128, 77])])
+def test_expert_gemm_exact_known_answer(hidden, inter, rows_per):
+    """Known-answer test in the style of the reference's MX matmul test
+    (tests/st/runtime/ops/test_matmul_mx.py:154-165, 283: integer-valued e4m3 operands, power-of-two scales,
+    rtol = atol = 0).  Every partial sum is an exactly representable fp32 number whatever the summation order,
+    so the grouped GEMM must equal the oracle bit for bit -- in the plain mode (the down projection; K = 2048
+    runs the six-stage ring, K = 7168 the four-stage one) and in the SwiGLU mode, where positive gate operands
+    put every gate value far above the point at which sigmoid(g) rounds to 1, so that silu(g) * u = g * u."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(hidden + inter)
+    experts, rows = len(rows_per), sum(rows_per)
+    off = torch.tensor([0] + list(torch.tensor(rows_per).cumsum(0)), dtype=torch.int32)
+    # plain mode: out = bf16(acc * route_w), signed operands
+    x = torch.randint(-2, 3, (rows, hidden), generator=g).float()
+    xs = _pow2((rows, hidden // 128), -1, 2, g)
+    w = torch.randint(-2, 3, (experts, hidden, inter), generator=g).float()            # x @ W layout [K, N]
+    ws = _pow2((experts, hidden // 128, inter // 128), -2, 1, g)
+    route_w = _pow2((rows,), -2, 0, g)
+    xq, wq = x.to(torch.float8_e4m3fn), w.to(torch.float8_e4m3fn)
+    w_kmajor = wq.view(torch.uint8).transpose(1, 2).contiguous().view(torch.float8_e4m3fn).cuda()
+    out = ops.moe_expert_gemm(False, w_kmajor, ws.transpose(1, 2).contiguous().cuda(), xq.cuda(), xs.cuda(), off.cuda(),
+                              route_w.cuda())
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    for e in range(experts):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if lo == hi:
+            continue
+        ref = (omoe.fp8_gemm(xq[lo:hi], xs[lo:hi], wq[e], ws[e]) * route_w[lo:hi, None]).bfloat16()
+        assert torch.equal(out[lo:hi].cpu().view(torch.int16), ref.view(torch.int16)), (e, (out[lo:hi].cpu().float() - ref.float()).abs().max())
+    # SwiGLU mode: gate operands positive (so g >= K/2 >> 17 and sigmoid(g) == 1 in fp32), up weights signed
+    xp = torch.randint(1, 3, (rows, hidden), generator=g).float()
+    wg = torch.randint(1, 3, (experts, hidden, inter), generator=g).float()
+    wu = torch.randint(-2, 3, (experts, hidden, inter), generator=g).float()
+    sg, su = _pow2((experts, hidden // 128, inter // 128), -1, 0, g), _pow2((experts, hidden // 128, inter // 128), -2, 0, g)
+    xs1 = _pow2((rows, hidden // 128), 0, 1, g)
+    xpq = xp.to(torch.float8_e4m3fn)
+    pk = _pack(dict(wg=wg.to(torch.float8_e4m3fn), sg=sg, wu=wu.to(torch.float8_e4m3fn), su=su,
+                    wd=torch.zeros(experts, inter, 128).to(torch.float8_e4m3fn), sd=torch.ones(experts, inter // 128, 1)))
+    act = ops.moe_expert_gemm(True, pk["w_gu"], pk["s_gu"], xpq.cuda(), xs1.cuda(), off.cuda())
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    for e in range(experts):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if lo == hi:
+            continue
+        gate = omoe.fp8_gemm(xpq[lo:hi], xs1[lo:hi], wg[e].to(torch.float8_e4m3fn), sg[e])
+        up = omoe.fp8_gemm(xpq[lo:hi], xs1[lo:hi], wu[e].to(torch.float8_e4m3fn), su[e])
+        assert gate.min() > 20
+        ref = (gate * torch.sigmoid(gate) * up).bfloat16()
+        assert torch.equal(act[lo:hi].cpu().view(torch.int16), ref.view(torch.int16)), (e, (act[lo:hi].cpu().float() - ref.float()).abs().max())
+
+
 def test_expert_gemm_is_reproducible_under_stream_concurrency():
     """The grouped GEMM has no atomics: repeated launches on the same operands must give identical bits, also
     while a second stream runs the same kernel (the shared expert does in the layer).  Long K (7168, the
@@ -189,6 +289,22 @@ def test_expert_gemm_is_reproducible_under_stream_concurrency():
     torch.cuda.synchronize()
     ops.check_device_status()
     assert torch.isfinite(first_y.float()).all()
+    # ... and the bits that repeat are the right ones: three experts (481, 129 and 1 rows) against the oracle
+    xq_h, xs_h, offs = xq.cpu(), xs.cpu(), off.cpu().tolist()
+    aq_h, as_h = (v.cpu() for v in ops.quantize_rows(first_a))
+    for e in (1, 4, 11):
+        lo, hi = offs[e], offs[e + 1]
+        w_e = w_gu[e].cpu().view(torch.uint8).t().contiguous().view(torch.float8_e4m3fn)      # [hidden, 2*inter]
+        s_e = s_gu[e].cpu().t().contiguous()
+        gu = omoe.fp8_gemm(xq_h[lo:hi], xs_h[lo:hi], w_e, s_e)
+        gate, up = gu[:, :inter], gu[:, inter:]
+        act = (gate * torch.sigmoid(gate) * up).bfloat16().float()
+        got = first_a[lo:hi].cpu().float()
+        assert (got - act).abs().max() <= 1e-2 * act.abs().max() + 1e-7, e
+        wd_e = w_d[e].cpu().view(torch.uint8).t().contiguous().view(torch.float8_e4m3fn)      # [inter, hidden]
+        ref = omoe.fp8_gemm(aq_h[lo:hi], as_h[lo:hi], wd_e, s_d[e].cpu().t().contiguous())
+        got = first_y[lo:hi].cpu().float()
+        assert (got - ref).abs().max() <= 1e-2 * ref.abs().max() + 1e-6, e
 
 
 def _layer_vs_oracle(tokens, hidden, inter, experts, topk, seed):

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import oracle
-from oracle import ep, ffn, gather, layer, moe
+from oracle import ep, ffn, gather, layer, matmul_mx, moe
 from oracle import paged_attention as pa
 
 PA_CASES = ["pa04_aligned", "pa04_unaligned", "pa04_ragged", "pa04_h64_b64", "pa04_tiny"]
@@ -153,3 +153,35 @@ def test_against_reference_tree_when_present():
              config=cfg)
     ns["golden"](t)
     assert torch.equal(_run_pa(t), t["out"])
+
+
+def test_rope_tables_and_rotation_fixture(golden):
+    """cos/sin tables and the rotate-half of the reference's llama test
+    (test_llama_7b_mini_1h.py:83-95, 146-159), bit for bit."""
+    t = golden("rope")
+    cos, sin = layer.rope_tables(t["cos_emb"].shape[0], t["head_dim"], t["theta"])
+    half = t["head_dim"] // 2
+    assert torch.equal(cos[:, :half], t["cos_emb"]) and torch.equal(cos[:, half:], t["cos_emb"])
+    assert torch.equal(sin[:, :half], t["sin_emb"]) and torch.equal(sin[:, half:], t["sin_emb"])
+    assert torch.equal(layer.rope_rotate(t["x"], cos, sin), t["rotated"])
+
+
+def test_matmul_mx_fixture(golden):
+    """The MXFP8 golden and the two physical scale layouts (test_matmul_mx.py:38-131), bit for bit."""
+    t = golden("matmul_mx")
+    a, b = t["a"].view(torch.float8_e4m3fn), t["b"].view(torch.float8_e4m3fn)
+    out = matmul_mx.matmul_mx(a, t["a_scale_codes"], b, t["b_scale_codes"])
+    assert torch.equal(out, t["out"])
+    assert torch.equal(matmul_mx.matmul_mx(a, t["a_scale_codes"], b, t["b_scale_codes"], acc=out), t["out_acc"])
+    assert torch.equal(matmul_mx.pack_a_scale(t["a_scale_codes"]), t["a_scale_packed"])
+    assert torch.equal(matmul_mx.pack_b_scale(t["b_scale_codes"]), t["b_scale_packed"])
+    assert torch.equal(matmul_mx.unpack_a_scale(t["a_scale_packed"]), t["a_scale_codes"])
+    assert torch.equal(matmul_mx.unpack_b_scale(t["b_scale_packed"]), t["b_scale_codes"])
+
+
+def test_quantize_mx_round_trips_within_e4m3_precision():
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(64, 256, generator=g) * 3
+    q, codes = matmul_mx.quantize_mx(x, dim=1)
+    deq = q.float() * matmul_mx.decode_scale(codes).float().repeat_interleave(32, dim=1)
+    assert codes.shape == (64, 8) and (deq - x).abs().max() <= x.abs().max() * 2 ** -3
