@@ -574,10 +574,9 @@ def synthetic_experts(dev, gen, e, hidden, inter, w_std=0.02):
 
 
 def run_moe(args, d: Dist):
-    import torch.distributed as dist
-
     from oracle import moe as omoe
     from pypto_b200 import ops
+    from pypto_b200.comm import Communicator
     from pypto_b200.moe import MoELayer
     pk = peaks()
     T, H, I, E, K = MOE["tokens"], MOE["hidden"], MOE["inter"], MOE["n_experts"], MOE["topk"]
@@ -586,9 +585,9 @@ def run_moe(args, d: Dist):
     gshared = torch.Generator(device=d.dev).manual_seed(12345)       # replicated pieces: same on all ranks
     gate_w = (torch.randn(H, E, device=d.dev, generator=gshared) * 0.02).bfloat16()
     bias = torch.rand(E, device=d.dev, generator=gshared) * 0.2 - 0.1
+    comm = Communicator.from_torch_distributed(device=d.local) if d.world > 1 else None
     layer = MoELayer.from_packed(ops.pack_weight(gate_w), bias, synthetic_experts(d.dev, gen, L, H, I),
-                                 synthetic_experts(d.dev, gshared, 1, H, I), K, n_experts=E,
-                                 group=dist.group.WORLD if d.world > 1 else None)
+                                 synthetic_experts(d.dev, gshared, 1, H, I), K, n_experts=E, comm=comm)
     x = torch.randn(tl, H, device=d.dev, generator=gen).bfloat16()
 
     ms, clocks = timed(lambda: layer.forward(x), d, args.steps, args.warmup)

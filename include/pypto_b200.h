@@ -88,6 +88,12 @@ PTO_API int pto_malloc(pto_worker* w, size_t nbytes, uint64_t* dev_ptr);      /*
 PTO_API int pto_free(pto_worker* w, uint64_t dev_ptr);                        /* worker.py:368-379; unknown or already freed pointers are an error */
 PTO_API int pto_copy_to(pto_worker* w, uint64_t dst_dev, const void* src_host, size_t nbytes);   /* worker.py:381-400 */
 PTO_API int pto_copy_from(pto_worker* w, void* dst_host, uint64_t src_dev, size_t nbytes);       /* worker.py:402-423 */
+/* The same copies enqueued on the worker's stream without waiting for them (a one-shot call stages every
+ * argument, launches, reads back and waits once at the end: runner.py:1459-1462 copies before and after a
+ * run).  The host buffer must stay valid until pto_synchronize / pto_device_status returns; with pageable
+ * host memory the CUDA runtime itself makes the call wait as far as that needs. */
+PTO_API int pto_copy_to_async(pto_worker* w, uint64_t dst_dev, const void* src_host, size_t nbytes);
+PTO_API int pto_copy_from_async(pto_worker* w, void* dst_host, uint64_t src_dev, size_t nbytes);
 PTO_API int pto_synchronize(pto_worker* w);
 PTO_API void* pto_worker_stream(pto_worker* w);
 /* Reads and clears the device error word of the worker's scratch arena:
@@ -101,8 +107,9 @@ PTO_API int pto_worker_scratch(pto_worker* w, size_t min_bytes, uint64_t* dev_pt
 
 /* Registered callables (replaces Worker.register / Worker.run with a ChipCallable:
  * device_runner.py:651-656, worker.py:532-626).  `op_name` names a fused operator:
- * "paged_attention", "paged_gather", "rms_norm", "rope_kv_append", "linear",
- * "ffn_swiglu", "moe_gate_topk", ...  (pto_op_list). */
+ * "paged_attention", "paged_gather", "rms_norm", "ffn_swiglu", "linear", "rope_kv_append", "scope3",
+ * "decoder_layer", "matmul_mx" (pto_op_list; tensor and scalar order beside each adapter in csrc/ops.cpp and
+ * csrc/layer_ops.cpp). */
 PTO_API int pto_register_callable(pto_worker* w, const char* op_name, int32_t* cid);
 PTO_API int pto_unregister_callable(pto_worker* w, int32_t cid);
 PTO_API int pto_run(pto_worker* w, int32_t cid, const pto_task_args* args);

@@ -76,4 +76,4 @@ def quantize_mx(x: torch.Tensor, dim: int):
     e = torch.where(amax > 0, torch.floor(torch.log2(amax)) - 8, torch.zeros_like(amax)).clamp(-127, 127)
     q = (g / torch.pow(2.0, e).unsqueeze(-1)).clamp(-448, 448).reshape(shp).to(torch.float8_e4m3fn)
     codes = (e + 127).to(torch.uint8)
-    return q.movedim(-1, dim), codes.movedim(-1, dim)
+    return q.movedim(-1, dim).contiguous(), codes.movedim(-1, dim).contiguous()

@@ -50,6 +50,8 @@ SIGNATURES = {
     "pto_free": (_i, [_p, C.c_uint64]),
     "pto_copy_to": (_i, [_p, C.c_uint64, _p, _sz]),
     "pto_copy_from": (_i, [_p, _p, C.c_uint64, _sz]),
+    "pto_copy_to_async": (_i, [_p, C.c_uint64, _p, _sz]),
+    "pto_copy_from_async": (_i, [_p, _p, C.c_uint64, _sz]),
     "pto_synchronize": (_i, [_p]),
     "pto_worker_stream": (_p, [_p]),
     "pto_device_status": (_i, [_p, _i32p]),

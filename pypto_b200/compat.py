@@ -8,7 +8,7 @@ import importlib
 import sys
 
 _SUBMODULES = ("language", "language.distributed", "runtime", "backend", "ir", "ir.pass_manager",
-               "ir.compiled_program", "jit")
+               "ir.compiled_program", "ir.distributed_compiled_program", "runtime.runner", "runtime.distributed_runner", "jit")
 
 
 def install(name: str = "pypto") -> None:

@@ -118,6 +118,25 @@ __global__ void rope_kv_append_kernel(const float* __restrict__ qkv, const int* 
   v_cache[row * head_dim + half + i] = __float2bfloat16_rn(vsrc[half + i]);
 }
 
+// Block tables that present a contiguous KV cache -- row = (b * kv_heads + ki) * max_seq + pos, the layout of
+// examples/models/qwen3_jit/kernels/attention.py:72 -- to the paged kernels:
+//   seq_table [batch]                          one block of max_seq tokens per sequence (for the cache append)
+//   head_table [batch * kv_heads, blocks]      every (sequence, kv head) as its own single-head sequence of
+//   head_lens [batch * kv_heads]               128-token blocks (for the attention kernel)
+__global__ void contiguous_cache_tables_kernel(const int* __restrict__ seq_lens, int batch, int kv_heads,
+                                               int blocks_per_seq, int* __restrict__ seq_table,
+                                               int* __restrict__ head_table, int* __restrict__ head_lens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long n = static_cast<long long>(batch) * kv_heads * blocks_per_seq;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    head_table[i] = static_cast<int>(i);
+    if (i < batch) seq_table[i] = static_cast<int>(i);
+    if (i < static_cast<long long>(batch) * kv_heads) head_lens[i] = seq_lens[i / kv_heads];
+  }
+}
+
 // gate_up fp32 [rows, 2 * inter] (gate columns first) -> act bf16 [rows, inter]
 __global__ void swiglu_act_kernel(const float* __restrict__ gate_up, __nv_bfloat16* __restrict__ act, long long rows,
                                   int inter) {
@@ -193,6 +212,16 @@ int rms_norm_launch(const void* x, int x_dtype, const float* gamma, void* out, i
   else
     return fail(kInvalidArgument, "rms_norm: dtypes must be fp32 or bf16");
   return check_cuda(cudaGetLastError(), "rms_norm_kernel launch");
+}
+
+int contiguous_cache_tables_launch(const int32_t* seq_lens, int batch, int kv_heads, int blocks_per_seq,
+                                   int32_t* seq_table, int32_t* head_table, int32_t* head_lens, cudaStream_t stream) {
+  PTO_REQUIRE(seq_lens && seq_table && head_table && head_lens, "contiguous_cache_tables: NULL tensor");
+  PTO_REQUIRE(batch > 0 && kv_heads > 0 && blocks_per_seq > 0, "contiguous_cache_tables: bad sizes");
+  const long long n = static_cast<long long>(batch) * kv_heads * blocks_per_seq;
+  launch_kernel(contiguous_cache_tables_kernel, dim3(grid_for(n, 256)), dim3(256), 0, stream, seq_lens, batch, kv_heads,
+                blocks_per_seq, seq_table, head_table, head_lens);
+  return check_cuda(cudaGetLastError(), "contiguous_cache_tables_kernel launch");
 }
 
 int rope_kv_append_launch(const float* qkv, const int32_t* seq_lens, const float* cos_t, const float* sin_t,

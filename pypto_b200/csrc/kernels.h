@@ -53,6 +53,8 @@ int rope_kv_append_launch(const float* qkv, const int32_t* seq_lens, const float
                           int table_rows, const int32_t* block_table, int max_blocks, void* k_cache, void* v_cache,
                           void* q_out, int batch, int num_heads, int kv_heads, int head_dim, int block_size,
                           long long pool_blocks, int* err, cudaStream_t stream);
+int contiguous_cache_tables_launch(const int32_t* seq_lens, int batch, int kv_heads, int blocks_per_seq,
+                                   int32_t* seq_table, int32_t* head_table, int32_t* head_lens, cudaStream_t stream);
 int swiglu_act_launch(const float* gate_up, void* act, long long rows, int inter, cudaStream_t stream);
 int cast_launch(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream);
 int pack_weight_launch(const void* src, int src_dtype, void* dst, int k, int n, cudaStream_t stream);

@@ -155,6 +155,11 @@ const OpEntry kOps[] = {
     {"paged_gather", op_paged_gather},
     {"rms_norm", op_rms_norm},
     {"ffn_swiglu", op_ffn_swiglu},
+    {"linear", op_linear},
+    {"rope_kv_append", op_rope_kv_append},
+    {"scope3", op_scope3},
+    {"decoder_layer", op_decoder_layer},
+    {"matmul_mx", op_matmul_mx},
 };
 
 }  // namespace

@@ -216,6 +216,22 @@ int pto_copy_from(pto_worker* h, void* dst_host, uint64_t src_dev, size_t nbytes
   return pto::kOk;
 }
 
+int pto_copy_to_async(pto_worker* h, uint64_t dst_dev, const void* src_host, size_t nbytes) {
+  PTO_WORKER(h);
+  if (nbytes == 0) return pto::kOk;
+  if (src_host == nullptr || dst_dev == 0) return pto::fail(pto::kInvalidArgument, "copy_to_async: NULL pointer");
+  PTO_CUDA(cudaMemcpyAsync(reinterpret_cast<void*>(dst_dev), src_host, nbytes, cudaMemcpyHostToDevice, w->stream));
+  return pto::kOk;
+}
+
+int pto_copy_from_async(pto_worker* h, void* dst_host, uint64_t src_dev, size_t nbytes) {
+  PTO_WORKER(h);
+  if (nbytes == 0) return pto::kOk;
+  if (dst_host == nullptr || src_dev == 0) return pto::fail(pto::kInvalidArgument, "copy_from_async: NULL pointer");
+  PTO_CUDA(cudaMemcpyAsync(dst_host, reinterpret_cast<const void*>(src_dev), nbytes, cudaMemcpyDeviceToHost, w->stream));
+  return pto::kOk;
+}
+
 int pto_synchronize(pto_worker* h) {
   PTO_WORKER(h);
   PTO_CUDA(cudaStreamSynchronize(w->stream));

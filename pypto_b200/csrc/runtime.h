@@ -40,4 +40,11 @@ struct Worker {
 
 OpFn find_op(const char* name);
 
+// layer_ops.cpp: callables composed of several kernels
+int op_scope3(Worker* w, const pto_task_args* a);
+int op_decoder_layer(Worker* w, const pto_task_args* a);
+int op_linear(Worker* w, const pto_task_args* a);
+int op_rope_kv_append(Worker* w, const pto_task_args* a);
+int op_matmul_mx(Worker* w, const pto_task_args* a);
+
 }  // namespace pto

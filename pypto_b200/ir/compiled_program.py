@@ -117,19 +117,18 @@ class CompiledProgram:
                 ptr = worker._stage_alloc(max(nbytes, 1))
                 staged.append((p, a, ptr, nbytes))
                 if p.direction is not Direction.Out and p.name not in plan.get("host_only", ()):
-                    worker.copy_to(ptr, a, nbytes)
+                    worker._copy_to_async(ptr, a, nbytes)
                 dev[p.name] = DeviceTensor(ptr, tuple(a.shape) or (1,), a.dtype)
             self.fused.launch(worker, dev, host, plan)
             for p, a, ptr, nbytes in staged:
-                if p.direction is not Direction.In:
-                    worker.copy_from(a, ptr, nbytes)   # synchronises the worker's stream
-            if not any(p.direction is not Direction.In for p, *_ in staged):
-                worker.synchronize()
+                if p.direction is not Direction.In or p.name in plan.get("copy_back", ()):
+                    worker._copy_from_async(a, ptr, nbytes)
+            # one wait for the whole call; it also reads the device error word, so a clamped block id, a refused
+            # index or a wait that ran out raises here instead of returning a silently wrong output
+            worker.device_status()
         finally:
             for p, a, ptr, nbytes in staged:
                 worker._stage_release(ptr, max(nbytes, 1))
-        code = worker.device_status() if plan.get("check_status", False) else None
-        del code
         if returned:
             return returned[0] if len(returned) == 1 else tuple(returned)
         return None
@@ -162,7 +161,7 @@ def compile(program, *, output_dir=None, strategy=OptimizationStrategy.Default, 
         raise BackendUnavailable(f"platform {platform!r} targets {bt.name}: its code generator and toolchain are "
                                  "not part of this build; compile for platform 'b200'")
     if distributed_config is not None:
-        raise NotImplementedError("distributed programs run through pypto_b200.moe (one process per GPU)")
+        return _compile_distributed(program, platform, distributed_config)
     if isinstance(program, Program):
         entry = program.entry
     elif isinstance(program, Function):
@@ -180,3 +179,19 @@ def compile(program, *, output_dir=None, strategy=OptimizationStrategy.Default, 
         if fused is None:
             raise
     return CompiledProgram(entry, fused, platform, bt, program)
+
+
+def _compile_distributed(program, platform: str, distributed_config):
+    """Level-3 compile (python/pypto/ir/compile.py with ``distributed_config=``): resolve the HOST-level
+    orchestrator of ``program`` to the rank-side fused body."""
+    from ..runtime import distributed_programs
+    from .distributed_compiled_program import DistributedCompiledProgram, DistributedConfig
+    if not isinstance(distributed_config, DistributedConfig):
+        raise TypeError(f"distributed_config must be a DistributedConfig, got {type(distributed_config).__name__}")
+    if not isinstance(program, Program):
+        raise TypeError(f"a distributed compile expects a @pl.program class, got {type(program).__name__}")
+    entry = program.host_entry or program.entry
+    if entry is None:
+        raise ValueError("program has no functions")
+    fused = distributed_programs.lookup(entry)
+    return DistributedCompiledProgram(entry, fused, platform, distributed_config, program)

@@ -40,6 +40,8 @@ BOOL = DataType("BOOL", torch.bool)
 INDEX = DataType("INDEX", torch.int64)
 FP8E4M3FN = DataType("FP8E4M3FN", getattr(torch, "float8_e4m3fn", torch.uint8))
 FP8E5M2 = DataType("FP8E5M2", getattr(torch, "float8_e5m2", torch.uint8))
+FP8E8M0 = DataType("FP8E8M0", getattr(torch, "float8_e8m0fnu", torch.uint8))      # MX scale codes
+FP4 = DataType("FP4", getattr(torch, "float4_e2m1fn_x2", torch.uint8))
 
 _BY_TORCH = {d.torch_dtype: d for d in (FP32, FP16, BF16, INT8, INT16, INT32, INT64, UINT8, BOOL, FP8E4M3FN)}
 
@@ -67,6 +69,8 @@ class MemorySpace(enum.Enum):
     Right = 4
     Acc = 5
     Bias = 6
+    LeftScale = 7
+    RightScale = 8
 
 
 Mem = MemorySpace
@@ -97,6 +101,17 @@ class PadValue(enum.Enum):
     min = 3
 
 
+class TensorLayout(enum.Enum):
+    """Physical layouts a tensor annotation can name (third item of ``pl.Tensor[[...], dtype, layout]``); the MX
+    scale layouts are the ones of tests/st/runtime/ops/test_matmul_mx.py:38-101."""
+    ND = 0
+    MX_A_ZZ = 1
+    MX_B_NN = 2
+
+
+MX_A_ZZ, MX_B_NN = TensorLayout.MX_A_ZZ, TensorLayout.MX_B_NN
+
+
 class _Dynamic:
     def __init__(self, name):
         self.name = name
@@ -114,9 +129,10 @@ class TensorType:
 
     kind = "tensor"
 
-    def __init__(self, shape=None, dtype: DataType | None = None):
+    def __init__(self, shape=None, dtype: DataType | None = None, layout: "TensorLayout | None" = None):
         self.shape = None if shape is None else tuple(shape)
         self.dtype = dtype
+        self.layout = layout
 
     def __repr__(self):
         return f"pl.Tensor[{list(self.shape) if self.shape is not None else '?'}, {self.dtype}]"
@@ -128,7 +144,7 @@ class _TensorMeta(type):
             item = (item,)
         shape = item[0] if item and isinstance(item[0], (list, tuple)) else None
         dt = next((x for x in item if isinstance(x, DataType)), None)
-        t = TensorType(shape, dt)
+        t = TensorType(shape, dt, next((x for x in item if isinstance(x, TensorLayout)), None))
         t.kind = cls.kind
         return t
 
@@ -242,7 +258,13 @@ class Program:
         self.__name__, self.__doc__ = cls.__name__, cls.__doc__
         self.functions = {k: v for k, v in vars(cls).items() if isinstance(v, Function)}
         orch = [f for f in self.functions.values() if f.type is FunctionType.Orchestration]
-        self.entry = orch[-1] if orch else (list(self.functions.values())[-1] if self.functions else None)
+        # a level-3 program's entry is its HOST-level orchestrator (@pl.function(level=pl.Level.HOST,
+        # role=pl.Role.Orchestrator), tests/st/distributed/test_l3_ep_dispatch_combine.py:455)
+        host = [f for f in self.functions.values()
+                if f.attrs.get("level") is Level.HOST and f.attrs.get("role") is Role.Orchestrator]
+        self.host_entry = host[-1] if host else None
+        self.entry = self.host_entry or (orch[-1] if orch else
+                                         (list(self.functions.values())[-1] if self.functions else None))
 
     def __repr__(self):
         return f"<pl.program {self.name} entry={self.entry.name if self.entry else None}>"

@@ -19,6 +19,8 @@ _DT = {torch.float32: _lib.PTO_FP32, torch.bfloat16: _lib.PTO_BF16, torch.float1
        torch.int32: _lib.PTO_INT32, torch.int64: _lib.PTO_INT64, torch.uint8: _lib.PTO_UINT8}
 if hasattr(torch, "float8_e4m3fn"):
     _DT[torch.float8_e4m3fn] = _lib.PTO_FP8E4M3
+if hasattr(torch, "float8_e8m0fnu"):
+    _DT[torch.float8_e8m0fnu] = _lib.PTO_UINT8          # E8M0 scale codes travel as bytes
 
 _scratch: dict[tuple[int, int], torch.Tensor] = {}
 

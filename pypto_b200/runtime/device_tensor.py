@@ -37,3 +37,22 @@ class DeviceTensor:
 
     def __repr__(self):
         return f"DeviceTensor(data_ptr=0x{self.data_ptr:x}, shape={self.shape}, dtype={self.dtype})"
+
+
+class StackedDeviceTensor:
+    """A rank-sharded resident tensor: shard i (shape ``full_shape[1:]``) lives on worker ``worker_ids[i]`` of
+    a ``DistributedWorker`` (python/pypto/runtime/device_tensor.py of the reference; made by
+    ``DistributedWorker.alloc_stacked_tensor``).  ``handle`` names the shards inside the rank processes."""
+
+    __slots__ = ("handle", "full_shape", "dtype", "worker_ids", "owner")
+
+    def __init__(self, handle: int, full_shape, dtype: torch.dtype, worker_ids, owner=None):
+        self.handle, self.full_shape, self.dtype = handle, tuple(full_shape), dtype
+        self.worker_ids, self.owner = tuple(worker_ids), owner
+
+    @property
+    def shape(self):
+        return self.full_shape
+
+    def __repr__(self):
+        return f"StackedDeviceTensor(shape={self.full_shape}, dtype={self.dtype}, workers={self.worker_ids})"

@@ -178,7 +178,90 @@ class RmsNormOp(FusedOp):
         worker.launch("rms_norm", [dev[n] for n in self.names], plan["scalars"])
 
 
-REGISTRY: list[FusedOp] = [PagedAttentionOp(), PagedAttentionSpmdOp(), PagedGatherOp(), FfnSwigluOp(), RmsNormOp()]
+def _f32_bits(v: float) -> int:
+    return struct.unpack("I", struct.pack("f", float(v)))[0]
+
+
+class Qwen3DecodeOp(FusedOp):
+    """``qwen3_decode(hidden_states, input_rms_weight, wq, wk, wv, seq_lens, rope_cos, rope_sin, k_cache, v_cache, wo,
+    post_rms_weight, w_gate, w_up, w_down, out)`` (examples/models/qwen3_jit/qwen3_decode.py:49-112): one decode
+    step of the layer, with grouped-query attention over the contiguous KV cache in the place the example leaves
+    open (:95-99).  The caches are updated in place at position seq_len - 1, so they are read back like outputs.
+    eps is the example's constant (qwen3_jit/config.py: EPS = 1e-6), the softmax scale 1 / sqrt(head_dim)."""
+
+    op_names = ("decoder_layer",)
+    names = ("hidden_states", "input_rms_weight", "wq", "wk", "wv", "seq_lens", "rope_cos", "rope_sin", "k_cache",
+             "v_cache", "wo", "post_rms_weight", "w_gate", "w_up", "w_down", "out")
+    eps = 1e-6
+
+    def matches(self, entry) -> bool:
+        return entry.name == "qwen3_decode" and tuple(p.name for p in entry.params) == self.names
+
+    def plan(self, compiled, host, worker):
+        h, cos, wk = host["hidden_states"], host["rope_cos"], host["wk"]
+        if h.dtype != torch.bfloat16 or host["out"].dtype != torch.bfloat16:
+            raise TypeError("qwen3_decode: hidden_states and out must be bfloat16")
+        batch, max_seq, hd = h.shape[0], cos.shape[0], cos.shape[1]
+        kvh = wk.shape[1] // hd
+        if _numel(host["k_cache"]) != batch * kvh * max_seq * hd:
+            raise ValueError("qwen3_decode: k_cache must hold batch * kv_heads * max_seq rows of head_dim")
+        if max_seq % 128:
+            raise ValueError("qwen3_decode: the cache length per sequence must be a multiple of 128")
+        return dict(scalars=[_f32_bits(self.eps), 0], copy_back=("k_cache", "v_cache"))
+
+    def launch(self, worker, dev, host, plan):
+        worker.launch("decoder_layer", [dev[n] for n in self.names], plan["scalars"])
+
+
+class Scope3Op(FusedOp):
+    """``scope3(attn_out, hidden_states, wo, post_rms_weight, w_gate, w_up, w_down, out)``
+    (tests/st/runtime/framework_and_models/test_qwen3_decode_scope3_mixed.py:207-250; golden :256-287)."""
+
+    op_names = ("scope3",)
+    names = ("attn_out", "hidden_states", "wo", "post_rms_weight", "w_gate", "w_up", "w_down", "out")
+    eps = 1e-6
+
+    def matches(self, entry) -> bool:
+        return entry.name == "scope3" and tuple(p.name for p in entry.params) == self.names
+
+    def plan(self, compiled, host, worker):
+        if any(host[n].dtype != torch.bfloat16 for n in ("attn_out", "hidden_states", "wo", "w_gate", "w_up", "w_down", "out")):
+            raise TypeError("scope3: activations and weights must be bfloat16")
+        return dict(scalars=[_f32_bits(self.eps)])
+
+    def launch(self, worker, dev, host, plan):
+        worker.launch("scope3", [dev[n] for n in self.names], plan["scalars"])
+
+
+class MatmulMxOp(FusedOp):
+    """``orchestrator(a, a_scale, b, b_scale, out, out_acc)`` of the reference's MX matmul program
+    (tests/st/runtime/ops/test_matmul_mx.py:203-226): out = matmul_mx(a, a_scale, b, b_scale), out_acc =
+    matmul_mx_acc(out, ...).  The scale layouts come from the annotations (``pl.MX_A_ZZ`` / ``pl.MX_B_NN``)."""
+
+    op_names = ("matmul_mx",)
+    names = ("a", "a_scale", "b", "b_scale", "out", "out_acc")
+
+    def matches(self, entry) -> bool:
+        return tuple(p.name for p in entry.params) == self.names
+
+    def plan(self, compiled, host, worker):
+        a, b = host["a"], host["b"]
+        if a.element_size() != 1 or b.element_size() != 1:
+            raise TypeError("matmul_mx: operands must be FP8 (the FP4 left operand of the reference's second case is "
+                            "cast to FP8E4M3FN before it reaches the matmul)")
+        if a.dtype != torch.float8_e4m3fn or b.dtype != torch.float8_e4m3fn:
+            raise TypeError("matmul_mx: operands must be float8_e4m3fn")
+        by_name = {p.name: p for p in compiled.params}
+        la = 1 if getattr(by_name["a_scale"].type, "layout", None) is pl.MX_A_ZZ else 0
+        lb = 2 if getattr(by_name["b_scale"].type, "layout", None) is pl.MX_B_NN else 0
+        return dict(scalars=[la, lb])
+
+    def launch(self, worker, dev, host, plan):
+        worker.launch("matmul_mx", [dev[n] for n in self.names], plan["scalars"])
+
+
+REGISTRY: list[FusedOp] = [PagedAttentionOp(), PagedAttentionSpmdOp(), PagedGatherOp(), FfnSwigluOp(), RmsNormOp(),
+                           Qwen3DecodeOp(), Scope3Op(), MatmulMxOp()]
 
 
 def lookup(entry) -> FusedOp:

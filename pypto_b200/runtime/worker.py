@@ -131,6 +131,12 @@ class ChipWorker:
         dst = dst_host.data_ptr() if isinstance(dst_host, torch.Tensor) else int(dst_host)
         _lib.check(_lib.load().pto_copy_from(self._handle, dst, src_dev, nbytes))
 
+    def _copy_to_async(self, dst_dev: int, src_host: torch.Tensor, nbytes: int) -> None:
+        _lib.check(_lib.load().pto_copy_to_async(self._handle, dst_dev, src_host.data_ptr(), nbytes))
+
+    def _copy_from_async(self, dst_host: torch.Tensor, src_dev: int, nbytes: int) -> None:
+        _lib.check(_lib.load().pto_copy_from_async(self._handle, dst_host.data_ptr(), src_dev, nbytes))
+
     def alloc_tensor(self, shape, dtype, *, init: torch.Tensor | None = None, worker_id: int = 0) -> DeviceTensor:
         """malloc + optional upload; rolled back if the upload fails (runtime_base.py:228-269)."""
         self._require_ready("alloc_tensor")

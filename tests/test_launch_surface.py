@@ -158,3 +158,23 @@ def test_reference_examples_import_and_compile_unchanged():
                                              max_num_blocks_per_req=4)
     c = ir.compile(prog, platform="b200")
     assert c.entry.name == "paged_attention" and len(c.params) == 7
+
+
+def test_reference_qwen3_decode_example_imports_and_compiles_unchanged():
+    """examples/models/qwen3_jit/qwen3_decode.py (a package with relative imports and @pl.jit.inline kernels)
+    through the ``pypto`` alias: its 16-parameter entry resolves to the registered decoder-layer callable."""
+    import importlib
+    import sys
+
+    import ref_extract
+    if not ref_extract.available():
+        pytest.skip("reference tree not mounted")
+    from pypto_b200 import compat, ir
+    compat.install()
+    sys.path.insert(0, ref_extract.REFERENCE_ROOT)
+    try:
+        mod = importlib.import_module("examples.models.qwen3_jit.qwen3_decode")
+    finally:
+        sys.path.remove(ref_extract.REFERENCE_ROOT)
+    compiled = ir.compile(mod.qwen3_decode, platform="b200")
+    assert compiled.op_names == ("decoder_layer",) and len(compiled.params) == 16
