@@ -23,6 +23,8 @@ class SwiGLUFFN:
     once.  fp32 inputs are cast to bf16 operands (fp32 accumulation), which the 2e-2 bar of the
     workload definition allows."""
 
+    launches_per_call = 3   # kernels of one call with fp32 input: cast, gate/up GEMM (+ SwiGLU), down GEMM
+
     def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor):
         self.hidden, self.inter = w_gate.shape
         self.n_out = w_down.shape[1]
@@ -38,6 +40,10 @@ class SwiGLUFFN:
 
 
 class DecoderLayer:
+    # kernels of one step: RMSNorm, QKV GEMM, RoPE + append, attention, merge, O GEMM, RMSNorm, gate/up GEMM,
+    # SwiGLU, down GEMM, cast
+    launches_per_step = 11
+
     def __init__(self, t: dict, *, num_heads: int, kv_heads: int, head_dim: int, block_size: int, eps: float,
                  scale: float):
         """``t`` holds device tensors wq/wk/wv/wo/w_gate/w_up/w_down in the reference's
