@@ -197,6 +197,10 @@ PTO_API int pto_paged_gather(const void* src, int64_t src_rows, int64_t src_cols
 PTO_API int pto_pack_weight(const void* w, int w_dtype, void* packed, int k, int n, void* stream);
 /* fp32 <-> bf16 element cast. */
 PTO_API int pto_cast(const void* in, int in_dtype, void* out, int out_dtype, int64_t n, void* stream);
+/* The same with a side job of the same launch: `zero` (16-byte aligned, zero_bytes a multiple of 16) is
+ * cleared -- e.g. the fp32 output that pto_ffn_swiglu then accumulates into. */
+PTO_API int pto_cast_zero(const void* in, int in_dtype, void* out, int out_dtype, int64_t n, void* zero,
+                          size_t zero_bytes, void* stream);
 
 /* out[m, n] = x[m, k] @ W (accumulate = 0) or out += x @ W (accumulate = 1; out then holds
  * e.g. the residual), x bf16, W packed [n, k] bf16, out fp32, fp32 accumulation.  Replaces the
@@ -211,7 +215,10 @@ PTO_API int pto_linear(const void* x, const void* w_packed, void* out, int m, in
  * (examples/models/qwen3_jit/kernels/mlp.py:23-61, kernels/projection.py:146-177).
  *   x bf16 [m, k]; w_gate_up packed [2*inter, k] (gate rows, then up rows);
  *   w_down packed [n_out, inter]; out fp32 [m, n_out];
- *   workspace: device buffer of pto_ffn_swiglu_workspace_bytes(m, inter), 256-byte aligned. */
+ *   workspace: device buffer of pto_ffn_swiglu_workspace_bytes(m, inter), 256-byte aligned.  With at most
+ *   128 rows both GEMMs run in ONE cooperative launch whose CTAs hand the activation over through counters
+ *   in the first 8 KB of the workspace: zero those bytes once after allocating it and leave them to the
+ *   operator afterwards (or clear them before every call); one call at a time per workspace. */
 PTO_API size_t pto_ffn_swiglu_workspace_bytes(int m, int inter);
 PTO_API int pto_ffn_swiglu(const void* x, const void* w_gate_up, const void* w_down, void* out, int m, int k,
                            int inter, int n_out, void* workspace, size_t workspace_bytes, int accumulate,

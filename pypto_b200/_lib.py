@@ -67,6 +67,7 @@ SIGNATURES = {
     "pto_paged_attention_static": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i64, _i, _f, _p, _p]),
     "pto_pack_weight": (_i, [_p, _i, _p, _i, _i, _p]),
     "pto_cast": (_i, [_p, _i, _p, _i, _i64, _p]),
+    "pto_cast_zero": (_i, [_p, _i, _p, _i, _i64, _p, _sz, _p]),
     "pto_linear": (_i, [_p, _p, _p, _i, _i, _i, _i, _p, _p]),
     "pto_ffn_swiglu_workspace_bytes": (_sz, [_i, _i]),
     "pto_ffn_swiglu": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p, _sz, _i, _p, _p]),

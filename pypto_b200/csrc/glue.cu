@@ -152,13 +152,17 @@ __global__ void swiglu_act_kernel(const float* __restrict__ gate_up, __nv_bfloat
   }
 }
 
+// out = cast(in); optional side job of the same launch: `zero` (16-byte aligned, zero_vec uint4 words) is
+// cleared, e.g. the fp32 accumulator of the GEMM that follows.
 template <typename TI, typename TO>
-__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, long long n) {
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, long long n, uint4* __restrict__ zero,
+                            long long zero_vec) {
   pdl_launch_dependents();
   pdl_wait();
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x)
-    out[i] = from_f32<TO>(to_f32(in[i]));
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nth = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = tid; i < n; i += nth) out[i] = from_f32<TO>(to_f32(in[i]));
+  for (long long i = tid; i < zero_vec; i += nth) zero[i] = make_uint4(0, 0, 0, 0);
 }
 
 // src [K, N] row-major -> dst [N, K] bf16; 32x32 tiles through shared memory.
@@ -247,13 +251,22 @@ int swiglu_act_launch(const float* gate_up, void* act, long long rows, int inter
 }
 
 int cast_launch(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream) {
+  return cast_zero_launch(in, in_dtype, out, out_dtype, n, nullptr, 0, stream);
+}
+
+int cast_zero_launch(const void* in, int in_dtype, void* out, int out_dtype, long long n, void* zero,
+                     size_t zero_bytes, cudaStream_t stream) {
   PTO_REQUIRE(in && out && n >= 0, "cast: bad arguments");
-  if (n == 0) return kOk;
-  const int g = grid_for(n, 256);
+  PTO_REQUIRE(zero_bytes == 0 || (zero && (reinterpret_cast<uintptr_t>(zero) & 15) == 0 && zero_bytes % 16 == 0),
+              "cast: the region to clear must be 16-byte aligned and a multiple of 16 bytes");
+  const long long zv = static_cast<long long>(zero_bytes / 16);
+  if (n == 0 && zv == 0) return kOk;
+  const int g = grid_for(n > zv * 4 ? n : zv * 4, 256);
+  uint4* z = static_cast<uint4*>(zero);
   if (in_dtype == PTO_FP32 && out_dtype == PTO_BF16)
-    launch_kernel(cast_kernel<float, __nv_bfloat16>, dim3(g), dim3(256), 0, stream, static_cast<const float*>(in), static_cast<__nv_bfloat16*>(out), n);
+    launch_kernel(cast_kernel<float, __nv_bfloat16>, dim3(g), dim3(256), 0, stream, static_cast<const float*>(in), static_cast<__nv_bfloat16*>(out), n, z, zv);
   else if (in_dtype == PTO_BF16 && out_dtype == PTO_FP32)
-    launch_kernel(cast_kernel<__nv_bfloat16, float>, dim3(g), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), static_cast<float*>(out), n);
+    launch_kernel(cast_kernel<__nv_bfloat16, float>, dim3(g), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(in), static_cast<float*>(out), n, z, zv);
   else
     return fail(kInvalidArgument, "cast: only fp32 <-> bf16");
   return check_cuda(cudaGetLastError(), "cast_kernel launch");

@@ -46,6 +46,12 @@ int ffn_swiglu_launch(const void* x, const void* w_gate_up, const void* w_down, 
                       int n_out, void* workspace, size_t workspace_bytes, int accumulate, int* err,
                       cudaStream_t stream);
 
+// ffn_fused.cu
+bool ffn_fused_ok(int m, int k, int inter, int n_out);
+size_t ffn_fused_workspace_bytes(int inter);
+int ffn_fused_launch(const void* x, const void* w_gate_up, const void* w_down, float* out, int m, int k, int inter,
+                     int n_out, void* workspace, size_t workspace_bytes, int* err, cudaStream_t stream);
+
 // glue.cu
 int rms_norm_launch(const void* x, int x_dtype, const float* gamma, void* out, int out_dtype, long long rows,
                     int hidden, float eps, float* copy_f32, void* zero, size_t zero_bytes, cudaStream_t stream);
@@ -57,6 +63,8 @@ int contiguous_cache_tables_launch(const int32_t* seq_lens, int batch, int kv_he
                                    int32_t* seq_table, int32_t* head_table, int32_t* head_lens, cudaStream_t stream);
 int swiglu_act_launch(const float* gate_up, void* act, long long rows, int inter, cudaStream_t stream);
 int cast_launch(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream);
+int cast_zero_launch(const void* in, int in_dtype, void* out, int out_dtype, long long n, void* zero,
+                     size_t zero_bytes, cudaStream_t stream);
 int pack_weight_launch(const void* src, int src_dtype, void* dst, int k, int n, cudaStream_t stream);
 
 // moe_route.cu

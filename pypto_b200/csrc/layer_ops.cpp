@@ -74,6 +74,9 @@ int scope3_body(Worker* w, Arena& a, const void* attn, int q_dim, float* resid, 
   st = rms_norm_launch(resid, PTO_FP32, static_cast<const float*>(tptr(gamma, 4)), post, PTO_BF16, b, hidden, eps,
                        nullptr, nullptr, 0, w->stream);
   if (st != kOk) return st;
+  // the arena is shared with other operators, so the FFN's call counter does not survive between calls: clear it
+  st = check_cuda(cudaMemsetAsync(ws, 0, ws_b < 8192 ? ws_b : 8192, w->stream), "cudaMemsetAsync(ffn header)");
+  if (st != kOk) return st;
   st = ffn_swiglu_launch(post, wgu_p, wd_p, resid, b, hidden, inter, hidden, ws, ws_b, 1, err, w->stream);
   if (st != kOk) return st;
   return cast_launch(resid, PTO_FP32, out_bf16, PTO_BF16, static_cast<long long>(b) * hidden, w->stream);

@@ -60,6 +60,8 @@ bool use_swiglu_epilogue(int m, int inter, int* bn) {
 }  // namespace
 
 size_t ffn_workspace_bytes(int m, int inter) {
+  // decode-sized batches: the one-launch kernel's header, slab counters and activation
+  if (m <= 128 && inter % 64 == 0 && inter >= 64) return ffn_fused_workspace_bytes(inter);
   // bf16 activation [m, inter]; plus fp32 gate|up [m, 2*inter] for the stream-K path
   const size_t act = (static_cast<size_t>(m) * inter * 2 + 255) / 256 * 256;
   int bn;
@@ -78,6 +80,11 @@ int ffn_swiglu_launch(const void* x, const void* w_gate_up, const void* w_down, 
               "ffn_swiglu: sizes must be positive, k and inter multiples of 8");
   PTO_REQUIRE(workspace_bytes >= ffn_workspace_bytes(m, inter), "ffn_swiglu: workspace too small");
   PTO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "ffn_swiglu: workspace must be 256-byte aligned");
+  if (ffn_fused_ok(m, k, inter, n_out)) {
+    // at most 128 rows: both GEMMs in one persistent launch (the workspace header keeps its call counter)
+    if (!accumulate) PTO_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * static_cast<size_t>(m) * n_out, stream));
+    return ffn_fused_launch(x, w_gate_up, w_down, out, m, k, inter, n_out, workspace, workspace_bytes, err, stream);
+  }
   __nv_bfloat16* act = static_cast<__nv_bfloat16*>(workspace);
   int st;
   int bn = 0;

@@ -20,7 +20,7 @@
 // `tcgen05.cp.32x128b.warpx4` and selects the byte with the scale-id field of the instruction.
 //
 // CTA = warp 0 TMA producer, warp 1 MMA issuer (owns tensor memory), warps 2-5 epilogue (one
-// TMEM lane quarter each), warps 6-9 scale loaders.  Tiles of 128 x bn outputs (bn = 128 with two
+// TMEM lane quarter each), warps 6-9 scale loaders (one K block each, in turn).  Tiles of 128 x bn outputs (bn = 128 with two
 // accumulator buffers, or 256 with one) are taken round-robin by persistent CTAs.  Every wait is bounded.
 #include "common.cuh"
 #include "kernels.h"
@@ -114,7 +114,7 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < p.stages; ++i) {
-      mbar_init(&full[i], 1 + kMxScaleWarps);
+      mbar_init(&full[i], 2);   // the TMA producer's expect_tx arrival and one scale-loader warp
       mbar_init(&empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -241,35 +241,52 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   } else {
     // ------------------------------ scale loaders ------------------------------
     // Per stage: 128 left-operand rows and bn right-operand columns, four scale bytes each, packed into one
-    // 32-bit word at its place in the 512-byte chunk of its 128 rows.
-    const int t = threadIdx.x - 6 * 32;   // 0 .. 127
+    // 32-bit word at its place in the 512-byte chunk of its 128 rows.  The four loader warps take K blocks in
+    // turn, so each has four MMA periods for the memory latency of its stage.
+    const int lw = warp - 6;   // 0 .. 3
     uint32_t it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
       const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
       for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+        if ((it & 3u) != static_cast<uint32_t>(lw)) continue;
         const uint32_t s = it % p.stages, round = it / p.stages;
+        const int g0 = kb * 4;
+        // loads first (they do not touch the stage), then the wait for the stage, then the stores
+        uint32_t wa[4], wb[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int row = mt * 128 + j * 32 + lane;
+          if (p.a_layout == PTO_MX_SCALE_LOGICAL && row < p.m && g0 + 4 <= p.kgroups && (p.kgroups & 3) == 0) {
+            wa[j] = *reinterpret_cast<const uint32_t*>(p.a_scale + static_cast<size_t>(row) * p.kgroups + g0);
+          } else {
+            wa[j] = 0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) wa[j] |= a_scale_code(p, row, g0 + g) << (8 * g);
+          }
+        }
+        const int nb_words = static_cast<int>(sfb_chunks) * 4;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          wb[j] = 0;
+          if (j < nb_words) {
+            const int col = nt * p.bn + j * 32 + lane;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) wb[j] |= b_scale_code(p, col, g0 + g) << (8 * g);
+          }
+        }
         if (!mbar_wait_warp(&empty[s], (round & 1u) ^ 1u)) {
           report_error(p.err, kErrBarrierTimeout, 75, static_cast<int>(it));
           ok = false;
           break;
         }
         uint8_t* sf = smem + static_cast<size_t>(s) * stage_bytes + a_bytes + b_bytes;
-        const int g0 = kb * 4;
-        {
-          const int row = mt * 128 + t;
-          uint32_t w = 0;
+        // row r = j * 32 + lane of a 128-row chunk sits at byte (r % 32) * 16 + (r / 32) * 4 = lane * 16 + j * 4
 #pragma unroll
-          for (int g = 0; g < 4; ++g) w |= a_scale_code(p, row, g0 + g) << (8 * g);
-          *reinterpret_cast<uint32_t*>(sf + (t & 31) * 16 + (t >> 5) * 4) = w;
-        }
-        for (uint32_t c = 0; c < sfb_chunks; ++c) {
-          const int col = nt * p.bn + static_cast<int>(c) * 128 + t;
-          uint32_t w = 0;
+        for (int j = 0; j < 4; ++j) *reinterpret_cast<uint32_t*>(sf + lane * 16 + j * 4) = wa[j];
 #pragma unroll
-          for (int g = 0; g < 4; ++g) w |= b_scale_code(p, col, g0 + g) << (8 * g);
-          *reinterpret_cast<uint32_t*>(sf + 512 * (1 + c) + (t & 31) * 16 + (t >> 5) * 4) = w;
-        }
+        for (int j = 0; j < 8; ++j)
+          if (j < nb_words) *reinterpret_cast<uint32_t*>(sf + 512 * (1 + (j >> 2)) + lane * 16 + (j & 3) * 4) = wb[j];
         fence_proxy_async_smem();   // the chunk is read by tcgen05.cp (async proxy)
         __syncwarp();
         if (lane == 0) mbar_arrive(&full[s]);

@@ -141,6 +141,9 @@ int op_ffn_swiglu(Worker* w, const pto_task_args* a) {
   if (st != kOk) return st;
   st = pack_weight_launch(tptr(t[3], dtype_bytes(t[3].dtype)), (int)t[3].dtype, wd, inter, n, w->stream);
   if (st != kOk) return st;
+  // the arena is shared with other operators, so the FFN's call counter does not survive between calls: clear it
+  st = check_cuda(cudaMemsetAsync(ws, 0, ws_b < 8192 ? ws_b : 8192, w->stream), "cudaMemsetAsync(ffn header)");
+  if (st != kOk) return st;
   return ffn_swiglu_launch(xb, gu, wd, static_cast<float*>(tptr(t[4], 4)), m, k, inter, n, ws, ws_b, 0,
                            static_cast<int*>(w->scratch), w->stream);
 }
@@ -234,6 +237,11 @@ int pto_pack_weight(const void* w, int w_dtype, void* packed, int k, int n, void
 
 int pto_cast(const void* in, int in_dtype, void* out, int out_dtype, int64_t n, void* stream) {
   return pto::cast_launch(in, in_dtype, out, out_dtype, n, static_cast<cudaStream_t>(stream));
+}
+
+int pto_cast_zero(const void* in, int in_dtype, void* out, int out_dtype, int64_t n, void* zero, size_t zero_bytes,
+                  void* stream) {
+  return pto::cast_zero_launch(in, in_dtype, out, out_dtype, n, zero, zero_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int pto_linear(const void* x, const void* w_packed, void* out, int m, int n, int k, int accumulate, int32_t* err,

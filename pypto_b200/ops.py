@@ -187,12 +187,21 @@ def pack_weight(w: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+def cast(x: torch.Tensor, dtype: torch.dtype, zero: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 <-> bf16 element cast; ``zero`` (contiguous, 16-byte aligned, a multiple of 16 bytes) is cleared by
+    the same launch."""
     dev = _need_cuda(x)
     out = torch.empty(x.shape, dtype=dtype, device=dev)
+    zb = 0
+    if zero is not None:
+        _need_cuda(zero)
+        zb = zero.numel() * zero.element_size()
+        if zb % 16 or zero.data_ptr() % 16:
+            raise ValueError("cast: the tensor to clear must be 16-byte aligned and a multiple of 16 bytes")
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().pto_cast(x.data_ptr(), dtype_code(x.dtype), out.data_ptr(), dtype_code(dtype),
-                                        x.numel(), _stream_ptr(dev)))
+        _lib.check(_lib.load().pto_cast_zero(x.data_ptr(), dtype_code(x.dtype), out.data_ptr(), dtype_code(dtype),
+                                             x.numel(), zero.data_ptr() if zero is not None else None, zb,
+                                             _stream_ptr(dev)))
     return out
 
 
@@ -243,7 +252,8 @@ def ffn_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, o
     key = (dev.index, _stream_ptr(dev))
     ws = _ffn_ws.get(key)
     if ws is None or ws.numel() < need:
-        ws = _ffn_ws[key] = torch.empty(need, dtype=torch.uint8, device=dev)
+        # zeroed once: the one-launch kernel for small batches keeps its call counter in the first bytes
+        ws = _ffn_ws[key] = torch.zeros(need, dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
         _lib.check(lib.pto_ffn_swiglu(x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), out.data_ptr(), m, k,
                                       inter, n_out, ws.data_ptr(), ws.numel(), 1 if accumulate else 0,

@@ -109,3 +109,34 @@ def test_ffn_64x64_reference_shape():
     exp = offn.ffn_swiglu(x, wg, wu, wd)
     got = SwiGLUFFN(wg.cuda(), wu.cuda(), wd.cuda())(x.cuda())
     _check(got, exp, 2e-2, "ffn 64x64")
+
+
+@pytest.mark.parametrize("m,k,inter,n_out", [(1, 256, 128, 256), (33, 1024, 4096, 1024), (128, 1024, 4096, 1024),
+                                             (32, 512, 14336, 520), (100, 200, 192, 68)])
+def test_one_launch_ffn_repeated_calls_and_residual(m, k, inter, n_out):
+    """At most 128 rows: both GEMMs in one cooperative launch whose CTAs hand the activation over through
+    counters kept in the workspace.  Several calls in a row on one workspace (the counters only grow and the
+    call number advances on the device), different inputs each time, with and without a residual in the output;
+    ragged K, output width and token count."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(m + inter)
+    wg = (torch.randn(k, inter, generator=g) * 0.05).bfloat16()
+    wu = (torch.randn(k, inter, generator=g) * 0.05).bfloat16()
+    wd = (torch.randn(inter, n_out, generator=g) * 0.05).bfloat16()
+    w_gu = ops.pack_weight(torch.cat([wg, wu], dim=1).contiguous().cuda())
+    w_d = ops.pack_weight(wd.cuda())
+    for rep in range(4):
+        x = torch.randn(m, k, generator=g).bfloat16()
+        act = (x.float() @ wg.float())
+        act = (act * torch.sigmoid(act) * (x.float() @ wu.float())).bfloat16()
+        exp = act.float() @ wd.float()
+        if rep % 2:
+            base = torch.randn(m, n_out, generator=g)
+            out = base.cuda().clone()
+            ops.ffn_swiglu(x.cuda(), w_gu, w_d, out=out, accumulate=True)
+            exp = exp + base
+        else:
+            out = ops.ffn_swiglu(x.cuda(), w_gu, w_d)
+        torch.cuda.synchronize()
+        ops.check_device_status()
+        _check(out, exp, 5e-3, f"one-launch ffn {m}x{k}x{inter}x{n_out} call {rep}")
