@@ -17,8 +17,8 @@
 //            waits (bounded) for the slab's counter; partial sums meet in `out` through red.global.add.f32.
 //
 // The producer warp runs ahead: the down-projection weights of a CTA's run are already in shared memory while
-// the grid finishes phase 1.  Counters only grow: a call adds `tiles per slab` to each; the call number is kept
-// in the workspace header and advanced by the last CTA to leave, so no launch is needed to reset anything.
+// the grid finishes phase 1.  The slab counters live in the first 8 KB of the workspace and start every call at
+// zero: the last CTA to leave clears the ones the call used, so no launch is needed to reset anything.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -29,7 +29,8 @@ constexpr int kFfThreads = 192;          // warp 0 TMA producer, warp 1 MMA issu
 constexpr int kFfStages = 6;
 constexpr int kFfStageBytes = 32 * 1024; // one 64-wide K atom: 16 KB of the lane operand + up to 16 KB of the other
 constexpr int kFfBn1 = 32;               // phase 1: features per tile (gate 32 | up 32 -> MMA N = 64)
-constexpr int kFfHeaderInts = 64;        // workspace header: [0] call number, [1] CTAs that have left
+constexpr int kFfHeaderInts = 64;        // workspace header: [1] CTAs that have left; slab counters follow
+constexpr size_t kFfHeaderBytes = 8192;  // header + counters; the activation starts here
 
 struct FfnParams {
   int m, k, inter, n_out, ntok;          // ntok: MMA N of phase 2 (tokens rounded up to 32 / 64 / 128)
@@ -102,10 +103,9 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const int call = ld_acquire(p.header);          // read by every CTA before the last one to leave advances it
   int* counters = p.header + kFfHeaderInts;
   constexpr int kTilesPerSlab = 64 / kFfBn1;      // phase-1 tiles that make one 64-feature slab
-  const int slab_target = (call + 1) * kTilesPerSlab;
+  constexpr int slab_target = kTilesPerSlab;
 
   // this CTA's phase-2 run of (tile, K block) iterations
   const int it2_lo = min(p.iters2, static_cast<int>(blockIdx.x) * p.iters2_per_cta);
@@ -281,15 +281,16 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+  // The last CTA to leave clears the counters for the next call: by then every CTA is past its last wait.
+  __shared__ int last_to_leave;
   if (threadIdx.x == 0) {
-    // the last CTA to leave opens the next call: every CTA read `call` before it got here
     __threadfence();
-    const int left = atomicAdd(p.header + 1, 1);
-    if (left == static_cast<int>(gridDim.x) - 1) {
-      p.header[1] = 0;
-      __threadfence();
-      atomicAdd(p.header, 1);
-    }
+    last_to_leave = atomicAdd(p.header + 1, 1) == static_cast<int>(gridDim.x) - 1;
+  }
+  __syncthreads();
+  if (last_to_leave) {
+    for (int i = threadIdx.x; i < p.kblocks2; i += kFfThreads) counters[i] = 0;
+    if (threadIdx.x == 0) p.header[1] = 0;
   }
 }
 
@@ -297,12 +298,12 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 
 size_t ffn_fused_workspace_bytes(int inter) {
   // header + slab counters, then the activation [128, inter] bf16
-  const size_t head = (sizeof(int) * (kFfHeaderInts + static_cast<size_t>(inter) / 64) + 255) / 256 * 256;
-  return head + static_cast<size_t>(128) * inter * 2;
+  return kFfHeaderBytes + static_cast<size_t>(128) * inter * 2;
 }
 
 bool ffn_fused_ok(int m, int k, int inter, int n_out) {
-  return m > 0 && m <= 128 && k % 8 == 0 && inter % 64 == 0 && inter >= 64 && n_out % 4 == 0;
+  return m > 0 && m <= 128 && k % 8 == 0 && inter % 64 == 0 && inter >= 64 && n_out % 4 == 0 &&
+         sizeof(int) * (kFfHeaderInts + static_cast<size_t>(inter) / 64) <= kFfHeaderBytes;
 }
 
 // x bf16 [m, k] (m <= 128), w_gate_up packed [2 * inter, k] (gate rows first), w_down packed [n_out, inter],
@@ -325,8 +326,7 @@ int ffn_fused_launch(const void* x, const void* w_gate_up, const void* w_down, f
   const int grid = sm_count();                     // CTAs without a phase-1 tile go straight to their phase-2 run
   p.iters2_per_cta = (p.iters2 + grid - 1) / grid;
   p.header = static_cast<int*>(workspace);
-  const size_t head = (sizeof(int) * (kFfHeaderInts + static_cast<size_t>(inter) / 64) + 255) / 256 * 256;
-  p.act = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(workspace) + head);
+  p.act = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(workspace) + kFfHeaderBytes);
   p.out = out; p.err = err;
 
   CUtensorMap tm_x, tm_gu, tm_act, tm_d;

@@ -59,13 +59,19 @@ bool use_swiglu_epilogue(int m, int inter, int* bn) {
 }
 }  // namespace
 
+// A workspace serves calls of any size; larger batches must not touch the header that the one-launch kernel of
+// small batches keeps its call number and slab counters in.
+constexpr size_t kFfnHeaderBytes = 8192;
+
 size_t ffn_workspace_bytes(int m, int inter) {
-  // decode-sized batches: the one-launch kernel's header, slab counters and activation
-  if (m <= 128 && inter % 64 == 0 && inter >= 64) return ffn_fused_workspace_bytes(inter);
+  // the first kFfnHeaderBytes stay reserved for the one-launch kernel's counters whatever path a call takes; then
   // bf16 activation [m, inter]; plus fp32 gate|up [m, 2*inter] for the stream-K path
   const size_t act = (static_cast<size_t>(m) * inter * 2 + 255) / 256 * 256;
   int bn;
-  return use_swiglu_epilogue(m, inter, &bn) ? act : act + static_cast<size_t>(m) * 2 * inter * 4;
+  const size_t chain = kFfnHeaderBytes + (use_swiglu_epilogue(m, inter, &bn) ? act : act + static_cast<size_t>(m) * 2 * inter * 4);
+  // decode-sized batches: the one-launch kernel's activation has 128 rows
+  const size_t fused = (m <= 128 && inter % 64 == 0 && inter >= 64) ? ffn_fused_workspace_bytes(inter) : 0;
+  return chain > fused ? chain : fused;
 }
 
 // out[m, n_out] (+)= (silu(x Wg) * (x Wu)) Wd with bf16 operands, fp32 accumulate, the
@@ -85,7 +91,8 @@ int ffn_swiglu_launch(const void* x, const void* w_gate_up, const void* w_down, 
     if (!accumulate) PTO_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * static_cast<size_t>(m) * n_out, stream));
     return ffn_fused_launch(x, w_gate_up, w_down, out, m, k, inter, n_out, workspace, workspace_bytes, err, stream);
   }
-  __nv_bfloat16* act = static_cast<__nv_bfloat16*>(workspace);
+  uint8_t* ws = static_cast<uint8_t*>(workspace) + kFfnHeaderBytes;
+  __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(ws);
   int st;
   int bn = 0;
   if (use_swiglu_epilogue(m, inter, &bn)) {
@@ -95,8 +102,7 @@ int ffn_swiglu_launch(const void* x, const void* w_gate_up, const void* w_down, 
                           stream);
     if (st != kOk) return st;
   } else {
-    float* gate_up = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) +
-                                              (static_cast<size_t>(m) * inter * 2 + 255) / 256 * 256);
+    float* gate_up = reinterpret_cast<float*>(ws + (static_cast<size_t>(m) * inter * 2 + 255) / 256 * 256);
     st = linear_launch(x, w_gate_up, gate_up, m, 2 * inter, k, 0, err, stream);
     if (st != kOk) return st;
     st = swiglu_act_launch(gate_up, act, m, inter, stream);
