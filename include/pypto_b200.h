@@ -271,11 +271,11 @@ PTO_API int pto_quantize_rows(const void* x, int x_dtype, void* q, float* scale,
 /* Dispatch plan (dispatch_step, tests/st/distributed/test_l3_ep_dispatch_combine.py:104-299):
  * bucket of route r is expert_of[r]; inside a bucket routes keep ascending r = t * TOPK + k.
  * Outputs: counts [buckets], offsets [buckets + 1], pos [routes] (slot of each route in the
- * bucket-sorted order), route_at [routes] (inverse).  rank_tmp: int32 [routes] work array.
+ * bucket-sorted order), route_at [routes] (inverse).  work: int32 [routes + buckets] work array.
  * An expert id outside [0, buckets) is not dereferenced: the route gets pos = -1, the unused
  * tail of route_at is set to -1 and `err` (device int32[4], may be NULL) receives code 3. */
 PTO_API int pto_moe_dispatch_plan(const int32_t* expert_of, int routes, int buckets, int32_t* counts,
-                                  int32_t* offsets, int32_t* pos, int32_t* route_at, int32_t* rank_tmp,
+                                  int32_t* offsets, int32_t* pos, int32_t* route_at, int32_t* work,
                                   int32_t* err, void* stream);
 
 /* Receiver side of dispatch_step (:184-218): rows arrive source-major and, inside a source, ordered

@@ -7,18 +7,22 @@
 // kernels/projection.py:146-177), where every intermediate goes through global memory between task launches.
 // At this size the step is bound by streaming 3 * k * inter weight elements once; a chain of launches pays a
 // prologue, a pipeline fill and a tail per GEMM, several times the streaming time.  Here one persistent grid
-// (one CTA per SM, launched cooperatively so that all CTAs are resident) runs both GEMMs:
+// (one CTA per SM, launched cooperatively so that all CTAs are resident) runs both GEMMs.  In both phases the
+// weights take the 128 TMEM lanes (A operand, 16 KB per 64-wide K block) and the tokens are the MMA N, so that a
+// pipeline stage is mostly weight bytes: what bounds the kernel is weight bytes in flight per SM.
 //
-//   phase 1  tile = 32 gate + 32 up features: tokens on the 128 TMEM lanes, the two weight tiles side by side as
-//            one MMA of N = 64; the epilogue writes bf16(silu(g) * u) to the activation buffer (stays in L2) and
-//            publishes it: fence, then one atomic increment of the counter of its 64-feature slab.
-//   phase 2  stream-K over (128 output features, 64-wide K block of the activation): every CTA takes an equal
-//            run of K blocks, weights on the TMEM lanes, tokens as MMA N; before it loads an activation block it
-//            waits (bounded) for the slab's counter; partial sums meet in `out` through red.global.add.f32.
+//   phase 1  tile = 64 gate rows (lanes 0-63) + the 64 matching up rows (lanes 64-127).  Epilogue: the up warps
+//            hand their values to the gate warps through shared memory; those write bf16(silu(g) * u) to the
+//            activation buffer (it stays in L2) and publish the 64-feature slab: barrier, one fence, one
+//            release-increment of the slab's counter.
+//   phase 2  stream-K over (128 output features, 64-wide K block of the activation).  CTAs that had fewer phase-1
+//            tiles take more K blocks.  A CTA first streams the down-projection weights of its run into the
+//            pipeline (they do not depend on phase 1), then waits (bounded) for the counters of the slabs it needs,
+//            then loads activation blocks; partial sums meet in `out` through red.global.add.f32, every CTA
+//            walking the tokens from a different start so that the reductions do not pile up on one line.
 //
-// The producer warp runs ahead: the down-projection weights of a CTA's run are already in shared memory while
-// the grid finishes phase 1.  The slab counters live in the first 8 KB of the workspace and start every call at
-// zero: the last CTA to leave clears the ones the call used, so no launch is needed to reset anything.
+// The slab counters live in the first 8 KB of the workspace and start every call at zero: the last CTA to leave
+// clears the ones the call used, so no launch is needed to reset anything.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -26,16 +30,20 @@ namespace pto {
 namespace {
 
 constexpr int kFfThreads = 192;          // warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue
-constexpr int kFfStages = 6;
-constexpr int kFfStageBytes = 32 * 1024; // one 64-wide K atom: 16 KB of the lane operand + up to 16 KB of the other
-constexpr int kFfBn1 = 32;               // phase 1: features per tile (gate 32 | up 32 -> MMA N = 64)
+constexpr int kFfMaxStages = 12;
+constexpr int kFfTile1 = 64;             // phase 1: features per tile (64 gate rows + 64 up rows on the lanes)
 constexpr int kFfHeaderInts = 64;        // workspace header: [1] CTAs that have left; slab counters follow
 constexpr size_t kFfHeaderBytes = 8192;  // header + counters; the activation starts here
 
 struct FfnParams {
-  int m, k, inter, n_out, ntok;          // ntok: MMA N of phase 2 (tokens rounded up to 32 / 64 / 128)
-  int tiles1, kblocks1;                  // phase 1: inter / 32 tiles, ceil(k / 64) K blocks each
-  int tiles2, kblocks2, iters2, iters2_per_cta;   // phase 2: ceil(n_out / 128) tiles x inter / 64 K blocks
+  int m, k, inter, n_out, ntok;          // ntok: MMA N (tokens rounded up to 32 / 64 / 128)
+  int tiles1, kblocks1;                  // phase 1: inter / 64 tiles, ceil(k / 64) K blocks each
+  int tiles2, kblocks2, iters2;          // phase 2: ceil(n_out / 128) tiles x inter / 64 K blocks
+  // phase-2 split: CTAs b < heavy (one more phase-1 tile than the rest) take n2_heavy iterations each, the others
+  // n2_base (+1 for the first n2_rem of them)
+  int heavy, n2_heavy, n2_base, n2_rem;
+  int stages;
+  uint32_t stage_bytes;
   __nv_bfloat16* act;                    // [128, inter]
   int* header;                           // kFfHeaderInts ints, then inter / 64 slab counters
   float* out;                            // [m, n_out]
@@ -48,16 +56,8 @@ __device__ __forceinline__ int ld_acquire(const int* p) {
   return v;
 }
 
-// Bounded wait until *p - target >= 0 (counters wrap; the difference does not).
-__device__ __forceinline__ bool wait_counter(const int* p, int target) {
-  if (ld_acquire(p) - target >= 0) return true;
-  const unsigned long long t0 = global_timer_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (ld_acquire(p) - target >= 0) return true;
-    if (global_timer_ns() - t0 > kWaitTimeoutNs) return false;
-  }
+__device__ __forceinline__ void red_release_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
@@ -69,21 +69,24 @@ __global__ void __launch_bounds__(kFfThreads, 1)
 ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_gu,
                  const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_d,
                  const FfnParams p) {
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kFfStages * kFfStageBytes);
-  uint64_t* empty = full + kFfStages;
-  uint64_t* tmem_full = empty + kFfStages;
+  float* exch = reinterpret_cast<float*>(smem + static_cast<size_t>(p.stages) * p.stage_bytes);   // [ntok][64]
+  uint64_t* full = reinterpret_cast<uint64_t*>(exch + static_cast<size_t>(p.ntok) * kFfTile1);
+  uint64_t* empty = full + kFfMaxStages;
+  uint64_t* tmem_full = empty + kFfMaxStages;
   uint64_t* tmem_empty = tmem_full + 2;
   uint64_t* drain = tmem_empty + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
+  int* last_to_leave = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr uint32_t tmem_cols = 256;   // two accumulator buffers of 128 columns (phase 1 uses 64 of them)
+  constexpr uint32_t tmem_cols = 256;   // two accumulator buffers of 128 token columns
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kFfStages; ++i) {
+    for (int i = 0; i < p.stages; ++i) {
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
     }
@@ -104,74 +107,115 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   int* counters = p.header + kFfHeaderInts;
-  constexpr int kTilesPerSlab = 64 / kFfBn1;      // phase-1 tiles that make one 64-feature slab
-  constexpr int slab_target = kTilesPerSlab;
 
-  // this CTA's phase-2 run of (tile, K block) iterations
-  const int it2_lo = min(p.iters2, static_cast<int>(blockIdx.x) * p.iters2_per_cta);
-  const int it2_hi = min(p.iters2, it2_lo + p.iters2_per_cta);
-  const uint32_t a1_bytes = 128 * 128, b1_bytes = 2 * kFfBn1 * 128;            // x tile, gate | up tiles
-  const uint32_t a2_bytes = 128 * 128, b2_bytes = static_cast<uint32_t>(p.ntok) * 128;   // Wd tile, activation tile
+  // this CTA's phase-1 tiles are blockIdx.x, + gridDim.x, ...; its phase-2 run of (tile, K block) iterations:
+  const int b = blockIdx.x;
+  int it2_lo, n2;
+  if (b < p.heavy) {
+    n2 = p.n2_heavy;
+    it2_lo = b * p.n2_heavy;
+  } else {
+    const int j = b - p.heavy;
+    n2 = p.n2_base + (j < p.n2_rem ? 1 : 0);
+    it2_lo = p.heavy * p.n2_heavy + j * p.n2_base + min(j, p.n2_rem);
+  }
+  const int it2_hi = min(p.iters2, it2_lo + n2);
+  const uint32_t w_bytes = 128 * 128;                                   // weight tile of one K block
+  const uint32_t t_bytes = static_cast<uint32_t>(p.ntok) * 128;         // token tile (x or activation) of one K block
+  int n1 = 0;
+  for (int tile = b; tile < p.tiles1; tile += gridDim.x) n1 += p.kblocks1;   // phase-1 iterations of this CTA
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
+    uint32_t it = 0;
+    bool ok = true;
+    const uint32_t S = static_cast<uint32_t>(p.stages);
+    auto stage_ptr = [&](uint32_t j) { return smem + static_cast<size_t>(j % S) * p.stage_bytes; };
+    auto wait_stage = [&](uint32_t j, int site) {
+      if (!mbar_spin_wait(&empty[j % S], ((j / S) & 1u) ^ 1u)) {
+        report_error(p.err, kErrBarrierTimeout, site, static_cast<int>(j));
+        ok = false;
+      }
+      return ok;
+    };
+    auto issue_w1 = [&](uint32_t j, int i1) {      // i1: phase-1 iteration of this CTA
+      const int tile = b + (i1 / p.kblocks1) * static_cast<int>(gridDim.x), kb = i1 % p.kblocks1;
+      uint8_t* st = stage_ptr(j);
+      mbar_arrive_expect_tx(&full[j % S], w_bytes + t_bytes);
+      tma_load_2d(st, &tm_gu, kb * 64, tile * kFfTile1, &full[j % S]);                               // gate rows
+      tma_load_2d(st + kFfTile1 * 128, &tm_gu, kb * 64, p.inter + tile * kFfTile1, &full[j % S]);    // up rows
+    };
+    auto issue_x1 = [&](uint32_t j, int i1) {
+      tma_load_2d(stage_ptr(j) + w_bytes, &tm_x, (i1 % p.kblocks1) * 64, 0, &full[j % S]);           // rows past m: zeros
+    };
     if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < p.tiles1 && ok; tile += gridDim.x) {
-        for (int kb = 0; kb < p.kblocks1; ++kb, ++it) {
-          const uint32_t s = it % kFfStages, round = it / kFfStages;
-          if (!mbar_spin_wait(&empty[s], (round & 1u) ^ 1u)) {
-            report_error(p.err, kErrBarrierTimeout, 80, static_cast<int>(it));
-            ok = false;
+      // The weights of the first stages do not depend on the kernel before this one: they are requested before
+      // the wait on it (programmatic dependent launch), the activations after.
+      const int first = min(n1, p.stages);
+      for (int i1 = 0; i1 < first; ++i1) issue_w1(it + i1, i1);
+      pdl_wait();
+      for (int i1 = 0; i1 < first; ++i1) issue_x1(it + i1, i1);
+      it += first;
+      for (int i1 = first; i1 < n1 && ok; ++i1, ++it) {
+        if (!wait_stage(it, 80)) break;
+        issue_w1(it, i1);
+        issue_x1(it, i1);
+      }
+    }
+    // Phase 2.  First window: down-projection weights into every stage that frees up, then the wait for the slabs.
+    const int win = min(it2_hi - it2_lo, p.stages);
+    if (lane == 0 && ok) {
+      for (int i = 0; i < win && ok; ++i) {
+        const int i2 = it2_lo + i, tile = i2 / p.kblocks2, kb = i2 - tile * p.kblocks2;
+        if (!wait_stage(it + i, 81)) break;
+        mbar_arrive_expect_tx(&full[(it + i) % S], w_bytes + t_bytes);
+        tma_load_2d(stage_ptr(it + i), &tm_d, kb * 64, tile * 128, &full[(it + i) % S]);
+      }
+    }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    // All lanes: wait until every slab of the run has been published (lane l polls the run's iterations l, l+32, ...).
+    // Not before the kernel ahead of this one has finished: it may be a call of this operator on the same
+    // workspace, whose last CTA clears the counters.
+    pdl_wait();
+    if (ok) {
+      bool mine = true;
+      const unsigned long long t0 = global_timer_ns();
+      for (int i2 = it2_lo + lane; i2 < it2_hi && mine; i2 += 32) {
+        const int* c = &counters[i2 % p.kblocks2];
+        while (ld_acquire(c) < 1) {
+          if (global_timer_ns() - t0 > kWaitTimeoutNs) {
+            mine = false;
             break;
           }
-          uint8_t* st = smem + static_cast<size_t>(s) * kFfStageBytes;
-          mbar_arrive_expect_tx(&full[s], a1_bytes + b1_bytes);
-          tma_load_2d(st, &tm_x, kb * 64, 0, &full[s]);                                   // rows past m: zeros
-          tma_load_2d(st + a1_bytes, &tm_gu, kb * 64, tile * kFfBn1, &full[s]);            // gate rows
-          tma_load_2d(st + a1_bytes + kFfBn1 * 128, &tm_gu, kb * 64, p.inter + tile * kFfBn1, &full[s]);   // up rows
         }
       }
-      // Phase 2 in windows of kFfStages iterations: first every weight tile of the window (they do not depend on
-      // phase 1, so they stream in while the grid finishes it), then, slab by slab, the activation tiles.
-      for (int w0 = it2_lo; w0 < it2_hi && ok; w0 += kFfStages) {
-        const int w1 = min(it2_hi, w0 + kFfStages);
-        for (int i2 = w0; i2 < w1; ++i2) {
-          const int tile = i2 / p.kblocks2, kb = i2 - tile * p.kblocks2;
-          const uint32_t j = it + static_cast<uint32_t>(i2 - w0);
-          const uint32_t s = j % kFfStages, round = j / kFfStages;
-          if (!mbar_spin_wait(&empty[s], (round & 1u) ^ 1u)) {
-            report_error(p.err, kErrBarrierTimeout, 81, static_cast<int>(j));
-            ok = false;
-            break;
-          }
-          mbar_arrive_expect_tx(&full[s], a2_bytes + b2_bytes);
-          tma_load_2d(smem + static_cast<size_t>(s) * kFfStageBytes, &tm_d, kb * 64, tile * 128, &full[s]);
-        }
-        for (int i2 = w0; i2 < w1 && ok; ++i2) {
-          const int kb = i2 % p.kblocks2;
-          const uint32_t s = (it + static_cast<uint32_t>(i2 - w0)) % kFfStages;
-          if (!wait_counter(&counters[kb], slab_target)) {
-            report_error(p.err, kErrBarrierTimeout, 82, kb);
-            ok = false;
-            break;
-          }
-          // the slab was written with ordinary stores by other CTAs: order the bulk (async-proxy) read after the acquire
-          asm volatile("fence.proxy.async.global;" ::: "memory");
-          tma_load_2d(smem + static_cast<size_t>(s) * kFfStageBytes + a2_bytes, &tm_act, kb * 64, 0, &full[s]);
-        }
-        it += static_cast<uint32_t>(w1 - w0);
+      if (!__all_sync(0xffffffffu, mine)) {
+        if (lane == 0) report_error(p.err, kErrBarrierTimeout, 82, it2_lo);
+        ok = false;
+      }
+    }
+    if (lane == 0 && ok) {
+      // the slabs were written with ordinary stores by other CTAs: order the bulk (async-proxy) reads after the acquires
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      for (int i = 0; i < win; ++i)
+        tma_load_2d(stage_ptr(it + i) + w_bytes, &tm_act, ((it2_lo + i) % p.kblocks2) * 64, 0, &full[(it + i) % S]);
+      it += win;
+      for (int i2 = it2_lo + win; i2 < it2_hi && ok; ++i2, ++it) {
+        const int tile = i2 / p.kblocks2, kb = i2 - tile * p.kblocks2;
+        if (!wait_stage(it, 81)) break;
+        mbar_arrive_expect_tx(&full[it % S], w_bytes + t_bytes);
+        tma_load_2d(stage_ptr(it), &tm_d, kb * 64, tile * 128, &full[it % S]);
+        tma_load_2d(stage_ptr(it) + w_bytes, &tm_act, kb * 64, 0, &full[it % S]);
       }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
-      const uint32_t idesc1 = umma_idesc(128, 2 * kFfBn1, 1, 1);
-      const uint32_t idesc2 = umma_idesc(128, static_cast<uint32_t>(p.ntok), 1, 1);
+      const uint32_t idesc = umma_idesc(128, static_cast<uint32_t>(p.ntok), 1, 1);
+      const uint32_t S = static_cast<uint32_t>(p.stages);
       uint32_t it = 0, ui = 0;
       bool ok = true;
-      auto unit = [&](int kblocks, uint32_t b_off, uint32_t idesc) {
+      auto unit = [&](int kblocks) {
         const uint32_t ab = ui & 1u;
         if (!mbar_spin_wait(&tmem_empty[ab], ((ui >> 1) & 1u) ^ 1u)) {
           report_error(p.err, kErrBarrierTimeout, 83, static_cast<int>(ui));
@@ -181,28 +225,27 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         tc_fence_after_sync();
         const uint32_t d0 = tmem_base + ab * 128;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const uint32_t s = it % kFfStages, round = it / kFfStages;
+          const uint32_t s = it % S, round = it / S;
           if (!mbar_spin_wait(&full[s], round & 1u)) {
             report_error(p.err, kErrBarrierTimeout, 84, static_cast<int>(it));
             ok = false;
             return;
           }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * kFfStageBytes);
+          const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * p.stage_bytes);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16(d0, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(a_addr + b_off + k * 32), idesc,
+            umma_bf16(d0, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(a_addr + w_bytes + k * 32), idesc,
                       (kb > 0 || k > 0) ? 1u : 0u);
           umma_commit(&empty[s]);
         }
         umma_commit(&tmem_full[ab]);
         ++ui;
       };
-      for (int tile = blockIdx.x; tile < p.tiles1 && ok; tile += gridDim.x) unit(p.kblocks1, a1_bytes, idesc1);
+      for (int tile = b; tile < p.tiles1 && ok; tile += gridDim.x) unit(p.kblocks1);
       for (int i2 = it2_lo; i2 < it2_hi && ok;) {          // segments of the run, cut at tile boundaries
-        const int tile = i2 / p.kblocks2;
-        const int seg_end = min(it2_hi, (tile + 1) * p.kblocks2);
-        unit(seg_end - i2, a2_bytes, idesc2);
+        const int seg_end = min(it2_hi, (i2 / p.kblocks2 + 1) * p.kblocks2);
+        unit(seg_end - i2);
         i2 = seg_end;
       }
       umma_commit(drain);   // tensor memory is released only after every MMA has completed
@@ -212,46 +255,55 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   } else {
     // -------------------------------- epilogue --------------------------------
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
-    const int row = q * 32 + lane;               // phase 1: token; phase 2: output feature within the tile
+    const bool is_up = q >= 2;                   // lanes 64-127 hold the up rows
+    const int f = (q & 1) * 32 + lane;           // phase 1: feature within the tile
     uint32_t ui = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.tiles1; tile += gridDim.x, ++ui) {
+    pdl_wait();                                  // before the first global write
+    for (int tile = b; tile < p.tiles1; tile += gridDim.x, ++ui) {
       const uint32_t ab = ui & 1u;
       if (ok && !mbar_wait_warp(&tmem_full[ab], (ui >> 1) & 1u)) {
         report_error(p.err, kErrBarrierTimeout, 86, static_cast<int>(ui));
         ok = false;
       }
-      if (ok) {
-        tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * 128;
-        uint32_t g[32], u[32];
-        tmem_ld_32x32(taddr, g);
-        tmem_ld_32x32(taddr + kFfBn1, u);
-        tmem_ld_wait();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * 128;
+      if (ok) tc_fence_after_sync();
+      if (ok && is_up) {
+        for (int c0 = 0; c0 < p.ntok; c0 += 32) {
+          uint32_t u[32];
+          tmem_ld_32x32(taddr + c0, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) exch[(c0 + j) * kFfTile1 + f] = __uint_as_float(u[j]);
+        }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[ab]);
-        // every one of the 128 rows is written (rows past m hold silu(0) * 0 = 0): phase 2 reads whole tiles
-        __nv_bfloat16* dst = p.act + static_cast<size_t>(row) * p.inter + tile * kFfBn1;
-#pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          uint4 pk;
-          pk.x = pack_bf16x2(silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j])),
-                             silu_mul(__uint_as_float(g[j + 1]), __uint_as_float(u[j + 1])));
-          pk.y = pack_bf16x2(silu_mul(__uint_as_float(g[j + 2]), __uint_as_float(u[j + 2])),
-                             silu_mul(__uint_as_float(g[j + 3]), __uint_as_float(u[j + 3])));
-          pk.z = pack_bf16x2(silu_mul(__uint_as_float(g[j + 4]), __uint_as_float(u[j + 4])),
-                             silu_mul(__uint_as_float(g[j + 5]), __uint_as_float(u[j + 5])));
-          pk.w = pack_bf16x2(silu_mul(__uint_as_float(g[j + 6]), __uint_as_float(u[j + 6])),
-                             silu_mul(__uint_as_float(g[j + 7]), __uint_as_float(u[j + 7])));
-          *reinterpret_cast<uint4*>(dst + j) = pk;
-        }
-        __threadfence();                           // this thread's stores are visible device-wide ...
       }
-      named_bar_sync(1, 128);                      // ... for all four epilogue warps ...
-      if (ok && warp == 2 && lane == 0)            // ... before the tile is counted
-        atomicAdd(&counters[tile / kTilesPerSlab], 1);
+      named_bar_sync(1, 128);                    // the up values of the tile are in shared memory
+      if (ok && !is_up) {
+        __nv_bfloat16* dst = p.act + static_cast<size_t>(tile) * kFfTile1 + f;
+        for (int c0 = 0; c0 < p.ntok; c0 += 32) {
+          uint32_t g[32];
+          tmem_ld_32x32(taddr + c0, g);
+          tmem_ld_wait();
+          // every one of the ntok rows is written (rows past m hold silu(0) * 0 = 0): phase 2 reads whole tiles
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            dst[static_cast<size_t>(c0 + j) * p.inter] =
+                __float2bfloat16_rn(silu_mul(__uint_as_float(g[j]), exch[(c0 + j) * kFfTile1 + f]));
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[ab]);
+      }
+      named_bar_sync(2, 128);                    // the slab is written; the exchange buffer is free again
+      if (ok && warp == 2 && lane == 0) {
+        __threadfence();                         // cumulative: covers the stores the barrier ordered before it
+        red_release_add(&counters[tile], 1);
+      }
     }
+    const int tok0 = (b * 32) % p.ntok;          // every CTA starts its walk over the tokens elsewhere
     for (int i2 = it2_lo; i2 < it2_hi && ok; ++ui) {
       const int tile = i2 / p.kblocks2;
       i2 = min(it2_hi, (tile + 1) * p.kblocks2);
@@ -262,15 +314,31 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * 128;
-      const int feat = tile * 128 + row;
-      for (int c0 = 0; c0 < p.ntok; c0 += 32) {
+      const int feat = tile * 128 + q * 32 + lane;
+      for (int cc = 0; cc < p.ntok; cc += 32) {
+        const int c0 = (tok0 + cc) % p.ntok;
         uint32_t v[32];
         tmem_ld_32x32(taddr + c0, v);
         tmem_ld_wait();
         if (feat < p.n_out) {
+          // lanes are consecutive features: coalesced reductions.  The CTAs that share an output tile start at
+          // different tokens (tok0 above, and the group of eight below), so they do not queue on one line.
+          auto reduce8 = [&](int j0) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)              // lanes are consecutive features: coalesced reductions
-            if (c0 + j < p.m) red_add_f32(p.out + static_cast<size_t>(c0 + j) * p.n_out + feat, __uint_as_float(v[j]));
+            for (int j = 0; j < 8; ++j)
+              if (c0 + j0 + j < p.m)
+                red_add_f32(p.out + static_cast<size_t>(c0 + j0 + j) * p.n_out + feat, __uint_as_float(v[j0 + j]));
+          };
+          const int rot = (b >> 2) & 3;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            switch ((g + rot) & 3) {
+              case 0: reduce8(0); break;
+              case 1: reduce8(8); break;
+              case 2: reduce8(16); break;
+              default: reduce8(24); break;
+            }
+          }
         }
       }
       tc_fence_before_sync();
@@ -282,13 +350,12 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
   // The last CTA to leave clears the counters for the next call: by then every CTA is past its last wait.
-  __shared__ int last_to_leave;
   if (threadIdx.x == 0) {
     __threadfence();
-    last_to_leave = atomicAdd(p.header + 1, 1) == static_cast<int>(gridDim.x) - 1;
+    *last_to_leave = atomicAdd(p.header + 1, 1) == static_cast<int>(gridDim.x) - 1;
   }
   __syncthreads();
-  if (last_to_leave) {
+  if (*last_to_leave) {
     for (int i = threadIdx.x; i < p.kblocks2; i += kFfThreads) counters[i] = 0;
     if (threadIdx.x == 0) p.header[1] = 0;
   }
@@ -315,26 +382,40 @@ int ffn_fused_launch(const void* x, const void* w_gate_up, const void* w_down, f
   PTO_REQUIRE(ffn_fused_ok(m, k, inter, n_out), "ffn_fused: m <= 128, k % 8 == 0, inter % 64 == 0, n_out % 4 == 0 required");
   PTO_REQUIRE(workspace_bytes >= ffn_fused_workspace_bytes(inter), "ffn_fused: workspace too small");
   PTO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "ffn_fused: workspace must be 256-byte aligned");
+  const int grid = sm_count();
   FfnParams p;
   p.m = m; p.k = k; p.inter = inter; p.n_out = n_out;
   p.ntok = m <= 32 ? 32 : (m <= 64 ? 64 : 128);
-  p.tiles1 = inter / kFfBn1;
+  p.tiles1 = inter / kFfTile1;
   p.kblocks1 = (k + 63) / 64;
   p.tiles2 = (n_out + 127) / 128;
   p.kblocks2 = inter / 64;
   p.iters2 = p.tiles2 * p.kblocks2;
-  const int grid = sm_count();                     // CTAs without a phase-1 tile go straight to their phase-2 run
-  p.iters2_per_cta = (p.iters2 + grid - 1) / grid;
+  // Phase-2 shares.  CTAs b < heavy have one more phase-1 tile (kblocks1 pipeline iterations) than the others;
+  // they take that many fewer phase-2 iterations, as far as the totals allow.
+  p.heavy = p.tiles1 % grid;
+  const long long extra = static_cast<long long>(p.heavy) * p.kblocks1;
+  const long long level = (p.iters2 + extra) / grid;                 // iterations per CTA if all were equal
+  p.n2_heavy = static_cast<int>(level > p.kblocks1 ? level - p.kblocks1 : 0);
+  const int light = grid - p.heavy;                                    // >= 1: heavy < grid
+  const long long rest = p.iters2 - static_cast<long long>(p.heavy) * p.n2_heavy;
+  p.n2_base = static_cast<int>(rest / light);
+  p.n2_rem = static_cast<int>(rest % light);
+  p.stage_bytes = 128 * 128 + static_cast<uint32_t>(p.ntok) * 128;
+  const size_t fixed = 1024 + static_cast<size_t>(p.ntok) * kFfTile1 * 4 + (2 * kFfMaxStages + 5) * 8 + 16;
+  int stages = static_cast<int>((227 * 1024 - fixed) / p.stage_bytes);
+  if (stages > kFfMaxStages) stages = kFfMaxStages;
+  p.stages = stages;
   p.header = static_cast<int*>(workspace);
   p.act = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(workspace) + kFfHeaderBytes);
   p.out = out; p.err = err;
 
   CUtensorMap tm_x, tm_gu, tm_act, tm_d;
-  int st = make_tensor_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, m, k, static_cast<uint64_t>(k) * 2, 64, 128,
-                              CU_TENSOR_MAP_SWIZZLE_128B);
+  int st = make_tensor_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, m, k, static_cast<uint64_t>(k) * 2, 64,
+                              p.ntok, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != kOk) return st;
   st = make_tensor_map_2d(&tm_gu, w_gate_up, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(2) * inter, k,
-                          static_cast<uint64_t>(k) * 2, 64, kFfBn1, CU_TENSOR_MAP_SWIZZLE_128B);
+                          static_cast<uint64_t>(k) * 2, 64, kFfTile1, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != kOk) return st;
   st = make_tensor_map_2d(&tm_act, p.act, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 128, inter,
                           static_cast<uint64_t>(inter) * 2, 64, p.ntok, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -342,21 +423,34 @@ int ffn_fused_launch(const void* x, const void* w_gate_up, const void* w_down, f
   st = make_tensor_map_2d(&tm_d, w_down, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n_out, inter,
                           static_cast<uint64_t>(inter) * 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != kOk) return st;
-  const size_t smem = 1024 + static_cast<size_t>(kFfStages) * kFfStageBytes + (2 * kFfStages + 5) * 8 + 16;
+  const size_t smem = fixed + static_cast<size_t>(stages) * p.stage_bytes;
   if (first_use_on_device(3))
     PTO_CUDA(cudaFuncSetAttribute(ffn_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-  // CTAs wait on one another (phase 2 on phase 1): a cooperative launch guarantees that all of them are resident
+  // CTAs wait on one another (phase 2 on phase 1): a cooperative launch guarantees that all of them are resident.
+  // Programmatic dependent launch lets the prologue and the first weight requests overlap the kernel before.
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kFfThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeCooperative;
   attr[0].val.cooperative = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return check_cuda(cudaLaunchKernelEx(&cfg, ffn_fused_kernel, tm_x, tm_gu, tm_act, tm_d, p), "ffn_fused_kernel launch");
+  static bool pdl_with_cooperative = pdl_enabled();
+  cfg.numAttrs = pdl_with_cooperative ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, ffn_fused_kernel, tm_x, tm_gu, tm_act, tm_d, p);
+  if (e != cudaSuccess && pdl_with_cooperative) {
+    // a driver that does not take both attributes together: cooperative alone (the kernel's waits on the previous
+    // kernel then return at once)
+    (void)cudaGetLastError();
+    pdl_with_cooperative = false;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, ffn_fused_kernel, tm_x, tm_gu, tm_act, tm_d, p);
+  }
+  return check_cuda(e, "ffn_fused_kernel launch");
 }
 
 }  // namespace pto

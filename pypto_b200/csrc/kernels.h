@@ -73,7 +73,7 @@ int moe_topk_launch(const float* scores, const float* bias, int is_logits, int t
 int quantize_rows_launch(const void* x, int x_dtype, void* q, float* scale, long long rows, int cols,
                          cudaStream_t stream);
 int moe_dispatch_plan_launch(const int32_t* expert_of, int routes, int buckets, int32_t* counts, int32_t* offsets,
-                             int32_t* pos, int32_t* route_at, int32_t* rank_tmp, int* err, cudaStream_t stream);
+                             int32_t* pos, int32_t* route_at, int32_t* work, int* err, cudaStream_t stream);
 int moe_recv_plan_launch(const int32_t* recv_counts, int world, int local_experts, int slot_stride, int capacity,
                          int32_t* counts, int32_t* offsets, int32_t* arrival_of, int32_t* grouped_of, int* err,
                          cudaStream_t stream);

@@ -111,41 +111,56 @@ quantize_rows_kernel(const TI* __restrict__ x, uint8_t* __restrict__ q, float* _
   }
 }
 
-// One CTA per bucket (global expert id): count the routes of the bucket and give each its
-// rank in (t, k) order.  rank[r] is written only for routes of this bucket.
-__global__ void __launch_bounds__(256)
-moe_count_rank_kernel(const int32_t* __restrict__ expert_of, int routes, int32_t* __restrict__ counts,
-                      int32_t* __restrict__ rank) {
-  pdl_launch_dependents();
-  pdl_wait();
-  __shared__ int warp_tot[8];
-  __shared__ int running_s;
-  const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) running_s = 0;
-  __syncthreads();
-  for (int base = 0; base < routes; base += 256) {
-    const int r = base + threadIdx.x;
-    const bool mine = r < routes && expert_of[r] == e;
-    const unsigned ballot = __ballot_sync(0xffffffffu, mine);
-    if (lane == 0) warp_tot[warp] = __popc(ballot);
-    __syncthreads();
-    int before = running_s;
-    for (int w = 0; w < warp; ++w) before += warp_tot[w];
-    if (mine) rank[r] = before + __popc(ballot & ((1u << lane) - 1u));
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int tot = 0;
-      for (int w = 0; w < 8; ++w) tot += warp_tot[w];
-      running_s += tot;
-    }
-    __syncthreads();
+// Dispatch plan = a stable counting sort of the routes by bucket (global expert id), in three small launches.
+// Routes are cut into chunks of `chunk` consecutive routes, one warp per chunk.
+//
+//   moe_chunk_hist_kernel   every warp walks its chunk 32 routes at a time and counts, per bucket, the routes
+//                           of the chunk: hist[chunk][bucket]
+//   moe_offsets_kernel      per bucket an exclusive scan over the chunks (hist becomes "routes of this bucket in
+//                           earlier chunks"), the bucket totals, and their exclusive scan: counts, offsets
+//   moe_positions_kernel    every warp walks its chunk again: a route's slot = offsets[bucket] + routes of the
+//                           bucket in earlier chunks + routes of the bucket earlier in this chunk
+//
+// The walk keeps (t, k) order: lanes holding the same bucket are found with a match, ranked by lane, and the
+// running per-chunk count is advanced by the lowest of them.
+__device__ __forceinline__ int chunk_walk_step(int e, bool valid, int lane, int* hist) {
+  // returns the number of earlier routes of the chunk in bucket e (for valid lanes); advances hist
+  const unsigned same = __match_any_sync(0xffffffffu, valid ? e : -1);
+  int before = 0;
+  if (valid) {
+    before = hist[e] + __popc(same & ((1u << lane) - 1u));
   }
-  if (threadIdx.x == 0) counts[e] = running_s;
+  __syncwarp();
+  if (valid && (same & ((1u << lane) - 1u)) == 0) hist[e] += __popc(same);   // the lowest lane of each group
+  __syncwarp();
+  return before;
 }
 
-// Single CTA: offsets[0..n] = exclusive scan of counts[0..n).
-__global__ void __launch_bounds__(1024) moe_offsets_kernel(const int32_t* __restrict__ counts, int n,
-                                                           int32_t* __restrict__ offsets) {
+__global__ void __launch_bounds__(256)
+moe_chunk_hist_kernel(const int32_t* __restrict__ expert_of, int routes, int buckets, int chunk, int n_chunks,
+                      int32_t* __restrict__ hist_out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ int hist_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int c = blockIdx.x * warps + warp;
+  int* hist = hist_smem + warp * buckets;
+  for (int i = lane; i < buckets; i += 32) hist[i] = 0;
+  __syncwarp();
+  if (c >= n_chunks) return;
+  const int r0 = c * chunk, r1 = min(routes, r0 + chunk);
+  for (int base = r0; base < r1; base += 32) {
+    const int r = base + lane;
+    const int e = r < r1 ? expert_of[r] : -1;
+    chunk_walk_step(e, r < r1 && e >= 0 && e < buckets, lane, hist);
+  }
+  for (int i = lane; i < buckets; i += 32) hist_out[static_cast<size_t>(c) * buckets + i] = hist[i];
+}
+
+// Single CTA.  hist [n_chunks][buckets] -> in place: routes of the bucket in earlier chunks; counts[b] = total;
+// offsets[0..buckets] = exclusive scan of counts.
+__global__ void __launch_bounds__(1024) moe_offsets_kernel(int32_t* __restrict__ hist, int n_chunks, int n,
+                                                           int32_t* __restrict__ counts, int32_t* __restrict__ offsets) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ int warp_sum_s[32];
@@ -155,7 +170,15 @@ __global__ void __launch_bounds__(1024) moe_offsets_kernel(const int32_t* __rest
   __syncthreads();
   for (int base = 0; base < n; base += 1024) {
     const int i = base + threadIdx.x;
-    const int v = i < n ? counts[i] : 0;
+    int v = 0;
+    if (i < n) {
+      for (int c = 0; c < n_chunks; ++c) {      // consecutive threads read consecutive buckets of a chunk
+        const int h = hist[static_cast<size_t>(c) * n + i];
+        hist[static_cast<size_t>(c) * n + i] = v;
+        v += h;
+      }
+      counts[i] = v;
+    }
     int inc = v;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -174,27 +197,42 @@ __global__ void __launch_bounds__(1024) moe_offsets_kernel(const int32_t* __rest
   if (threadIdx.x == 0) offsets[n] = carry_s;
 }
 
-// pos[r] = offsets[expert_of[r]] + rank[r]; route_at[pos[r]] = r.
+// pos[r] = slot of route r in the bucket-sorted order; route_at[pos[r]] = r.
 // A route whose expert id lies outside [0, buckets) belongs to no bucket: it is reported through the error
 // word (kErrBadIndex), gets pos = -1 (the combine skips it) and nothing is read or written at an address
 // derived from the id.  Such routes leave the last slots of route_at unused; those are set to -1.
-__global__ void moe_positions_kernel(const int32_t* __restrict__ expert_of, const int32_t* __restrict__ rank,
-                                     const int32_t* __restrict__ offsets, int routes, int buckets,
-                                     int32_t* __restrict__ pos, int32_t* __restrict__ route_at, int* err) {
+__global__ void __launch_bounds__(256)
+moe_positions_kernel(const int32_t* __restrict__ expert_of, const int32_t* __restrict__ chunk_before,
+                     const int32_t* __restrict__ offsets, int routes, int buckets, int chunk, int n_chunks,
+                     int32_t* __restrict__ pos, int32_t* __restrict__ route_at, int* err) {
   pdl_launch_dependents();
   pdl_wait();
-  const int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= routes) return;
-  if (r >= offsets[buckets]) route_at[r] = -1;   // slots [total valid routes, routes) have no route
-  const int e = expert_of[r];
-  if (e < 0 || e >= buckets) {
-    report_error(err, kErrBadIndex, 60, r);
-    pos[r] = -1;
-    return;
+  extern __shared__ int hist_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int c = blockIdx.x * warps + warp;
+  int* hist = hist_smem + warp * buckets;
+  if (c >= n_chunks) return;
+  // start the walk at "offset of the bucket + routes of the bucket in earlier chunks"
+  for (int i = lane; i < buckets; i += 32) hist[i] = offsets[i] + chunk_before[static_cast<size_t>(c) * buckets + i];
+  __syncwarp();
+  const int total = offsets[buckets];
+  const int r0 = c * chunk, r1 = min(routes, r0 + chunk);
+  for (int base = r0; base < r1; base += 32) {
+    const int r = base + lane;
+    const int e = r < r1 ? expert_of[r] : -1;
+    const bool valid = r < r1 && e >= 0 && e < buckets;
+    const int p = chunk_walk_step(e, valid, lane, hist);
+    if (r < r1) {
+      if (r >= total) route_at[r] = -1;   // slots [total valid routes, routes) have no route
+      if (valid) {
+        pos[r] = p;
+        route_at[p] = r;
+      } else {
+        report_error(err, kErrBadIndex, 60, r);
+        pos[r] = -1;
+      }
+    }
   }
-  const int p = offsets[e] + rank[r];
-  pos[r] = p;
-  route_at[p] = r;
 }
 
 // Arrival plan of the expert-parallel receiver.  Rows arrive source-major, and inside a source ordered by
@@ -414,18 +452,29 @@ int quantize_rows_launch(const void* x, int x_dtype, void* q, float* scale, long
 }
 
 // expert_of int32 [routes] -> counts [buckets], offsets [buckets + 1], pos [routes], route_at [routes].
-// `rank_tmp` is an int32 [routes] work array.
+// `work` is an int32 [routes + buckets] work array (per-chunk bucket histograms).
 int moe_dispatch_plan_launch(const int32_t* expert_of, int routes, int buckets, int32_t* counts, int32_t* offsets,
-                             int32_t* pos, int32_t* route_at, int32_t* rank_tmp, int* err, cudaStream_t stream) {
-  PTO_REQUIRE(expert_of && counts && offsets && pos && route_at && rank_tmp, "moe_dispatch_plan: NULL tensor");
-  PTO_REQUIRE(buckets > 0 && routes >= 0, "moe_dispatch_plan: bad sizes");
-  launch_kernel(moe_count_rank_kernel, dim3(buckets), dim3(256), 0, stream, expert_of, routes, counts, rank_tmp);
+                             int32_t* pos, int32_t* route_at, int32_t* work, int* err, cudaStream_t stream) {
+  PTO_REQUIRE(expert_of && counts && offsets && pos && route_at && work, "moe_dispatch_plan: NULL tensor");
+  PTO_REQUIRE(buckets > 0 && buckets <= 8192 && routes >= 0, "moe_dispatch_plan: 1..8192 buckets, routes >= 0");
+  // chunk >= buckets keeps the histograms (n_chunks x buckets ints) inside routes + buckets ints
+  const int chunk = ((buckets > 512 ? buckets : 512) + 31) / 32 * 32;
+  const int n_chunks = routes > 0 ? (routes + chunk - 1) / chunk : 0;
+  int warps = 12288 / buckets;
+  warps = warps > 8 ? 8 : (warps < 1 ? 1 : warps);
+  const size_t smem = sizeof(int) * static_cast<size_t>(warps) * buckets;
+  const int blocks = (n_chunks + warps - 1) / warps;
+  if (n_chunks > 0) {
+    launch_kernel(moe_chunk_hist_kernel, dim3(blocks), dim3(warps * 32), smem, stream, expert_of, routes, buckets, chunk,
+                  n_chunks, work);
+    PTO_CUDA(cudaGetLastError());
+  }
+  launch_kernel(moe_offsets_kernel, dim3(1), dim3(1024), 0, stream, work, n_chunks, buckets, counts, offsets);
   PTO_CUDA(cudaGetLastError());
-  launch_kernel(moe_offsets_kernel, dim3(1), dim3(1024), 0, stream, counts, buckets, offsets);
-  PTO_CUDA(cudaGetLastError());
-  if (routes > 0) {
-    launch_kernel(moe_positions_kernel, dim3((routes + 255) / 256), dim3(256), 0, stream, expert_of, rank_tmp, offsets,
-                  routes, buckets, pos, route_at, err);
+  if (n_chunks > 0) {
+    launch_kernel(moe_positions_kernel, dim3(blocks), dim3(warps * 32), smem, stream, expert_of,
+                  static_cast<const int32_t*>(work), static_cast<const int32_t*>(offsets), routes, buckets, chunk,
+                  n_chunks, pos, route_at, err);
     PTO_CUDA(cudaGetLastError());
   }
   return kOk;

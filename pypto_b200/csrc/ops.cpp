@@ -297,8 +297,8 @@ int pto_quantize_rows(const void* x, int x_dtype, void* q, float* scale, int64_t
 }
 
 int pto_moe_dispatch_plan(const int32_t* expert_of, int routes, int buckets, int32_t* counts, int32_t* offsets,
-                          int32_t* pos, int32_t* route_at, int32_t* rank_tmp, int32_t* err, void* stream) {
-  return pto::moe_dispatch_plan_launch(expert_of, routes, buckets, counts, offsets, pos, route_at, rank_tmp, err,
+                          int32_t* pos, int32_t* route_at, int32_t* work, int32_t* err, void* stream) {
+  return pto::moe_dispatch_plan_launch(expert_of, routes, buckets, counts, offsets, pos, route_at, work, err,
                                        static_cast<cudaStream_t>(stream));
 }
 

@@ -374,7 +374,7 @@ def moe_dispatch_plan(expert_of: torch.Tensor, buckets: int):
     offsets = torch.empty(buckets + 1, dtype=torch.int32, device=dev)
     pos = torch.empty(n, dtype=torch.int32, device=dev)
     route_at = torch.empty(n, dtype=torch.int32, device=dev)
-    tmp = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    tmp = torch.empty(n + buckets, dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         _lib.check(_lib.load().pto_moe_dispatch_plan(expert_of.data_ptr(), n, buckets, counts.data_ptr(),
                                                      offsets.data_ptr(), pos.data_ptr(), route_at.data_ptr(),
