@@ -1,4 +1,4 @@
-// SwiGLU FFN for a decode-sized batch (at most 128 rows) in ONE launch:
+// SwiGLU FFN for a decode-sized batch (at most 128 rows) and weights of a few tens of MB in ONE launch:
 //
 //   out[m, n_out] += bf16(silu(x Wg) * (x Wu)) Wd          (out holds zeros or the residual on entry)
 //
@@ -7,19 +7,20 @@
 // kernels/projection.py:146-177), where every intermediate goes through global memory between task launches.
 // At this size the step is bound by streaming 3 * k * inter weight elements once; a chain of launches pays a
 // prologue, a pipeline fill and a tail per GEMM, several times the streaming time.  Here one persistent grid
-// (one CTA per SM, launched cooperatively so that all CTAs are resident) runs both GEMMs.  In both phases the
-// weights take the 128 TMEM lanes (A operand, 16 KB per 64-wide K block) and the tokens are the MMA N, so that a
-// pipeline stage is mostly weight bytes: what bounds the kernel is weight bytes in flight per SM.
+// (one CTA per SM, launched cooperatively so that all CTAs are resident) runs both GEMMs:
 //
-//   phase 1  tile = 64 gate rows (lanes 0-63) + the 64 matching up rows (lanes 64-127).  Epilogue: the up warps
-//            hand their values to the gate warps through shared memory; those write bf16(silu(g) * u) to the
-//            activation buffer (it stays in L2) and publish the 64-feature slab: barrier, one fence, one
-//            release-increment of the slab's counter.
-//   phase 2  stream-K over (128 output features, 64-wide K block of the activation).  CTAs that had fewer phase-1
-//            tiles take more K blocks.  A CTA first streams the down-projection weights of its run into the
-//            pipeline (they do not depend on phase 1), then waits (bounded) for the counters of the slabs it needs,
-//            then loads activation blocks; partial sums meet in `out` through red.global.add.f32, every CTA
-//            walking the tokens from a different start so that the reductions do not pile up on one line.
+//   phase 1  tile = 32 gate + 32 up features: tokens on the 128 TMEM lanes, the two weight tiles side by side as
+//            one MMA of N = 64 (the finest tile the tensor core takes at M = 128: 4096 features give 128 CTAs
+//            work).  The epilogue writes bf16(silu(g) * u) to the activation buffer (it stays in L2) and
+//            publishes it: barrier, one fence, one release-increment of the counter of its 64-feature slab.
+//   phase 2  stream-K over (128 output features, 64-wide K block of the activation), an equal run per CTA, weights
+//            on the TMEM lanes, tokens as MMA N.  A CTA first streams the down-projection weights of its run into
+//            the pipeline (they do not depend on phase 1), then waits (bounded) for the counters of the slabs it
+//            needs, then loads activation blocks; partial sums meet in `out` through red.global.add.f32, every CTA
+//            walking the tokens from a different start so that the reductions do not queue on one line.
+//
+// What bounds phase 1 at 128 tokens is not DRAM: every CTA needs all of x (k * 256 bytes, from L2) next to its own
+// weight tile, and an SM takes in about 55 GB/s through TMA, so the phase costs (weights / CTAs + x) / 55 GB/s.
 //
 // The slab counters live in the first 8 KB of the workspace and start every call at zero: the last CTA to leave
 // clears the ones the call used, so no launch is needed to reset anything.
@@ -31,17 +32,16 @@ namespace {
 
 constexpr int kFfThreads = 192;          // warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue
 constexpr int kFfMaxStages = 12;
-constexpr int kFfTile1 = 64;             // phase 1: features per tile (64 gate rows + 64 up rows on the lanes)
+constexpr int kFfTile1 = 32;             // phase 1: features per tile (gate 32 | up 32 -> MMA N = 64)
+constexpr int kTilesPerSlab = 64 / kFfTile1;   // phase-1 tiles that make one 64-feature slab (= one phase-2 K block)
 constexpr int kFfHeaderInts = 64;        // workspace header: [1] CTAs that have left; slab counters follow
 constexpr size_t kFfHeaderBytes = 8192;  // header + counters; the activation starts here
 
 struct FfnParams {
   int m, k, inter, n_out, ntok;          // ntok: MMA N (tokens rounded up to 32 / 64 / 128)
-  int tiles1, kblocks1;                  // phase 1: inter / 64 tiles, ceil(k / 64) K blocks each
+  int tiles1, kblocks1;                  // phase 1: inter / 32 tiles, ceil(k / 64) K blocks each
   int tiles2, kblocks2, iters2;          // phase 2: ceil(n_out / 128) tiles x inter / 64 K blocks
-  // phase-2 split: CTAs b < heavy (one more phase-1 tile than the rest) take n2_heavy iterations each, the others
-  // n2_base (+1 for the first n2_rem of them)
-  int heavy, n2_heavy, n2_base, n2_rem;
+  int n2_base, n2_rem;                   // phase-2 run of CTA b: n2_base (+1 for b < n2_rem) iterations
   int stages;
   uint32_t stage_bytes;
   __nv_bfloat16* act;                    // [128, inter]
@@ -61,8 +61,8 @@ __device__ __forceinline__ void red_release_add(int* p, int v) {
 }
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
-  // sigmoid as recip(1 + exp(-g)), the form of examples/models/01_ffn.py:66-77
-  return g * (1.f / (1.f + __expf(-g))) * u;
+  // sigmoid as recip(1 + exp(-g)), the form of examples/models/01_ffn.py:66-77 (hardware reciprocal)
+  return __fdividef(g, 1.f + __expf(-g)) * u;
 }
 
 __global__ void __launch_bounds__(kFfThreads, 1)
@@ -73,8 +73,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  float* exch = reinterpret_cast<float*>(smem + static_cast<size_t>(p.stages) * p.stage_bytes);   // [ntok][64]
-  uint64_t* full = reinterpret_cast<uint64_t*>(exch + static_cast<size_t>(p.ntok) * kFfTile1);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(p.stages) * p.stage_bytes);
   uint64_t* empty = full + kFfMaxStages;
   uint64_t* tmem_full = empty + kFfMaxStages;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -83,7 +82,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   int* last_to_leave = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr uint32_t tmem_cols = 256;   // two accumulator buffers of 128 token columns
+  constexpr uint32_t tmem_cols = 256;   // two accumulator buffers of 128 columns (phase 1 uses 64 of them)
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < p.stages; ++i) {
@@ -110,18 +109,12 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 
   // this CTA's phase-1 tiles are blockIdx.x, + gridDim.x, ...; its phase-2 run of (tile, K block) iterations:
   const int b = blockIdx.x;
-  int it2_lo, n2;
-  if (b < p.heavy) {
-    n2 = p.n2_heavy;
-    it2_lo = b * p.n2_heavy;
-  } else {
-    const int j = b - p.heavy;
-    n2 = p.n2_base + (j < p.n2_rem ? 1 : 0);
-    it2_lo = p.heavy * p.n2_heavy + j * p.n2_base + min(j, p.n2_rem);
-  }
+  const int n2 = p.n2_base + (b < p.n2_rem ? 1 : 0);
+  const int it2_lo = b * p.n2_base + min(b, p.n2_rem);
   const int it2_hi = min(p.iters2, it2_lo + n2);
-  const uint32_t w_bytes = 128 * 128;                                   // weight tile of one K block
-  const uint32_t t_bytes = static_cast<uint32_t>(p.ntok) * 128;         // token tile (x or activation) of one K block
+  const uint32_t lane_bytes = 128 * 128;                                 // operand on the lanes: x tile / Wd tile of a K block
+  const uint32_t w1_bytes = 2 * kFfTile1 * 128;                          // phase 1: gate | up weight tiles of a K block
+  const uint32_t t2_bytes = static_cast<uint32_t>(p.ntok) * 128;         // phase 2: activation tile of a K block
   int n1 = 0;
   for (int tile = b; tile < p.tiles1; tile += gridDim.x) n1 += p.kblocks1;   // phase-1 iterations of this CTA
 
@@ -140,13 +133,13 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     };
     auto issue_w1 = [&](uint32_t j, int i1) {      // i1: phase-1 iteration of this CTA
       const int tile = b + (i1 / p.kblocks1) * static_cast<int>(gridDim.x), kb = i1 % p.kblocks1;
-      uint8_t* st = stage_ptr(j);
-      mbar_arrive_expect_tx(&full[j % S], w_bytes + t_bytes);
+      uint8_t* st = stage_ptr(j) + lane_bytes;
+      mbar_arrive_expect_tx(&full[j % S], lane_bytes + w1_bytes);
       tma_load_2d(st, &tm_gu, kb * 64, tile * kFfTile1, &full[j % S]);                               // gate rows
       tma_load_2d(st + kFfTile1 * 128, &tm_gu, kb * 64, p.inter + tile * kFfTile1, &full[j % S]);    // up rows
     };
     auto issue_x1 = [&](uint32_t j, int i1) {
-      tma_load_2d(stage_ptr(j) + w_bytes, &tm_x, (i1 % p.kblocks1) * 64, 0, &full[j % S]);           // rows past m: zeros
+      tma_load_2d(stage_ptr(j), &tm_x, (i1 % p.kblocks1) * 64, 0, &full[j % S]);                     // rows past m: zeros
     };
     if (lane == 0) {
       // The weights of the first stages do not depend on the kernel before this one: they are requested before
@@ -168,7 +161,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       for (int i = 0; i < win && ok; ++i) {
         const int i2 = it2_lo + i, tile = i2 / p.kblocks2, kb = i2 - tile * p.kblocks2;
         if (!wait_stage(it + i, 81)) break;
-        mbar_arrive_expect_tx(&full[(it + i) % S], w_bytes + t_bytes);
+        mbar_arrive_expect_tx(&full[(it + i) % S], lane_bytes + t2_bytes);
         tma_load_2d(stage_ptr(it + i), &tm_d, kb * 64, tile * 128, &full[(it + i) % S]);
       }
     }
@@ -182,7 +175,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const unsigned long long t0 = global_timer_ns();
       for (int i2 = it2_lo + lane; i2 < it2_hi && mine; i2 += 32) {
         const int* c = &counters[i2 % p.kblocks2];
-        while (ld_acquire(c) < 1) {
+        while (ld_acquire(c) < kTilesPerSlab) {
           if (global_timer_ns() - t0 > kWaitTimeoutNs) {
             mine = false;
             break;
@@ -198,24 +191,25 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       // the slabs were written with ordinary stores by other CTAs: order the bulk (async-proxy) reads after the acquires
       asm volatile("fence.proxy.async.global;" ::: "memory");
       for (int i = 0; i < win; ++i)
-        tma_load_2d(stage_ptr(it + i) + w_bytes, &tm_act, ((it2_lo + i) % p.kblocks2) * 64, 0, &full[(it + i) % S]);
+        tma_load_2d(stage_ptr(it + i) + lane_bytes, &tm_act, ((it2_lo + i) % p.kblocks2) * 64, 0, &full[(it + i) % S]);
       it += win;
       for (int i2 = it2_lo + win; i2 < it2_hi && ok; ++i2, ++it) {
         const int tile = i2 / p.kblocks2, kb = i2 - tile * p.kblocks2;
         if (!wait_stage(it, 81)) break;
-        mbar_arrive_expect_tx(&full[it % S], w_bytes + t_bytes);
+        mbar_arrive_expect_tx(&full[it % S], lane_bytes + t2_bytes);
         tma_load_2d(stage_ptr(it), &tm_d, kb * 64, tile * 128, &full[it % S]);
-        tma_load_2d(stage_ptr(it) + w_bytes, &tm_act, kb * 64, 0, &full[it % S]);
+        tma_load_2d(stage_ptr(it) + lane_bytes, &tm_act, kb * 64, 0, &full[it % S]);
       }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc(128, static_cast<uint32_t>(p.ntok), 1, 1);
+      const uint32_t idesc1 = umma_idesc(128, 2 * kFfTile1, 1, 1);
+      const uint32_t idesc2 = umma_idesc(128, static_cast<uint32_t>(p.ntok), 1, 1);
       const uint32_t S = static_cast<uint32_t>(p.stages);
       uint32_t it = 0, ui = 0;
       bool ok = true;
-      auto unit = [&](int kblocks) {
+      auto unit = [&](int kblocks, uint32_t idesc) {
         const uint32_t ab = ui & 1u;
         if (!mbar_spin_wait(&tmem_empty[ab], ((ui >> 1) & 1u) ^ 1u)) {
           report_error(p.err, kErrBarrierTimeout, 83, static_cast<int>(ui));
@@ -235,17 +229,17 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * p.stage_bytes);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16(d0, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(a_addr + w_bytes + k * 32), idesc,
+            umma_bf16(d0, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(a_addr + lane_bytes + k * 32), idesc,
                       (kb > 0 || k > 0) ? 1u : 0u);
           umma_commit(&empty[s]);
         }
         umma_commit(&tmem_full[ab]);
         ++ui;
       };
-      for (int tile = b; tile < p.tiles1 && ok; tile += gridDim.x) unit(p.kblocks1);
+      for (int tile = b; tile < p.tiles1 && ok; tile += gridDim.x) unit(p.kblocks1, idesc1);
       for (int i2 = it2_lo; i2 < it2_hi && ok;) {          // segments of the run, cut at tile boundaries
         const int seg_end = min(it2_hi, (i2 / p.kblocks2 + 1) * p.kblocks2);
-        unit(seg_end - i2);
+        unit(seg_end - i2, idesc2);
         i2 = seg_end;
       }
       umma_commit(drain);   // tensor memory is released only after every MMA has completed
@@ -255,8 +249,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   } else {
     // -------------------------------- epilogue --------------------------------
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
-    const bool is_up = q >= 2;                   // lanes 64-127 hold the up rows
-    const int f = (q & 1) * 32 + lane;           // phase 1: feature within the tile
+    const int row = q * 32 + lane;               // phase 1: token; phase 2: output feature within the tile
     uint32_t ui = 0;
     bool ok = true;
     pdl_wait();                                  // before the first global write
@@ -266,41 +259,36 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         report_error(p.err, kErrBarrierTimeout, 86, static_cast<int>(ui));
         ok = false;
       }
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * 128;
-      if (ok) tc_fence_after_sync();
-      if (ok && is_up) {
-        for (int c0 = 0; c0 < p.ntok; c0 += 32) {
-          uint32_t u[32];
-          tmem_ld_32x32(taddr + c0, u);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) exch[(c0 + j) * kFfTile1 + f] = __uint_as_float(u[j]);
-        }
+      if (ok) {
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * 128;
+        uint32_t g[32], u[32];
+        tmem_ld_32x32(taddr, g);
+        tmem_ld_32x32(taddr + kFfTile1, u);
+        tmem_ld_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[ab]);
-      }
-      named_bar_sync(1, 128);                    // the up values of the tile are in shared memory
-      if (ok && !is_up) {
-        __nv_bfloat16* dst = p.act + static_cast<size_t>(tile) * kFfTile1 + f;
-        for (int c0 = 0; c0 < p.ntok; c0 += 32) {
-          uint32_t g[32];
-          tmem_ld_32x32(taddr + c0, g);
-          tmem_ld_wait();
-          // every one of the ntok rows is written (rows past m hold silu(0) * 0 = 0): phase 2 reads whole tiles
+        // every one of the 128 rows is written (rows past m hold silu(0) * 0 = 0): phase 2 reads whole tiles
+        __nv_bfloat16* dst = p.act + static_cast<size_t>(row) * p.inter + tile * kFfTile1;
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            dst[static_cast<size_t>(c0 + j) * p.inter] =
-                __float2bfloat16_rn(silu_mul(__uint_as_float(g[j]), exch[(c0 + j) * kFfTile1 + f]));
+        for (int j = 0; j < 32; j += 8) {
+          uint4 pk;
+          pk.x = pack_bf16x2(silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j])),
+                             silu_mul(__uint_as_float(g[j + 1]), __uint_as_float(u[j + 1])));
+          pk.y = pack_bf16x2(silu_mul(__uint_as_float(g[j + 2]), __uint_as_float(u[j + 2])),
+                             silu_mul(__uint_as_float(g[j + 3]), __uint_as_float(u[j + 3])));
+          pk.z = pack_bf16x2(silu_mul(__uint_as_float(g[j + 4]), __uint_as_float(u[j + 4])),
+                             silu_mul(__uint_as_float(g[j + 5]), __uint_as_float(u[j + 5])));
+          pk.w = pack_bf16x2(silu_mul(__uint_as_float(g[j + 6]), __uint_as_float(u[j + 6])),
+                             silu_mul(__uint_as_float(g[j + 7]), __uint_as_float(u[j + 7])));
+          *reinterpret_cast<uint4*>(dst + j) = pk;
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[ab]);
       }
-      named_bar_sync(2, 128);                    // the slab is written; the exchange buffer is free again
+      named_bar_sync(1, 128);                      // the tile is written by all four epilogue warps
       if (ok && warp == 2 && lane == 0) {
-        __threadfence();                         // cumulative: covers the stores the barrier ordered before it
-        red_release_add(&counters[tile], 1);
+        __threadfence();                           // cumulative: covers the stores the barrier ordered before it
+        red_release_add(&counters[tile / kTilesPerSlab], 1);
       }
     }
     const int tok0 = (b * 32) % p.ntok;          // every CTA starts its walk over the tokens elsewhere
@@ -314,7 +302,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * 128;
-      const int feat = tile * 128 + q * 32 + lane;
+      const int feat = tile * 128 + row;
       for (int cc = 0; cc < p.ntok; cc += 32) {
         const int c0 = (tok0 + cc) % p.ntok;
         uint32_t v[32];
@@ -369,7 +357,11 @@ size_t ffn_fused_workspace_bytes(int inter) {
 }
 
 bool ffn_fused_ok(int m, int k, int inter, int n_out) {
+  // Worth it while prologues and pipeline fills of a launch chain weigh more than this kernel's re-reading of x
+  // by every CTA: weights of a few tens of MB.  Larger FFNs keep the chain of stream-K GEMMs.
+  const size_t weight_bytes = (static_cast<size_t>(2) * inter * k + static_cast<size_t>(n_out) * inter) * 2;
   return m > 0 && m <= 128 && k % 8 == 0 && inter % 64 == 0 && inter >= 64 && n_out % 4 == 0 &&
+         weight_bytes <= (static_cast<size_t>(64) << 20) &&
          sizeof(int) * (kFfHeaderInts + static_cast<size_t>(inter) / 64) <= kFfHeaderBytes;
 }
 
@@ -391,18 +383,11 @@ int ffn_fused_launch(const void* x, const void* w_gate_up, const void* w_down, f
   p.tiles2 = (n_out + 127) / 128;
   p.kblocks2 = inter / 64;
   p.iters2 = p.tiles2 * p.kblocks2;
-  // Phase-2 shares.  CTAs b < heavy have one more phase-1 tile (kblocks1 pipeline iterations) than the others;
-  // they take that many fewer phase-2 iterations, as far as the totals allow.
-  p.heavy = p.tiles1 % grid;
-  const long long extra = static_cast<long long>(p.heavy) * p.kblocks1;
-  const long long level = (p.iters2 + extra) / grid;                 // iterations per CTA if all were equal
-  p.n2_heavy = static_cast<int>(level > p.kblocks1 ? level - p.kblocks1 : 0);
-  const int light = grid - p.heavy;                                    // >= 1: heavy < grid
-  const long long rest = p.iters2 - static_cast<long long>(p.heavy) * p.n2_heavy;
-  p.n2_base = static_cast<int>(rest / light);
-  p.n2_rem = static_cast<int>(rest % light);
-  p.stage_bytes = 128 * 128 + static_cast<uint32_t>(p.ntok) * 128;
-  const size_t fixed = 1024 + static_cast<size_t>(p.ntok) * kFfTile1 * 4 + (2 * kFfMaxStages + 5) * 8 + 16;
+  p.n2_base = p.iters2 / grid;
+  p.n2_rem = p.iters2 % grid;
+  // a stage holds a phase-1 K block (x tile 16 KB + gate | up tiles 8 KB) or a phase-2 one (Wd tile 16 KB + activation)
+  p.stage_bytes = 128 * 128 + (p.ntok * 128 > 2 * kFfTile1 * 128 ? static_cast<uint32_t>(p.ntok) * 128 : 2 * kFfTile1 * 128);
+  const size_t fixed = 1024 + (2 * kFfMaxStages + 5) * 8 + 16;
   int stages = static_cast<int>((227 * 1024 - fixed) / p.stage_bytes);
   if (stages > kFfMaxStages) stages = kFfMaxStages;
   p.stages = stages;
@@ -412,7 +397,7 @@ int ffn_fused_launch(const void* x, const void* w_gate_up, const void* w_down, f
 
   CUtensorMap tm_x, tm_gu, tm_act, tm_d;
   int st = make_tensor_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, m, k, static_cast<uint64_t>(k) * 2, 64,
-                              p.ntok, CU_TENSOR_MAP_SWIZZLE_128B);
+                              128, CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != kOk) return st;
   st = make_tensor_map_2d(&tm_gu, w_gate_up, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(2) * inter, k,
                           static_cast<uint64_t>(k) * 2, 64, kFfTile1, CU_TENSOR_MAP_SWIZZLE_128B);

@@ -48,8 +48,9 @@ class SwiGLUFFN:
 
 
 class DecoderLayer:
-    # kernels of one step: RMSNorm, QKV GEMM, RoPE + append, attention, merge, O GEMM, RMSNorm, fused FFN, cast
-    launches_per_step = 9
+    # kernels of one step: RMSNorm, QKV GEMM, RoPE + append, attention, merge, O GEMM, RMSNorm, gate/up GEMM,
+    # SwiGLU, down GEMM, cast
+    launches_per_step = 11
 
     def __init__(self, t: dict, *, num_heads: int, kv_heads: int, head_dim: int, block_size: int, eps: float,
                  scale: float):
