@@ -314,10 +314,14 @@ PTO_API int pto_scale_rows(const void* x, const float* w, int w_stride, const in
  *   x fp8 [rows, k], x_scale fp32 [rows][k / 128], offsets int32 [experts + 1]
  * swiglu = 1: w_rows = 2 * n_out (gate rows then up rows); out bf16 [rows, n_out] =
  *             bf16(silu(gate) * up) (re-quantise it with pto_quantize_rows for the down projection).
- * swiglu = 0: w_rows = n_out; out bf16 [rows, n_out] = acc * route_w[row] (route_w may be NULL). */
+ * swiglu = 0: w_rows = n_out; out bf16 [rows, n_out]: row (out_rows ? out_rows[r] : r) = acc[r] * route_w[r]
+ *             (route_w may be NULL; out_rows, int32 [rows] or NULL, lets the expert-parallel receiver get its
+ *             results back in the order the rows arrived in, ready to be sent home; a mapped row outside
+ *             [0, rows) is not written). */
 PTO_API int pto_moe_expert_gemm(int swiglu, const void* w, const float* w_scale, int experts, int w_rows,
                                 int n_out, int k, const void* x, const float* x_scale, const int32_t* offsets,
-                                int rows, const float* route_w, void* out, int32_t* err, void* stream);
+                                int rows, const float* route_w, const int32_t* out_rows, void* out, int32_t* err,
+                                void* stream);
 
 /* Combine (combine_step, test_l3_ep_dispatch_combine.py:337-402): y[t] = sum_k fp32(rows[pos[t*topk+k]])
  * (+ fp32(shared[t]) if given), k ascending; written as bf16 (y_bf16) and/or fp32 (y_f32).  `rows` holds

@@ -90,7 +90,8 @@ int moe_combine_launch(const void* rows, const int32_t* pos, const void* shared,
 // moe_gemm.cu
 int moe_gemm_fp8_launch(int swiglu, const void* w, const float* w_scale, int experts, int w_rows_per_expert,
                         int n_out, int k, const void* x, const float* x_scale, const int32_t* offsets,
-                        int total_rows, const float* route_w, void* out, int* err, cudaStream_t stream);
+                        int total_rows, const float* route_w, const int32_t* out_rows, void* out, int* err,
+                        cudaStream_t stream);
 
 // matmul_mx.cu
 int matmul_mx_launch(const void* a, const void* a_scale, int a_scale_layout, const void* b_t, const void* b_scale,

@@ -51,6 +51,7 @@ struct MoeGemmParams {
   const float* w_scale;     // [experts][w_rows_per_expert / 128][kblocks]
   const float* x_scale;     // [rows][kblocks]
   const float* route_w;     // [rows] or NULL
+  const int32_t* out_rows;  // [rows] or NULL: output row of each input row (plain mode)
   __nv_bfloat16* out;       // [rows][n_out]
   int total_rows, stages;
   int* err;
@@ -357,7 +358,9 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           const int row = row0 + col0 + j;
           if (row < row_end) {
             const float wgt = p.route_w ? p.route_w[row] : 1.f;
-            p.out[static_cast<size_t>(row) * p.n_out + feat] = __float2bfloat16_rn(acc[j] * wgt);
+            const int orow = p.out_rows ? p.out_rows[row] : row;     // e.g. back to the order the rows arrived in
+            if (orow >= 0 && orow < p.total_rows)
+              p.out[static_cast<size_t>(orow) * p.n_out + feat] = __float2bfloat16_rn(acc[j] * wgt);
           }
         }
       }
@@ -371,23 +374,26 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 }  // namespace
 
 // swiglu = 1: w rows per expert = 2 * n_out (gate rows then up rows), out = bf16(silu(g) * u) [rows, n_out];
-// swiglu = 0: w rows per expert = n_out, out = bf16(acc * route_w[row]).
+// swiglu = 0: w rows per expert = n_out, out[out_rows ? out_rows[row] : row] = bf16(acc * route_w[row]).
 // w: fp8 [experts * w_rows_per_expert, k] K-major; w_scale [experts][w_rows_per_expert/128][k/128];
 // x: fp8 [rows, k]; x_scale [rows][k/128]; offsets int32 [experts + 1] (device).
 int moe_gemm_fp8_launch(int swiglu, const void* w, const float* w_scale, int experts, int w_rows_per_expert,
                         int n_out, int k, const void* x, const float* x_scale, const int32_t* offsets,
-                        int total_rows, const float* route_w, void* out, int* err, cudaStream_t stream) {
+                        int total_rows, const float* route_w, const int32_t* out_rows, void* out, int* err,
+                        cudaStream_t stream) {
   PTO_REQUIRE(w && w_scale && x && x_scale && offsets && out, "moe_gemm: NULL tensor");
   PTO_REQUIRE(experts > 0 && experts <= 4096, "moe_gemm: 1..4096 experts");
   PTO_REQUIRE(k > 0 && k % 128 == 0 && k <= kMoeMaxKBlocks * 128, "moe_gemm: K must be a multiple of 128, at most 8192");
   PTO_REQUIRE(n_out > 0 && n_out % 128 == 0, "moe_gemm: output features must be a multiple of 128");
   PTO_REQUIRE(w_rows_per_expert == (swiglu ? 2 * n_out : n_out), "moe_gemm: weight rows per expert mismatch");
+  PTO_REQUIRE(!(swiglu && out_rows), "moe_gemm: an output row map applies to the plain mode only");
   if (total_rows <= 0) return kOk;
   MoeGemmParams p;
   p.offsets = offsets; p.experts = experts; p.kblocks = k / 128; p.n_out = n_out;
   p.n_tiles = swiglu ? n_out / 64 : n_out / 128;
   p.w_rows_per_expert = w_rows_per_expert; p.up_row_off = swiglu ? n_out : 0;
-  p.w_scale = w_scale; p.x_scale = x_scale; p.route_w = route_w; p.out = static_cast<__nv_bfloat16*>(out);
+  p.w_scale = w_scale; p.x_scale = x_scale; p.route_w = route_w; p.out_rows = out_rows;
+  p.out = static_cast<__nv_bfloat16*>(out);
   p.total_rows = total_rows; p.err = err;
   const size_t stage_bytes = static_cast<size_t>(2) * 128 * 128;
   const size_t fixed = 1024 + sizeof(float) * static_cast<size_t>(scale_region_floats(swiglu != 0, p.kblocks)) +

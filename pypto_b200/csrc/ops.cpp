@@ -337,9 +337,9 @@ int pto_scale_rows(const void* x, const float* w, int w_stride, const int32_t* c
 
 int pto_moe_expert_gemm(int swiglu, const void* w, const float* w_scale, int experts, int w_rows, int n_out, int k,
                         const void* x, const float* x_scale, const int32_t* offsets, int rows, const float* route_w,
-                        void* out, int32_t* err, void* stream) {
+                        const int32_t* out_rows, void* out, int32_t* err, void* stream) {
   return pto::moe_gemm_fp8_launch(swiglu, w, w_scale, experts, w_rows, n_out, k, x, x_scale, offsets, rows, route_w,
-                                  out, err, static_cast<cudaStream_t>(stream));
+                                  out_rows, out, err, static_cast<cudaStream_t>(stream));
 }
 
 int pto_moe_combine(const void* rows, const int32_t* pos, const void* shared, int tokens, int topk, int hidden,

@@ -150,13 +150,16 @@ class EpExchanger:
             timer("unpack")
         return d
 
-    def give_back(self, d: Dispatched, y_grouped: torch.Tensor, timer=None) -> torch.Tensor:
-        """y_grouped [capacity, H] (one result row per grouped row) -> [routes, H] in this rank's sorted route
-        order (row ``Dispatched.pos[t*K + k]`` belongs to route (t, k))."""
+    def give_back(self, d: Dispatched, y_grouped: torch.Tensor, timer=None, in_arrival_order: bool = False) -> torch.Tensor:
+        """y_grouped [capacity, H] (one result row per grouped row, or already one per arrival row with
+        ``in_arrival_order``) -> [routes, H] in this rank's sorted route order (row ``Dispatched.pos[t*K + k]``
+        belongs to route (t, k))."""
         if d.grouped_of is None:
             return y_grouped
         shape = tuple(y_grouped.shape[1:])
-        if d.rows:
+        if in_arrival_order and d.rows:
+            y_arrival = y_grouped
+        elif d.rows:
             (y_arrival,) = ops.gather_rows([y_grouped], d.grouped_of, div=1, rows=d.rows)
         else:
             y_arrival = torch.zeros((1,) + shape, dtype=y_grouped.dtype, device=y_grouped.device)
@@ -228,10 +231,10 @@ class MoELayer:
         logits = ops.linear(x, self.gate_packed)
         return ops.moe_topk(logits, self.bias, self.topk, is_logits=True)
 
-    def _experts(self, weights: dict, xq, xs, offsets, route_w, rows=None):
+    def _experts(self, weights: dict, xq, xs, offsets, route_w, out_rows=None):
         act = ops.moe_expert_gemm(True, weights["w_gu"], weights["s_gu"], xq, xs, offsets)
         act_q, act_s = ops.quantize_rows(act)
-        return ops.moe_expert_gemm(False, weights["w_d"], weights["s_d"], act_q, act_s, offsets, route_w)
+        return ops.moe_expert_gemm(False, weights["w_d"], weights["s_d"], act_q, act_s, offsets, route_w, out_rows)
 
     def forward(self, x: torch.Tensor, routing=None, timer=None):
         """x bf16 [T, H] (this rank's tokens) -> (y bf16 [T, H], idx int32 [T, k], w fp32 [T, k])."""
@@ -252,13 +255,16 @@ class MoELayer:
                 shared_out = self._experts(self.shared, xq, xs, self._whole(t, x.device), None)
         d = self.exchanger.dispatch(idx.reshape(-1), [(xq, k), (xs, k), (w.reshape(-1, 1), 1)], timer=timer)
         xq_g, xs_g, w_g = d.parts
+        # with ranks to return to, the down projection writes its rows straight in arrival order (no regrouping pass)
+        in_arrival_order = d.grouped_of is not None
         if d.capacity > 0:
-            y_g = self._experts(self.routed, xq_g, xs_g, d.offsets, w_g.reshape(-1))
+            y_g = self._experts(self.routed, xq_g, xs_g, d.offsets, w_g.reshape(-1),
+                                d.arrival_of if in_arrival_order else None)
         else:
             y_g = torch.empty(0, self.hidden, dtype=torch.bfloat16, device=x.device)
         if timer:
             timer("experts")
-        y_rows = self.exchanger.give_back(d, y_g, timer=timer)
+        y_rows = self.exchanger.give_back(d, y_g, timer=timer, in_arrival_order=in_arrival_order)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
             for tns in (xq, xs, shared_out):

@@ -463,11 +463,12 @@ def scale_rows(x: torch.Tensor, w: torch.Tensor, w_stride: int = 1, count: torch
 
 
 def moe_expert_gemm(swiglu: bool, w: torch.Tensor, w_scale: torch.Tensor, x: torch.Tensor, x_scale: torch.Tensor,
-                    offsets: torch.Tensor, route_w: torch.Tensor | None = None):
+                    offsets: torch.Tensor, route_w: torch.Tensor | None = None, out_rows: torch.Tensor | None = None):
     """Grouped FP8 GEMM over tokens sorted by expert.  w [E, rows, K] e4m3 (K-major), w_scale
     [E, rows/128, K/128]; x [R, K] e4m3, x_scale [R, K/128]; offsets int32 [E+1].
     swiglu: rows = 2*n_out (gate then up), returns bf16(silu(g)*u) [R, n_out];
-    else returns bf16 [R, rows] scaled by route_w."""
+    else returns bf16 [R, rows] scaled by route_w, row r written at out_rows[r] when a row map is given (rows that
+    nothing maps to are left as allocated)."""
     dev = _need_cuda(w, w_scale, x, x_scale, offsets)
     e, w_rows, k = w.shape
     r = x.shape[0]
@@ -481,7 +482,7 @@ def moe_expert_gemm(swiglu: bool, w: torch.Tensor, w_scale: torch.Tensor, x: tor
         _lib.check(_lib.load().pto_moe_expert_gemm(
             1 if swiglu else 0, w.data_ptr(), w_scale.data_ptr(), e, w_rows, n_out, k, x.data_ptr(),
             x_scale.data_ptr(), offsets.data_ptr(), r, route_w.data_ptr() if route_w is not None else None,
-            out.data_ptr(), _err_ptr(dev), _stream_ptr(dev)))
+            out_rows.data_ptr() if out_rows is not None else None, out.data_ptr(), _err_ptr(dev), _stream_ptr(dev)))
     return out
 
 

@@ -18,19 +18,17 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SHAPE = dict(tokens=256, hidden=7168, inter=256, experts=16, topk=4)
 
 
-def _worker(rank, world, uid, q):
+def _worker(rank, world, uid, case_path, q):
     try:
         sys.path.insert(0, ROOT)
-        import oracle
-        from oracle import moe as omoe
         from pypto_b200 import ops
         from pypto_b200.comm import Communicator
         from pypto_b200.moe import MoELayer, PhaseTimer
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         torch.cuda.set_device(rank)
-        tokens, hidden, inter, experts, topk = (SHAPE[k] for k in ("tokens", "hidden", "inter", "experts", "topk"))
-        m = oracle.inputs.moe_inputs(tokens=tokens, hidden=hidden, inter=inter, n_experts=experts, topk=topk, seed=9)
-        y_exp, idx_exp, w_exp = omoe.moe_layer(m["x"], m["gate_w"], m["bias"], m["routed"], m["shared"], topk)
+        tokens, experts, topk = SHAPE["tokens"], SHAPE["experts"], SHAPE["topk"]
+        case = torch.load(case_path, weights_only=True)       # inputs and the oracle's layer output, made once by the parent
+        m, y_exp, idx_exp, w_exp = case["inputs"], case["y"], case["idx"], case["w"]
         L, tl = experts // world, tokens // world
         mine = {k: v[rank * L:(rank + 1) * L].cuda() for k, v in m["routed"].items()}
         comm = Communicator(rank, world, uid, rank)          # collective: after everything that can fail alone
@@ -91,12 +89,25 @@ def run_ranks(target, world, args=(), timeout=420):
     return results
 
 
+@pytest.fixture(scope="module")
+def oracle_case(tmp_path_factory):
+    """Inputs of the case and the oracle's single-process layer output, computed once for every world size."""
+    import oracle
+    from oracle import moe as omoe
+    m = oracle.inputs.moe_inputs(tokens=SHAPE["tokens"], hidden=SHAPE["hidden"], inter=SHAPE["inter"],
+                                 n_experts=SHAPE["experts"], topk=SHAPE["topk"], seed=9)
+    y, idx, w = omoe.moe_layer(m["x"], m["gate_w"], m["bias"], m["routed"], m["shared"], SHAPE["topk"])
+    path = str(tmp_path_factory.mktemp("ep_case") / "case.pt")
+    torch.save(dict(inputs={k: v for k, v in m.items() if k != "topk"}, y=y, idx=idx, w=w), path)
+    return path
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_expert_parallel_layer_matches_oracle(world):
+def test_expert_parallel_layer_matches_oracle(world, oracle_case):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from pypto_b200 import comm
-    results = run_ranks(_worker, world, args=(comm.unique_id(),))
+    results = run_ranks(_worker, world, args=(comm.unique_id(), oracle_case))
     for rank, _ok, rel, rel2, frac_same, status, phases in results:
         assert status == 0
         assert rel < 2e-2 and rel2 < 2e-2 and frac_same > 0.97, (rank, rel, rel2, frac_same)
