@@ -678,13 +678,15 @@ def run_moe(args, d: Dist):
 
     ms, clocks, rounds = timed(lambda: layer.forward(x), d, steps, args.warmup)
     ops.check_device_status()
+    if layer.status()[0]:
+        raise RuntimeError(f"the MoE layer's kernels reported an error: {layer.status()}")
     ms_max, = d.reduce([ms], "MAX")
     sec = ms_max / 1e3 / steps
     flops = omoe.moe_flops(T, H, I, E, K)
     w_bytes = sum(v.numel() * v.element_size() for v in layer.routed.values()) + \
         sum(v.numel() * v.element_size() for v in layer.shared.values())
-    # per-phase device times of one step (CUDA events between the phases on the main stream; the shared expert
-    # runs beside them on its own stream), max over ranks
+    # per-phase device times of one step (CUDA events the layer records between its phases on the main stream; the
+    # shared expert runs beside them on its own stream), max over ranks
     ph = {}
     for _ in range(2):
         timer = PhaseTimer()
@@ -741,7 +743,7 @@ def run_moe(args, d: Dist):
                         "l2": f"expert weights per GPU {w_bytes / 1e9:.2f} GB, larger than L2",
                         "parallelism": f"ep{d.world}" if d.world > 1 else "single GPU, all experts local",
                         "rounds": rounds},
-                launches=(22 if d.world > 1 else 16) * steps, clocks=clocks,
+                launches=(17 if d.world > 1 else 15) * steps, clocks=clocks,
                 roofline={"bound": "hbm", "achieved": w_bytes / t_rank / 1e9, "peak": pk["hbm"], "unit": "GB/s",
                           "frac": w_bytes / t_rank / 1e9 / pk["hbm"], "traffic": NCU_TRAFFIC["moe"],
                           "peak_source": pk["source"],

@@ -375,6 +375,41 @@ PTO_API int pto_all_to_all(pto_comm* c, const void* send, void* recv, size_t byt
 PTO_API int pto_all_to_all_v(pto_comm* c, const void* send, const int64_t* send_rows, void* recv,
                              const int64_t* recv_rows, size_t row_bytes, void* stream);
 
+/* ---- the mixture-of-experts layer as one runtime object ---- */
+
+/* Gate + top-k routing, dispatch, grouped FP8 expert FFN and combine behind one call; with a communicator the
+ * experts are split over its ranks (global expert e on rank e / (n_experts / nranks)) and a forward call performs
+ * the reference's dispatch_step / local_expert_step / combine_step protocol
+ * (tests/st/distributed/test_l3_ep_dispatch_combine.py:104-402) with one payload exchange each way.
+ * Weights stay owned by the caller and must outlive the layer:
+ *   gate_packed  bf16 [n_experts, hidden] (pto_pack_weight of the [hidden, n_experts] gate); bias fp32 [n_experts]
+ *   w_gu e4m3 [local, 2*inter, hidden] (gate rows, then up rows), s_gu fp32 [local, 2*inter/128, hidden/128]
+ *   w_d  e4m3 [local, hidden, inter],   s_d  fp32 [local, hidden/128, inter/128]
+ *   sh_* the same for one shared expert, or all NULL
+ * pto_moe_layer_create allocates every buffer a step needs, sized for max_tokens tokens per call and the worst
+ * case of rows arriving at this rank; with a communicator it and every forward call are collective. */
+typedef struct pto_moe_layer_desc {
+  int hidden, inter, n_experts, topk, max_tokens;
+  const void* gate_packed;
+  const float* bias;
+  const void* w_gu; const float* s_gu; const void* w_d; const float* s_d;
+  const void* sh_w_gu; const float* sh_s_gu; const void* sh_w_d; const float* sh_s_d;
+  pto_comm* comm; /* NULL: one GPU, all experts local */
+} pto_moe_layer_desc;
+typedef struct pto_moe_layer pto_moe_layer;
+PTO_API int pto_moe_layer_create(const pto_moe_layer_desc* desc, pto_moe_layer** out);
+PTO_API int pto_moe_layer_destroy(pto_moe_layer* layer); /* idempotent on NULL */
+/* x bf16 [tokens, hidden] -> y bf16 [tokens, hidden].  idx_in / w_in (int32 / fp32 [tokens, topk], both or
+ * neither) replace the layer's own routing; idx_out / w_out (may be NULL) receive the routing used.  phase_ms
+ * (host float[8] or NULL) receives the device time of route+quantise, plan, pack, exchange out, unpack, experts,
+ * exchange back, combine; asking for it makes the call wait for the step.  The host waits once per call for the
+ * row counts of the exchange (not at all on one GPU). */
+PTO_API int pto_moe_layer_forward(pto_moe_layer* layer, const void* x, int tokens, const int32_t* idx_in,
+                                  const float* w_in, void* y, int32_t* idx_out, float* w_out, float* phase_ms,
+                                  void* stream);
+/* Reads (and clears) the layer's device error word, see pto_device_status; synchronises `stream`. */
+PTO_API int pto_moe_layer_status(pto_moe_layer* layer, int32_t out[4], void* stream);
+
 #ifdef __cplusplus
 }
 #endif

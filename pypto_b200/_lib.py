@@ -99,6 +99,20 @@ SIGNATURES = {
     "pto_paged_gather": (_i, [_p, _i64, _i64, _i, _p, _i64, _p, _i64, _i, _i64, _i64, _p, _p, _p]),
 }
 
+class MoeLayerDesc(C.Structure):
+    _fields_ = [("hidden", C.c_int), ("inter", C.c_int), ("n_experts", C.c_int), ("topk", C.c_int),
+                ("max_tokens", C.c_int), ("gate_packed", C.c_void_p), ("bias", C.c_void_p), ("w_gu", C.c_void_p),
+                ("s_gu", C.c_void_p), ("w_d", C.c_void_p), ("s_d", C.c_void_p), ("sh_w_gu", C.c_void_p),
+                ("sh_s_gu", C.c_void_p), ("sh_w_d", C.c_void_p), ("sh_s_d", C.c_void_p), ("comm", C.c_void_p)]
+
+
+SIGNATURES.update({
+    "pto_moe_layer_create": (_i, [C.POINTER(MoeLayerDesc), C.POINTER(_p)]),
+    "pto_moe_layer_destroy": (_i, [_p]),
+    "pto_moe_layer_forward": (_i, [_p, _p, _i, _p, _p, _p, _p, _p, C.POINTER(C.c_float), _p]),
+    "pto_moe_layer_status": (_i, [_p, _i32p, _p]),
+})
+
 _lock = threading.Lock()
 _lib = None
 

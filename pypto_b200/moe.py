@@ -11,7 +11,10 @@ The reference moves rows with one-sided puts into peer windows; here a step is
     receive-plan kernel -> unpack -> experts -> ONE all-to-all-v of result rows -> combine
 
 with exact row counts only.  Everything that touches data is a kernel of the library or an NCCL
-call issued through the C ABI (``pypto_b200.comm``); torch supplies buffers and streams.
+call issued through the C ABI; ``MoELayer.forward`` is ONE call into the runtime's layer object
+(``pto_moe_layer_forward``), which issues the whole step.  ``EpExchanger`` is the same exchange as a
+building block with any payload, for programs that dispatch other data (the reference's own
+expert-parallel test program does).  torch supplies buffers and streams.
 
 Launch model: one process per GPU.  With ``comm=None`` the layer runs on one GPU with all experts
 local and no collective.
@@ -184,7 +187,13 @@ class PhaseTimer:
         e.record()
         self.marks.append((name, e))
 
+    def ingest(self, phases: dict) -> None:
+        """Phase times measured inside the runtime's own forward call (``pto_moe_layer_forward``)."""
+        self.given = dict(phases)
+
     def result(self) -> dict:
+        if getattr(self, "given", None) is not None:
+            return dict(self.given)
         torch.cuda.synchronize()
         out: dict = {}
         for (_n0, e0), (n1, e1) in zip(self.marks, self.marks[1:]):
@@ -214,7 +223,7 @@ class MoELayer:
         if self.n_experts != self.local_experts * self.world:
             raise ValueError("experts must be split evenly over the ranks")
         self.topk = topk
-        self.exchanger = EpExchanger(comm, local_experts)
+        self._handle, self._handle_tokens = None, 0
 
     @classmethod
     def from_packed(cls, gate_packed: torch.Tensor, bias: torch.Tensor, routed: dict, shared: dict | None,
@@ -231,63 +240,88 @@ class MoELayer:
         logits = ops.linear(x, self.gate_packed)
         return ops.moe_topk(logits, self.bias, self.topk, is_logits=True)
 
-    def _experts(self, weights: dict, xq, xs, offsets, route_w, out_rows=None):
-        act = ops.moe_expert_gemm(True, weights["w_gu"], weights["s_gu"], xq, xs, offsets)
-        act_q, act_s = ops.quantize_rows(act)
-        return ops.moe_expert_gemm(False, weights["w_d"], weights["s_d"], act_q, act_s, offsets, route_w, out_rows)
+    PHASES = ("route_quantize", "plan", "pack", "exchange_out", "unpack", "experts", "exchange_back", "combine")
+
+    def _native(self, tokens: int, dev):
+        """The runtime's layer object (``pto_moe_layer``), created on first use and again if a call brings more
+        tokens than it was sized for.  With a communicator, creation is collective like the forward call."""
+        import ctypes as C
+
+        from . import _lib
+        h = getattr(self, "_handle", None)
+        if h is not None and self._handle_tokens >= tokens:
+            return h
+        lib = _lib.load()
+        if h is not None:
+            _lib.check(lib.pto_moe_layer_destroy(h))
+            self._handle = None
+        d = _lib.MoeLayerDesc()
+        d.hidden, d.inter = self.hidden, self.routed["w_d"].shape[2]
+        d.n_experts, d.topk, d.max_tokens = self.n_experts, self.topk, tokens
+        d.gate_packed, d.bias = self.gate_packed.data_ptr(), self.bias.data_ptr()
+        for k in ("w_gu", "s_gu", "w_d", "s_d"):
+            setattr(d, k, self.routed[k].data_ptr())
+            setattr(d, "sh_" + k, self.shared[k].data_ptr() if self.shared is not None else None)
+        d.comm = self.comm._h if self.comm is not None else None
+        out = C.c_void_p()
+        with torch.cuda.device(dev):
+            _lib.check(lib.pto_moe_layer_create(C.byref(d), C.byref(out)))
+        self._handle, self._handle_tokens = out, tokens
+        return out
+
+    def close(self) -> None:
+        h = getattr(self, "_handle", None)
+        if h is not None:
+            from . import _lib
+            self._handle = None
+            _lib.check(_lib.load().pto_moe_layer_destroy(h))
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def status(self) -> tuple:
+        """The layer's device error word (code, site, CTA, detail); reading clears it."""
+        import ctypes as C
+
+        from . import _lib
+        h = getattr(self, "_handle", None)
+        if h is None:
+            return (0, 0, 0, 0)
+        words = (C.c_int32 * 4)()
+        dev = self.gate_packed.device
+        with torch.cuda.device(dev):
+            _lib.check(_lib.load().pto_moe_layer_status(h, words, torch.cuda.current_stream(dev).cuda_stream))
+        return tuple(words)
 
     def forward(self, x: torch.Tensor, routing=None, timer=None):
-        """x bf16 [T, H] (this rank's tokens) -> (y bf16 [T, H], idx int32 [T, k], w fp32 [T, k])."""
-        t, _h = x.shape
-        k = self.topk
-        idx, w = routing if routing is not None else self.route(x)
-        xq, xs = ops.quantize_rows(x)
-        if timer:
-            timer("route_quantize")
-        # The shared expert depends on nothing but the quantised tokens: run it on a side stream so
-        # that it fills the GPU while the host waits for the row counts of the exchange.
-        shared_out, side = None, None
-        if self.shared is not None:
-            main = torch.cuda.current_stream()
-            side = self._side_stream(x.device)
-            side.wait_stream(main)
-            with torch.cuda.stream(side):
-                shared_out = self._experts(self.shared, xq, xs, self._whole(t, x.device), None)
-        d = self.exchanger.dispatch(idx.reshape(-1), [(xq, k), (xs, k), (w.reshape(-1, 1), 1)], timer=timer)
-        xq_g, xs_g, w_g = d.parts
-        # with ranks to return to, the down projection writes its rows straight in arrival order (no regrouping pass)
-        in_arrival_order = d.grouped_of is not None
-        if d.capacity > 0:
-            y_g = self._experts(self.routed, xq_g, xs_g, d.offsets, w_g.reshape(-1),
-                                d.arrival_of if in_arrival_order else None)
+        """x bf16 [T, H] (this rank's tokens) -> (y bf16 [T, H], idx int32 [T, k], w fp32 [T, k]).  One call into
+        the runtime (``pto_moe_layer_forward``) issues every kernel and both exchanges of the step."""
+        import ctypes as C
+
+        from . import _lib
+        if not x.is_cuda or x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != self.hidden or not x.is_contiguous():
+            raise ValueError("MoELayer.forward: x must be a contiguous CUDA bf16 [tokens, hidden] tensor")
+        t, dev = x.shape[0], x.device
+        h = self._native(t, dev)
+        y = torch.empty_like(x)
+        if routing is not None:
+            idx, w = routing
+            if idx.dtype != torch.int32 or w.dtype != torch.float32 or tuple(idx.shape) != (t, self.topk) \
+                    or tuple(w.shape) != (t, self.topk) or not idx.is_contiguous() or not w.is_contiguous():
+                raise ValueError("MoELayer.forward: routing must be (int32 [T, k], fp32 [T, k]) contiguous tensors")
+            args = (idx.data_ptr(), w.data_ptr(), y.data_ptr(), None, None)
         else:
-            y_g = torch.empty(0, self.hidden, dtype=torch.bfloat16, device=x.device)
-        if timer:
-            timer("experts")
-        y_rows = self.exchanger.give_back(d, y_g, timer=timer, in_arrival_order=in_arrival_order)
-        if side is not None:
-            torch.cuda.current_stream().wait_stream(side)
-            for tns in (xq, xs, shared_out):
-                tns.record_stream(side)
-        y = ops.moe_combine(y_rows, d.pos, shared_out, t, k)
-        if timer:
-            timer("combine")
+            idx = torch.empty(t, self.topk, dtype=torch.int32, device=dev)
+            w = torch.empty(t, self.topk, dtype=torch.float32, device=dev)
+            args = (None, None, y.data_ptr(), idx.data_ptr(), w.data_ptr())
+        phases = (C.c_float * 8)() if timer is not None else None
+        with torch.cuda.device(dev):
+            _lib.check(_lib.load().pto_moe_layer_forward(h, x.data_ptr(), t, *args, phases,
+                                                         torch.cuda.current_stream(dev).cuda_stream))
+        if timer is not None:
+            timer.ingest(dict(zip(self.PHASES, list(phases))))
         return y, idx, w
 
-    _streams: dict = {}
-    _whole_cache: dict = {}
-
-    def _whole(self, t: int, dev) -> torch.Tensor:
-        """offsets [0, t] of a one-expert group that spans all tokens (the shared expert)."""
-        key = (dev.index, t)
-        o = MoELayer._whole_cache.get(key)
-        if o is None:
-            o = MoELayer._whole_cache[key] = torch.tensor([0, t], dtype=torch.int32, device=dev)
-        return o
-
-    def _side_stream(self, dev):
-        key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
-        s = MoELayer._streams.get(key)
-        if s is None:
-            s = MoELayer._streams[key] = torch.cuda.Stream(device=dev)
-        return s

@@ -39,8 +39,7 @@ def _worker(rank, world, uid, case_path, q):
             y, _, _ = layer.forward(m["x"][sl].cuda(), routing=(idx_exp[sl].cuda(), w_exp[sl].cuda()))
             torch.cuda.synchronize()
             status = ops.device_status()
-            with torch.cuda.stream(layer._side_stream(y.device)):
-                side_status = ops.device_status()
+            side_status = layer.status()          # the layer's own error word (all of its kernels report there)
             rel = ((y.cpu().float() - y_exp[sl].float()).norm() / y_exp[sl].float().norm()).item()
             timer = PhaseTimer()
             y2, idx2, _ = layer.forward(m["x"][sl].cuda(), timer=timer)     # own routing, a second pass over the exchange

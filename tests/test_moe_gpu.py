@@ -318,6 +318,7 @@ def _layer_vs_oracle(tokens, hidden, inter, experts, topk, seed):
     torch.cuda.synchronize()
     _ops().check_device_status()
     y_own, idx, w = layer.forward(m["x"].cuda())
+    assert layer.status()[0] == 0           # the layer's kernels report into its own error word
     return m, y.cpu().float(), y_exp.float(), idx.cpu(), idx_exp, y_own.cpu().float()
 
 
@@ -333,3 +334,35 @@ def test_moe_layer_matches_oracle(tokens, hidden, inter, experts, topk):
     y_math = omoe.dequant_reference(m["x"], idx_exp.long(), omoe.gate_topk(m["x"], m["gate_w"], m["bias"], topk)[1],
                                     m["routed"], m["shared"])
     assert ((y - y_math).norm() / y_math.norm()).item() < 5e-2
+
+
+def test_moe_layer_object_regrows_times_its_phases_and_reports_bad_routes():
+    """The runtime's layer object behind MoELayer.forward: a call with more tokens than it was sized for builds a
+    larger one; a call with a timer returns the eight phase times; a route to an expert that does not exist is
+    reported in the layer's error word (code 3, the route's index) and the layer stays usable."""
+    from pypto_b200.moe import MoELayer, PhaseTimer
+    tokens, hidden, inter, experts, topk = 96, 512, 256, 8, 2
+    m = oracle.inputs.moe_inputs(tokens=tokens, hidden=hidden, inter=inter, n_experts=experts, topk=topk, shared=False,
+                                 seed=21)
+    y_exp, idx_exp, w_exp = omoe.moe_layer(m["x"], m["gate_w"], m["bias"], m["routed"], None, topk)
+    layer = MoELayer(m["gate_w"].cuda(), m["bias"].cuda(), {k: v.cuda() for k, v in m["routed"].items()}, None, topk)
+    x = m["x"].cuda()
+    y_small, _, _ = layer.forward(x[:32], routing=(idx_exp[:32].cuda(), w_exp[:32].cuda()))
+    first = layer._handle_tokens
+    timer = PhaseTimer()
+    y, _, _ = layer.forward(x, routing=(idx_exp.cuda(), w_exp.cuda()), timer=timer)
+    assert first == 32 and layer._handle_tokens == tokens
+    ph = timer.result()
+    assert set(ph) == set(MoELayer.PHASES) and all(v >= 0 for v in ph.values()) and ph["experts"] > 0
+    assert layer.status()[0] == 0
+    for got, exp in ((y_small.cpu().float(), y_exp[:32].float()), (y.cpu().float(), y_exp.float())):
+        assert ((got - exp).norm() / exp.norm()).item() < 2e-2
+    bad = idx_exp.clone()
+    bad[5, 1] = experts + 3
+    layer.forward(x, routing=(bad.cuda(), w_exp.cuda()))
+    code, site, _cta, detail = layer.status()
+    assert code == 3 and site == 60 and detail == 5 * topk + 1
+    y_again, _, _ = layer.forward(x, routing=(idx_exp.cuda(), w_exp.cuda()))
+    assert layer.status()[0] == 0
+    assert torch.equal(y_again.cpu(), y.cpu())
+    layer.close()
