@@ -197,6 +197,15 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity) {
   return __all_sync(0xffffffffu, ok) != 0;
 }
 
+// Whole-warp wait with ONE polling lane: lane 0 waits, the shuffle hands its result to the others and brings the
+// warp back together.  Thirty-two lanes polling one mbarrier serialise on it, which costs more than the wait
+// itself when sixteen warps do so for every K block.
+__device__ __forceinline__ bool mbar_wait_lane0(uint64_t* bar, uint32_t parity) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // 2-D tiled TMA load into this CTA's shared memory; completion is signalled on
 // `bar` as transaction bytes.  No cluster multicast is used anywhere.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y,
