@@ -287,26 +287,29 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           decode(u + grid, e2, tile2, chunk2);
           if (me == 0) ok = stage_table(n + 1, e2, tile2, chunk2);
         }
-        if (lane == 0 && ok) {
+        if (ok) {   // the whole warp walks the K blocks and waits; one elected lane issues the copies
           const int row0 = offs[e] + chunk * kTN;
           const int wrow = e * p.w_rows_per_expert + tile * (SWIGLU ? 64 : 128);
           const uint32_t end_i = it + static_cast<uint32_t>(p.kblocks);
           for (; next_i < end_i; next_i += 2) {
             const int kb = static_cast<int>(next_i - it);
-            if (!mbar_wait(&empty[st_i], st_ph ^ 1u)) {
-              report_error(p.err, kErrBarrierTimeout, 50, static_cast<int>(next_i));
+            if (!__all_sync(0xffffffffu, mbar_wait(&empty[st_i], st_ph ^ 1u))) {
+              if (lane == 0) report_error(p.err, kErrBarrierTimeout, 50, static_cast<int>(next_i));
               ok = false;
               break;
             }
-            uint8_t* st = smem + st_i * stage_bytes;
-            mbar_arrive_expect_tx(&full[st_i], stage_bytes);
-            if (SWIGLU) {   // two 64-row boxes: gate rows, then the matching up rows
-              tma_load_2d(st, &tm_w, kb * 128, wrow, &full[st_i]);
-              tma_load_2d(st + 64 * 128, &tm_w, kb * 128, wrow + p.up_row_off, &full[st_i]);
-            } else {
-              tma_load_2d(st, &tm_w, kb * 128, wrow, &full[st_i]);
+            if (elect_one()) {
+              uint8_t* st = smem + st_i * stage_bytes;
+              mbar_arrive_expect_tx(&full[st_i], stage_bytes);
+              if (SWIGLU) {   // two 64-row boxes: gate rows, then the matching up rows
+                tma_load_2d(st, &tm_w, kb * 128, wrow, &full[st_i]);
+                tma_load_2d(st + 64 * 128, &tm_w, kb * 128, wrow + p.up_row_off, &full[st_i]);
+              } else {
+                tma_load_2d(st, &tm_w, kb * 128, wrow, &full[st_i]);
+              }
+              tma_load_2d(st + tile_bytes, &tm_x, kb * 128, row0, &full[st_i]);
             }
-            tma_load_2d(st + tile_bytes, &tm_x, kb * 128, row0, &full[st_i]);
+            __syncwarp();
             st_i += 2;                  // the stage count is even: a producer keeps to the stages of its parity
             if (st_i >= static_cast<uint32_t>(p.stages)) {
               st_i -= static_cast<uint32_t>(p.stages);
@@ -314,31 +317,33 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             }
           }
         }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         it += static_cast<uint32_t>(p.kblocks);
         e = e2; tile = tile2; chunk = chunk2;
       }
     } else {
       // ------------------------------- MMA issuers -------------------------------
-      if (lane == 0) {
-        const uint32_t me = static_cast<uint32_t>(warp - 2);
-        const uint32_t idesc = umma_idesc(kTN, 128, 0, 0);  // e4m3 x e4m3 -> fp32; M = tokens, N = features
-        // The issuer does not need the units, only the number of K blocks of this CTA.  Issuer `me` takes the
-        // blocks i with i % 2 == me: stage i % stages, partial buffer i % 4 (me or me + 2).  Stage, buffer and
-        // barrier phases are carried along, and the operand descriptors advance by additions.
-        const int my_units = static_cast<int>(blockIdx.x) < units ? (units - 1 - static_cast<int>(blockIdx.x)) / grid + 1 : 0;
-        const uint32_t total = static_cast<uint32_t>(my_units) * static_cast<uint32_t>(p.kblocks);
-        const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);   // stride byte offset, version, 128-byte swizzle
-        const uint32_t lo0 = ((smem_u32(smem) & 0x3FFFFu) >> 4) | (1u << 16);
-        uint32_t st_i = me, st_ph = 0;       // stage and phase of its `full` barrier
-        uint32_t pb = me, pb_ph = 1;         // partial buffer and the phase of `pempty` to wait for (first use: free)
-        uint32_t i = me;
-        for (; i < total; i += 2) {
-          if (!mbar_wait(&full[st_i], st_ph) || !mbar_wait(&pempty[pb], pb_ph)) {
-            report_error(p.err, kErrBarrierTimeout, 51, static_cast<int>(i));
-            break;
-          }
-          tc_fence_after_sync();
+      // The whole warp walks the loop and waits; one elected lane issues.  Warp-uniform code keeps descriptors and
+      // barrier addresses in uniform registers, which is what the MMA and commit instructions take.
+      const uint32_t me = static_cast<uint32_t>(warp - 2);
+      const uint32_t idesc = umma_idesc(kTN, 128, 0, 0);  // e4m3 x e4m3 -> fp32; M = tokens, N = features
+      // The issuer does not need the units, only the number of K blocks of this CTA.  Issuer `me` takes the
+      // blocks i with i % 2 == me: stage i % stages, partial buffer i % 4 (me or me + 2).  Stage, buffer and
+      // barrier phases are carried along, and the operand descriptors advance by additions.
+      const int my_units = static_cast<int>(blockIdx.x) < units ? (units - 1 - static_cast<int>(blockIdx.x)) / grid + 1 : 0;
+      const uint32_t total = static_cast<uint32_t>(my_units) * static_cast<uint32_t>(p.kblocks);
+      const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);   // stride byte offset, version, 128-byte swizzle
+      const uint32_t lo0 = ((smem_u32(smem) & 0x3FFFFu) >> 4) | (1u << 16);
+      uint32_t st_i = me, st_ph = 0;       // stage and phase of its `full` barrier
+      uint32_t pb = me, pb_ph = 1;         // partial buffer and the phase of `pempty` to wait for (first use: free)
+      uint32_t i = me;
+      for (; i < total; i += 2) {
+        const bool ok = mbar_wait(&full[st_i], st_ph) && mbar_wait(&pempty[pb], pb_ph);
+        if (!__all_sync(0xffffffffu, ok)) {
+          if (lane == 0) report_error(p.err, kErrBarrierTimeout, 51, static_cast<int>(i));
+          break;
+        }
+        tc_fence_after_sync();
+        if (elect_one()) {
           const uint32_t w_lo = lo0 + st_i * (stage_bytes >> 4);
           const uint32_t x_lo = w_lo + (tile_bytes >> 4);
           const uint32_t d0 = tmem_base + pb * 128;
@@ -350,19 +355,21 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           }
           umma_commit(&empty[st_i]);
           umma_commit(&pfull[pb]);
-          st_i += 2;
-          if (st_i >= static_cast<uint32_t>(p.stages)) {
-            st_i -= static_cast<uint32_t>(p.stages);
-            st_ph ^= 1u;
-          }
-          pb ^= 2u;
-          if (pb == me) pb_ph ^= 1u;
         }
-        const uint32_t it = i;
-        // TMEM is released only after every MMA of this thread has completed, also when a wait gave up:
-        // a CTA that exits with tensor-core work in flight ends the whole launch with an error.
+        __syncwarp();
+        st_i += 2;
+        if (st_i >= static_cast<uint32_t>(p.stages)) {
+          st_i -= static_cast<uint32_t>(p.stages);
+          st_ph ^= 1u;
+        }
+        pb ^= 2u;
+        if (pb == me) pb_ph ^= 1u;
+      }
+      // TMEM is released only after every MMA of this warp has completed, also when a wait gave up:
+      // a CTA that exits with tensor-core work in flight ends the whole launch with an error.
+      if (elect_one()) {
         umma_commit(&drain[me]);
-        if (!mbar_wait(&drain[me], 0)) report_error(p.err, kErrBarrierTimeout, 53, static_cast<int>(it));
+        if (!mbar_wait(&drain[me], 0)) report_error(p.err, kErrBarrierTimeout, 53, static_cast<int>(i));
       }
     }
     __syncwarp();
@@ -453,19 +460,20 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const float sa = xsv * lds_f32(ws_a + kb * 4);
         const float sb = SWIGLU ? xsv * lds_f32(ws_a + (kbp + kb) * 4) : sa;
         const unsigned long long sa2 = pack_f32x2(sa, sa), sb2 = pack_f32x2(sb, sb);
-        tmem_ld_wait_regs(ra0, ra1);
+        // the second half joins the first in flight; once both have landed the buffer goes back
         tmem_ld_32x16(lane_base + pb * 128 + cb, rb0);
         tmem_ld_32x16(lane_base + pb * 128 + cb + 16, rb1);
+        tmem_ld_wait_regs(ra0, ra1);
+        tmem_ld_wait_regs(rb0, rb1);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&pempty[pb]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           fma_f32x2(acc_a[j], pack_f32x2(__uint_as_float(ra0[2 * j]), __uint_as_float(ra0[2 * j + 1])), sa2);
           fma_f32x2(acc_a[8 + j], pack_f32x2(__uint_as_float(ra1[2 * j]), __uint_as_float(ra1[2 * j + 1])), sa2);
         }
-        tmem_ld_wait_regs(rb0, rb1);
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&pempty[pb]);
-        if (has_next) open_block(kb + 1, s_next, ph_next);
+        if (has_next) open_block(kb + 1, s_next, ph_next);   // the first half of the next K block loads during the FMAs below
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           fma_f32x2(acc_b[j], pack_f32x2(__uint_as_float(rb0[2 * j]), __uint_as_float(rb0[2 * j + 1])), sb2);

@@ -41,9 +41,9 @@ bool pdl_enabled() {
 
 bool first_use_on_device(int key) {
   static std::mutex mu;
-  static bool seen[8][64] = {};
+  static bool seen[32][64] = {};
   int dev = 0;
-  if (key < 0 || key >= 8 || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+  if (key < 0 || key >= 32 || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
   std::lock_guard<std::mutex> g(mu);
   const bool first = !seen[key][dev];
   seen[key][dev] = true;
