@@ -265,4 +265,59 @@ int op_matmul_mx(Worker* w, const pto_task_args* a) {
                           static_cast<float*>(tptr(t[5], 4)), m, n, k, err, w->stream);
 }
 
+// Mixture-of-experts layer on one GPU (all experts local): sigmoid gate + top-k routing, grouped FP8 expert FFN,
+// shared expert, combine.  The data movement of the reference's expert-parallel program
+// (tests/st/distributed/test_l3_ep_dispatch_combine.py:104-402) with the real expert in place of its stand-in.
+// tensors: x bf16 [T, H], gate bf16 [E, H] (packed), bias fp32 [E],
+//          w_gu e4m3 [E, 2I, H], s_gu fp32 [E, 2I/128, H/128], w_d e4m3 [E, H, I], s_d fp32 [E, H/128, I/128],
+//          the same four for the shared expert ([1, ...]; a shared expert is not optional here),
+//          y bf16 [T, H]
+// scalars: top-k
+int op_moe_layer(Worker* w, const pto_task_args* a) {
+  if (a->n_tensors != 12 || a->n_scalars != 1) return fail(kInvalidArgument, "moe_layer: expects 12 tensors and 1 scalar");
+  const pto_chip_tensor* t = a->tensors;
+  if (t[0].ndims != 2 || t[1].ndims != 2 || t[3].ndims != 3 || t[5].ndims != 3)
+    return fail(kInvalidArgument, "moe_layer: x [T, H], gate [E, H], w_gu [E, 2I, H], w_d [E, H, I] expected");
+  const int tokens = t[0].shapes[0], hidden = t[0].shapes[1], experts = t[1].shapes[0], inter = t[5].shapes[2];
+  if (t[0].dtype != PTO_BF16 || t[1].dtype != PTO_BF16 || (int)t[1].shapes[1] != hidden || !is2d(t[11], tokens, hidden, PTO_BF16) ||
+      numel(t[2]) != experts || t[2].dtype != PTO_FP32 || (int)t[3].shapes[0] != experts || (int)t[3].shapes[1] != 2 * inter ||
+      (int)t[3].shapes[2] != hidden || (int)t[5].shapes[0] != experts || (int)t[5].shapes[1] != hidden ||
+      numel(t[7]) != static_cast<int64_t>(2) * inter * hidden || numel(t[9]) != static_cast<int64_t>(hidden) * inter)
+    return fail(kInvalidArgument, "moe_layer: tensor shapes or dtypes do not match");
+  pto_moe_layer_desc d = {};
+  d.hidden = hidden; d.inter = inter; d.n_experts = experts; d.topk = static_cast<int>(a->scalars[0]); d.max_tokens = tokens;
+  d.gate_packed = tptr(t[1], 2); d.bias = static_cast<const float*>(tptr(t[2], 4));
+  d.w_gu = tptr(t[3], 1); d.s_gu = static_cast<const float*>(tptr(t[4], 4));
+  d.w_d = tptr(t[5], 1); d.s_d = static_cast<const float*>(tptr(t[6], 4));
+  d.sh_w_gu = tptr(t[7], 1); d.sh_s_gu = static_cast<const float*>(tptr(t[8], 4));
+  d.sh_w_d = tptr(t[9], 1); d.sh_s_d = static_cast<const float*>(tptr(t[10], 4));
+  d.comm = nullptr;
+  pto_moe_layer_desc have = w->moe_desc;
+  have.max_tokens = d.max_tokens;   // a layer built for more tokens serves a smaller call
+  if (w->moe == nullptr || memcmp(&have, &d, sizeof d) != 0 || w->moe_desc.max_tokens < tokens) {
+    if (w->moe) {
+      PTO_CUDA(cudaStreamSynchronize(w->stream));
+      pto_moe_layer_destroy(w->moe);
+      w->moe = nullptr;
+    }
+    int st = pto_moe_layer_create(&d, &w->moe);
+    if (st != kOk) return st;
+    w->moe_desc = d;
+  }
+  int st = pto_moe_layer_forward(w->moe, tptr(t[0], 2), tokens, nullptr, nullptr, tptr(t[11], 2), nullptr, nullptr, nullptr,
+                                 w->stream);
+  if (st != kOk) return st;
+  // the layer's kernels report into its own error word: fold it into the worker's, which pto_device_status reads
+  int32_t words[4];
+  st = pto_moe_layer_status(w->moe, words, w->stream);
+  if (st != kOk) return st;
+  if (words[0] != 0) {
+    st = w->ensure_scratch(4096);
+    if (st != kOk) return st;
+    PTO_CUDA(cudaMemcpyAsync(w->scratch, words, sizeof words, cudaMemcpyHostToDevice, w->stream));
+    PTO_CUDA(cudaStreamSynchronize(w->stream));
+  }
+  return kOk;
+}
+
 }  // namespace pto

@@ -163,6 +163,7 @@ const OpEntry kOps[] = {
     {"scope3", op_scope3},
     {"decoder_layer", op_decoder_layer},
     {"matmul_mx", op_matmul_mx},
+    {"moe_layer", op_moe_layer},
 };
 
 }  // namespace

@@ -116,6 +116,7 @@ Worker::~Worker() {
     if (kv.second.library) cudaLibraryUnload(kv.second.library);
   }
   kernels.clear();
+  if (moe) pto_moe_layer_destroy(moe);
   if (scratch) cudaFree(scratch);
   if (stream) cudaStreamDestroy(stream);
 }

@@ -34,6 +34,10 @@ struct Worker {
   int32_t next_cid = 1;
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
+  // the mixture-of-experts layer object behind the "moe_layer" callable: built on first use, rebuilt when the
+  // weights or sizes of a call differ from the ones it was built for
+  pto_moe_layer* moe = nullptr;
+  pto_moe_layer_desc moe_desc = {};
   ~Worker();
   int ensure_scratch(size_t nbytes);
 };
@@ -46,5 +50,6 @@ int op_decoder_layer(Worker* w, const pto_task_args* a);
 int op_linear(Worker* w, const pto_task_args* a);
 int op_rope_kv_append(Worker* w, const pto_task_args* a);
 int op_matmul_mx(Worker* w, const pto_task_args* a);
+int op_moe_layer(Worker* w, const pto_task_args* a);
 
 }  // namespace pto

@@ -366,3 +366,40 @@ def test_moe_layer_object_regrows_times_its_phases_and_reports_bad_routes():
     assert layer.status()[0] == 0
     assert torch.equal(y_again.cpu(), y.cpu())
     layer.close()
+
+
+def test_moe_layer_callable_of_the_op_table_matches_the_layer_object():
+    """``moe_layer`` in the runtime's operator table (``pto_register_callable`` / ``pto_run``): tensors in the
+    kernels' packed layout, top-k as the scalar.  Same kernels as ``MoELayer.forward``, so the outputs are equal;
+    a second call with fewer tokens reuses the layer the first call built."""
+    from pypto_b200.moe import MoELayer
+    from pypto_b200.runtime import ChipWorker, DeviceTensor, RunConfig
+    tokens, hidden, inter, experts, topk = 80, 512, 256, 8, 2
+    m = oracle.inputs.moe_inputs(tokens=tokens, hidden=hidden, inter=inter, n_experts=experts, topk=topk, seed=33)
+    layer = MoELayer(m["gate_w"].cuda(), m["bias"].cuda(), {k: v.cuda() for k, v in m["routed"].items()},
+                     {k: v.cuda() for k, v in m["shared"].items()}, topk)
+    x = m["x"].cuda()
+    y_ref, _, _ = layer.forward(x)
+    y_exp, _, _ = omoe.moe_layer(m["x"], m["gate_w"], m["bias"], m["routed"], m["shared"], topk)
+
+    def dt(t):
+        return DeviceTensor(t.data_ptr(), tuple(t.shape), t.dtype, buffer=t)
+
+    worker = ChipWorker(RunConfig(platform="b200"))
+    worker.init()
+    try:
+        weights = [layer.gate_packed, layer.bias] + [layer.routed[k] for k in ("w_gu", "s_gu", "w_d", "s_d")] + \
+                  [layer.shared[k] for k in ("w_gu", "s_gu", "w_d", "s_d")]
+        for n in (tokens, 48):
+            y = torch.zeros(n, hidden, dtype=torch.bfloat16, device="cuda")
+            torch.cuda.synchronize()
+            worker.launch("moe_layer", [dt(x[:n].contiguous())] + [dt(w) for w in weights] + [dt(y)], [topk])
+            worker.synchronize()
+            assert worker.device_status()[0] == 0
+            assert torch.equal(y.cpu(), y_ref[:n].cpu())
+        rel = ((y_ref.cpu().float() - y_exp.float()).norm() / y_exp.float().norm()).item()
+        assert rel < 3e-2, rel     # own routing: a near-tie in the gate may pick another expert for a token
+        with pytest.raises(Exception):
+            worker.launch("moe_layer", [dt(x)] + [dt(w) for w in weights[:-1]] + [dt(y)], [topk])
+    finally:
+        worker.close()

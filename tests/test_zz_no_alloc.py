@@ -3,9 +3,9 @@
 Engines that pre-commit all device memory, plugins inside a foreign allocator and
 latency-critical loops cannot call cudaMalloc when they launch; this entry point keeps its
 scratch in a fixed array inside the library.  The test drives it through the C ABI with raw
-pointers and checks it against ``pto_paged_attention`` on two consecutive calls with
-different inputs (the shared array keeps the first call's contents, so the second call
-shows whether stale partial rows or a stale plan leak through).  Collected last so that a
+pointers and checks it against the oracle and against ``pto_paged_attention`` on two consecutive
+calls with different inputs (the shared array keeps the first call's contents, so the second
+call shows whether stale partial rows or a stale plan leak through).  Collected last so that a
 failure here cannot hide the other tests in a stop-at-first-failure run.
 """
 
@@ -45,11 +45,15 @@ def test_static_scratch_entry_matches_allocating_entry_twice_in_a_row():
     first = oracle.inputs.paged_attention_inputs(batch=24, num_heads=32, kv_heads=8, ctx_lo=1, ctx_hi=3000, seed=31)
     second = oracle.inputs.paged_attention_inputs(batch=7, num_heads=16, kv_heads=2, ctx_lo=200, ctx_hi=5000,
                                                   q_len=2, seed=32)
+    from oracle import paged_attention as opa
     for d in (first, second):
         got, ref = _call_both(d)
         assert torch.isfinite(got).all()
-        assert torch.allclose(got, ref, rtol=RTOL, atol=ATOL), (got - ref).abs().max()
-        assert torch.equal(got, ref)   # same kernels, same order of operations
+        exp = opa.paged_attention(d["query"], d["key_cache"], d["value_cache"], d["block_table"], d["context_lens"],
+                                  num_heads=d["num_heads"], head_dim=d["head_dim"], block_size=d["block_size"],
+                                  scale=d["scale"], kv_heads=d["kv_heads"], q_len=d.get("q_len", 1)).float()
+        assert torch.allclose(got, exp.reshape(got.shape), rtol=RTOL, atol=ATOL), (got - exp.reshape(got.shape)).abs().max()
+        assert torch.equal(got, ref)   # same kernels, same order of operations as the allocating entry
 
 
 def test_static_scratch_rejects_geometry_beyond_its_capacity():
