@@ -874,6 +874,10 @@ def main():
                     help="reduced case of the workload for profiler captures (a few GB on the device at most): "
                          "verify batch 16, moe 16 experts / 256 tokens, matmul_mx 1024^3; other workloads unchanged")
     args = ap.parse_args()
+    # stdout carries the JSON line and nothing else: NCCL's "NCCL version ..." banner (NCCL_DEBUG=VERSION) would sit
+    # in front of it.  An explicit higher level (INFO, TRACE) is left alone.
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+        os.environ["NCCL_DEBUG"] = "WARN"
     if args.impl == "reference":
         run_reference(args)
         return
