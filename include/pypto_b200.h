@@ -253,6 +253,15 @@ PTO_API int pto_rope_kv_append(const float* qkv, const int32_t* seq_lens, const 
 /* act[r, c] = bf16(silu(gate_up[r, c]) * gate_up[r, inter + c]), gate_up fp32 [rows, 2*inter]. */
 PTO_API int pto_swiglu_act(const float* gate_up, void* act, int64_t rows, int inter, void* stream);
 
+/* The minimal LLaMA forward pass of examples/models/08_llama_mini.py:384-483 (orchestration `llama_mini_orch`;
+ * golden tests/st/examples/03_llm_models/test_llama_7b_mini_1h.py:118-199), all tensors fp32 row-major:
+ * hidden [S, D], causal_mask [S, S] (added to the scaled scores), cos_emb / sin_emb [S, D/2], wq wk wv w_dense
+ * w_gate w_up w_down [D, D], w_lm [D, V], logits [S, V].  5*S*D + S*S floats must fit in 200 KB. */
+PTO_API int pto_llama_mini(const float* hidden, const float* causal_mask, const float* cos_emb, const float* sin_emb,
+                           const float* wq, const float* wk, const float* wv, const float* w_dense,
+                           const float* w_gate, const float* w_up, const float* w_down, const float* w_lm,
+                           float* logits, int seq_len, int head_dim, int vocab, void* stream);
+
 /* ---- mixture of experts ---- */
 
 /* Top-k routing.  `scores` fp32 [tokens, experts] holds gate logits (is_logits = 1: sigmoid is

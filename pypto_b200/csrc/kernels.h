@@ -62,6 +62,10 @@ int rope_kv_append_launch(const float* qkv, const int32_t* seq_lens, const float
 int contiguous_cache_tables_launch(const int32_t* seq_lens, int batch, int kv_heads, int blocks_per_seq,
                                    int32_t* seq_table, int32_t* head_table, int32_t* head_lens, cudaStream_t stream);
 int swiglu_act_launch(const float* gate_up, void* act, long long rows, int inter, cudaStream_t stream);
+int llama_mini_launch(const float* hidden, const float* mask, const float* cos_emb, const float* sin_emb, const float* wq,
+                      const float* wk, const float* wv, const float* w_dense, const float* w_gate, const float* w_up,
+                      const float* w_down, const float* w_lm, float* logits, int seq_len, int head_dim, int vocab,
+                      cudaStream_t stream);
 int cast_launch(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream);
 int cast_zero_launch(const void* in, int in_dtype, void* out, int out_dtype, long long n, void* zero,
                      size_t zero_bytes, cudaStream_t stream);

@@ -320,4 +320,21 @@ int op_moe_layer(Worker* w, const pto_task_args* a) {
   return kOk;
 }
 
+// tensors (all fp32): hidden [S, D], causal_mask [S, S], cos_emb, sin_emb [S, D/2], wq, wk, wv, w_dense, w_gate, w_up,
+// w_down [D, D], w_lm [D, V], logits [S, V] -- the signature of llama_mini_orch (examples/models/08_llama_mini.py:385-408)
+int op_llama_mini(Worker* w, const pto_task_args* a) {
+  if (a->n_tensors != 13 || a->n_scalars != 0) return fail(kInvalidArgument, "llama_mini: expects 13 tensors and no scalars");
+  const pto_chip_tensor* t = a->tensors;
+  if (t[0].ndims != 2 || t[11].ndims != 2) return fail(kInvalidArgument, "llama_mini: hidden [S, D] and w_lm [D, V] expected");
+  const int s = t[0].shapes[0], d = t[0].shapes[1], v = t[11].shapes[1];
+  bool ok = is2d(t[0], s, d, PTO_FP32) && is2d(t[1], s, s, PTO_FP32) && is2d(t[2], s, d / 2, PTO_FP32) &&
+            is2d(t[3], s, d / 2, PTO_FP32) && is2d(t[11], d, v, PTO_FP32) && is2d(t[12], s, v, PTO_FP32);
+  for (int i = 4; i <= 10; ++i) ok = ok && is2d(t[i], d, d, PTO_FP32);
+  if (!ok) return fail(kInvalidArgument, "llama_mini: tensor shapes or dtypes do not match the program's signature");
+  const float* f[12];
+  for (int i = 0; i < 12; ++i) f[i] = static_cast<const float*>(tptr(t[i], 4));
+  return llama_mini_launch(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7], f[8], f[9], f[10], f[11],
+                           static_cast<float*>(tptr(t[12], 4)), s, d, v, w->stream);
+}
+
 }  // namespace pto

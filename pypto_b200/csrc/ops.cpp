@@ -164,6 +164,7 @@ const OpEntry kOps[] = {
     {"decoder_layer", op_decoder_layer},
     {"matmul_mx", op_matmul_mx},
     {"moe_layer", op_moe_layer},
+    {"llama_mini", op_llama_mini},
 };
 
 }  // namespace
@@ -281,6 +282,14 @@ int pto_rope_kv_append(const float* qkv, const int32_t* seq_lens, const float* c
   return pto::rope_kv_append_launch(qkv, seq_lens, cos_table, sin_table, table_rows, block_table, max_blocks,
                                     k_cache, v_cache, q_out, batch, num_heads, kv_heads, head_dim, block_size,
                                     pool_blocks, err, static_cast<cudaStream_t>(stream));
+}
+
+int pto_llama_mini(const float* hidden, const float* causal_mask, const float* cos_emb, const float* sin_emb,
+                   const float* wq, const float* wk, const float* wv, const float* w_dense, const float* w_gate,
+                   const float* w_up, const float* w_down, const float* w_lm, float* logits, int seq_len, int head_dim,
+                   int vocab, void* stream) {
+  return pto::llama_mini_launch(hidden, causal_mask, cos_emb, sin_emb, wq, wk, wv, w_dense, w_gate, w_up, w_down, w_lm,
+                                logits, seq_len, head_dim, vocab, static_cast<cudaStream_t>(stream));
 }
 
 int pto_swiglu_act(const float* gate_up, void* act, int64_t rows, int inter, void* stream) {

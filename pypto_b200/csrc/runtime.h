@@ -51,5 +51,6 @@ int op_linear(Worker* w, const pto_task_args* a);
 int op_rope_kv_append(Worker* w, const pto_task_args* a);
 int op_matmul_mx(Worker* w, const pto_task_args* a);
 int op_moe_layer(Worker* w, const pto_task_args* a);
+int op_llama_mini(Worker* w, const pto_task_args* a);
 
 }  // namespace pto

@@ -316,6 +316,23 @@ def rope_kv_append(qkv, seq_lens, cos, sin, block_table, k_cache, v_cache, *, nu
     return q_out
 
 
+def llama_mini(hidden, causal_mask, cos_emb, sin_emb, wq, wk, wv, w_dense, w_gate, w_up, w_down, w_lm) -> torch.Tensor:
+    """The reference's minimal LLaMA forward pass (examples/models/08_llama_mini.py:384-483), fp32 -> logits [S, V]."""
+    ts = (hidden, causal_mask, cos_emb, sin_emb, wq, wk, wv, w_dense, w_gate, w_up, w_down, w_lm)
+    dev = _need_cuda(*ts)
+    if any(t.dtype != torch.float32 or not t.is_contiguous() or t.dim() != 2 for t in ts):
+        raise TypeError("llama_mini: all tensors must be contiguous 2-D float32")
+    s, d = hidden.shape
+    v = w_lm.shape[1]
+    want = [(s, d), (s, s), (s, d // 2), (s, d // 2)] + [(d, d)] * 7 + [(d, v)]
+    if [tuple(t.shape) for t in ts] != want:
+        raise ValueError(f"llama_mini: shapes {[tuple(t.shape) for t in ts]} do not match {want}")
+    out = torch.empty(s, v, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_llama_mini(*[t.data_ptr() for t in ts], out.data_ptr(), s, d, v, _stream_ptr(dev)))
+    return out
+
+
 def swiglu_act(gate_up: torch.Tensor) -> torch.Tensor:
     dev = _need_cuda(gate_up)
     rows, two_i = gate_up.shape

@@ -260,7 +260,31 @@ class MatmulMxOp(FusedOp):
         worker.launch("matmul_mx", [dev[n] for n in self.names], plan["scalars"])
 
 
-REGISTRY: list[FusedOp] = [PagedAttentionOp(), PagedAttentionSpmdOp(), PagedGatherOp(), FfnSwigluOp(), RmsNormOp(),
+class LlamaMiniOp(FusedOp):
+    """``llama_mini_orch(hidden, causal_mask, cos_emb, sin_emb, wq, wk, wv, w_dense, w_gate, w_up, w_down, w_lm,
+    logits)`` (examples/models/08_llama_mini.py:384-483), all fp32: one kernel for the whole forward pass."""
+
+    op_names = ("llama_mini",)
+    names = ("hidden", "causal_mask", "cos_emb", "sin_emb", "wq", "wk", "wv", "w_dense", "w_gate", "w_up", "w_down",
+             "w_lm", "logits")
+
+    def matches(self, entry) -> bool:
+        return entry.name == "llama_mini_orch" and tuple(p.name for p in entry.params) == self.names
+
+    def plan(self, compiled, host, worker):
+        if any(host[n].dtype != torch.float32 for n in self.names):
+            raise TypeError("llama_mini_orch: every tensor must be float32")
+        s, d = host["hidden"].shape
+        if d % 2 or 4 * (5 * s * d + s * s) > 200 * 1024:
+            raise ValueError("llama_mini_orch: head_dim must be even and 5*S*D + S*S floats must fit in 200 KB of "
+                             "shared memory")
+        return {}
+
+    def launch(self, worker, dev, host, plan):
+        worker.launch("llama_mini", [dev[n] for n in self.names], [])
+
+
+REGISTRY: list[FusedOp] = [LlamaMiniOp(), PagedAttentionOp(), PagedAttentionSpmdOp(), PagedGatherOp(), FfnSwigluOp(), RmsNormOp(),
                            Qwen3DecodeOp(), Scope3Op(), MatmulMxOp()]
 
 

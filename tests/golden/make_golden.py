@@ -54,6 +54,22 @@ def rope_case():
     return dict(cos_emb=cos, sin_emb=sin, x=x, rotated=rot["apply_rope"](x), head_dim=64, theta=10000.0)
 
 
+def llama_mini_case():
+    """The reference's minimal LLaMA case (test_llama_7b_mini_1h.py:69-199): its own tensor initialisers (nested in
+    define_tensors) and its own ``compute_expected``, run unmodified; S = 16, D = 64, V = 64."""
+    init = ref_extract.extract(LLAMA, ["make_small_weight", "make_causal_mask", "make_cos_emb", "make_sin_emb"],
+                               overrides={"head_dim": 64}, nested=True)
+    torch.manual_seed(29)
+    t = dict(hidden=torch.randn(16, 64), causal_mask=init["make_causal_mask"](), cos_emb=init["make_cos_emb"](),
+             sin_emb=init["make_sin_emb"]())
+    for name in ("wq", "wk", "wv", "w_dense", "w_gate", "w_up", "w_down", "w_lm"):
+        t[name] = init["make_small_weight"]()
+    t["output"] = torch.zeros(16, 64)
+    ns = ref_extract.extract(LLAMA, ["compute_expected"], nested=True)
+    ns["compute_expected"](None, t)
+    return t
+
+
 def matmul_mx_case():
     """The reference's MXFP8 x MXFP8 case (test_matmul_mx.py:146-168): integer-valued e4m3 data in
     [-2, 2], E8M0 scale codes 126..129, scales in the packed MX_A_ZZ / MX_B_NN layouts it hands to the
@@ -136,6 +152,7 @@ def main():
 
     fx["rope"] = rope_case()
     fx["matmul_mx"] = matmul_mx_case()
+    fx["llama_mini"] = llama_mini_case()
 
     for name, data in fx.items():
         torch.save(data, os.path.join(HERE, name + ".pt"))

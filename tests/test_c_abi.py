@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
 def test_op_list_and_version():
     from pypto_b200 import _lib
     assert {"paged_attention", "paged_gather", "rms_norm", "ffn_swiglu", "linear", "rope_kv_append", "scope3",
-            "decoder_layer", "matmul_mx", "moe_layer"} <= set(_lib.op_names())
+            "decoder_layer", "matmul_mx", "moe_layer", "llama_mini"} <= set(_lib.op_names())
     assert b"sm_100a" in _lib.load().pto_version()
 
 

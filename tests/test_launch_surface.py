@@ -178,3 +178,21 @@ def test_reference_qwen3_decode_example_imports_and_compiles_unchanged():
         sys.path.remove(ref_extract.REFERENCE_ROOT)
     compiled = ir.compile(mod.qwen3_decode, platform="b200")
     assert compiled.op_names == ("decoder_layer",) and len(compiled.params) == 16
+
+
+def test_reference_llama_mini_example_imports_and_compiles_unchanged():
+    """examples/models/08_llama_mini.py through the ``pypto`` alias: the program built by its own
+    ``build_llama_mini_program`` resolves to the one-kernel forward pass."""
+    import importlib.util
+
+    import ref_extract
+    if not ref_extract.available():
+        pytest.skip("reference tree not mounted")
+    from pypto_b200 import compat
+    compat.install()
+    path = os.path.join(ref_extract.REFERENCE_ROOT, "examples/models/08_llama_mini.py")
+    spec = importlib.util.spec_from_file_location("ref_example_08", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    c = ir.compile(mod.build_llama_mini_program(seq_len=16, head_dim=64, vocab_size=64), platform="b200")
+    assert c.entry.name == "llama_mini_orch" and len(c.params) == 13 and c.op_names == ("llama_mini",)

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import oracle
-from oracle import ep, ffn, gather, layer, matmul_mx, moe
+from oracle import ep, ffn, gather, layer, llama_mini, matmul_mx, moe
 from oracle import paged_attention as pa
 
 PA_CASES = ["pa04_aligned", "pa04_unaligned", "pa04_ragged", "pa04_h64_b64", "pa04_tiny"]
@@ -185,3 +185,15 @@ def test_quantize_mx_round_trips_within_e4m3_precision():
     q, codes = matmul_mx.quantize_mx(x, dim=1)
     deq = q.float() * matmul_mx.decode_scale(codes).float().repeat_interleave(32, dim=1)
     assert codes.shape == (64, 8) and (deq - x).abs().max() <= x.abs().max() * 2 ** -3
+
+
+def test_llama_mini_fixture(golden):
+    """The minimal LLaMA forward pass against the output of the reference's own ``compute_expected``
+    (test_llama_7b_mini_1h.py:118-199) on tensors made by its own initialisers."""
+    t = golden("llama_mini")
+    got = llama_mini.forward(t)
+    assert got.shape == t["output"].shape
+    assert torch.allclose(got, t["output"], rtol=1e-6, atol=1e-7)
+    own = llama_mini.make_inputs(seed=3)
+    assert llama_mini.forward(own).shape == (16, 64)
+    assert torch.equal(own["cos_emb"], t["cos_emb"]) and torch.equal(own["causal_mask"], t["causal_mask"])

@@ -122,3 +122,37 @@ def test_block_id_outside_the_pool_raises_through_the_launch_surface():
     with pytest.raises(PtoError, match="block id"):
         compiled(*args)
     compiled(*[a if i != 3 else d["block_table"].flatten() for i, a in enumerate(args)])      # and the word was cleared
+
+
+def test_llama_mini_program_matches_reference_fixture(golden):
+    """``llama_mini_orch`` (examples/models/08_llama_mini.py:385-408) through ``run``: logits against the output of the
+    reference's own golden, and a second size against the oracle."""
+    from oracle import llama_mini as olm
+    from pypto_b200.runtime import RunConfig, run
+
+    def program(S, D, V):
+        H = D // 2
+
+        @pl.program
+        class LlamaMiniProgram:
+            @pl.function(type=pl.FunctionType.Orchestration)
+            def llama_mini_orch(self, hidden: pl.Tensor[[S, D], pl.FP32], causal_mask: pl.Tensor[[S, S], pl.FP32],
+                                cos_emb: pl.Tensor[[S, H], pl.FP32], sin_emb: pl.Tensor[[S, H], pl.FP32],
+                                wq: pl.Tensor[[D, D], pl.FP32], wk: pl.Tensor[[D, D], pl.FP32],
+                                wv: pl.Tensor[[D, D], pl.FP32], w_dense: pl.Tensor[[D, D], pl.FP32],
+                                w_gate: pl.Tensor[[D, D], pl.FP32], w_up: pl.Tensor[[D, D], pl.FP32],
+                                w_down: pl.Tensor[[D, D], pl.FP32], w_lm: pl.Tensor[[D, V], pl.FP32],
+                                logits: pl.Out[pl.Tensor[[S, V], pl.FP32]]) -> pl.Tensor[[S, V], pl.FP32]:
+                ...
+        return LlamaMiniProgram
+
+    names = ("hidden", "causal_mask", "cos_emb", "sin_emb", "wq", "wk", "wv", "w_dense", "w_gate", "w_up", "w_down", "w_lm")
+    t = golden("llama_mini")
+    out = torch.zeros(16, 64)
+    run(program(16, 64, 64), *[t[n] for n in names], out, config=RunConfig(platform="b200"))
+    assert torch.allclose(out, t["output"], rtol=1e-4, atol=1e-5), (out - t["output"]).abs().max()
+    big = olm.make_inputs(seq_len=48, head_dim=128, vocab=320, seed=5)
+    out2 = torch.zeros(48, 320)
+    run(program(48, 128, 320), *[big[n] for n in names], out2, config=RunConfig(platform="b200"))
+    exp2 = olm.forward(big)
+    assert torch.allclose(out2, exp2, rtol=1e-4, atol=1e-5), (out2 - exp2).abs().max()
