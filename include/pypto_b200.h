@@ -253,6 +253,16 @@ PTO_API int pto_rope_kv_append(const float* qkv, const int32_t* seq_lens, const 
 /* act[r, c] = bf16(silu(gate_up[r, c]) * gate_up[r, inter + c]), gate_up fp32 [rows, 2*inter]. */
 PTO_API int pto_swiglu_act(const float* gate_up, void* act, int64_t rows, int inter, void* stream);
 
+/* ---- tracing (the reference's run-time diagnostics: RunConfig.enable_chip_swimlane and friends,
+ * python/pypto/runtime/runner.py:344-348, docs/en/dev/03-runtime-dfx.md:10-18) ----
+ * level 0: off (default; the environment variable PTO_TRACE sets the initial level);
+ * level 1: an NVTX range around every registered callable (named after the operator) and around every phase of the
+ *          MoE layer's forward call, for timeline tools;
+ * level 2: also CUDA events around every pto_run; pto_last_run_ms waits for the last one and returns its device time. */
+PTO_API int pto_set_trace(int level);
+PTO_API int pto_get_trace(void);
+PTO_API int pto_last_run_ms(pto_worker* worker, float* ms);
+
 /* The minimal LLaMA forward pass of examples/models/08_llama_mini.py:384-483 (orchestration `llama_mini_orch`;
  * golden tests/st/examples/03_llm_models/test_llama_7b_mini_1h.py:118-199), all tensors fp32 row-major:
  * hidden [S, D], causal_mask [S, S] (added to the scaled scores), cos_emb / sin_emb [S, D/2], wq wk wv w_dense

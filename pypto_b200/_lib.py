@@ -76,6 +76,9 @@ SIGNATURES = {
     "pto_rope_kv_append": (_i, [_p, _p, _p, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i64, _p, _p]),
     "pto_swiglu_act": (_i, [_p, _p, _i64, _i, _p]),
     "pto_llama_mini": (_i, [_p] * 13 + [_i, _i, _i, _p]),
+    "pto_set_trace": (_i, [_i]),
+    "pto_get_trace": (_i, []),
+    "pto_last_run_ms": (_i, [_p, C.POINTER(C.c_float)]),
     "pto_moe_topk": (_i, [_p, _p, _i, _i, _i, _i, _p, _p, _p]),
     "pto_quantize_rows": (_i, [_p, _i, _p, _p, _i64, _i, _p]),
     "pto_moe_dispatch_plan": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p, _p]),

@@ -14,12 +14,15 @@
 // The host waits once per step, for the row counts of the exchange (a pinned buffer and an event); everything
 // before that wait is already queued, so the GPU packs the payload and runs the shared expert meanwhile.
 // All buffers are allocated when the layer is created, sized for `max_tokens` and the worst-case arrival count.
+#include <nvtx3/nvToolsExt.h>
+
 #include <cstring>
 #include <vector>
 
 #include "common.cuh"
 #include "kernels.h"
 #include "pypto_b200.h"
+#include "runtime.h"
 
 extern "C" int pto_comm_rank(const pto_comm* c);
 extern "C" int pto_comm_size(const pto_comm* c);
@@ -176,10 +179,23 @@ int pto_moe_layer_forward(pto_moe_layer* L, const void* x, int tokens, const int
   const int T = tokens, K = d.topk, H = d.hidden, E = d.n_experts, W = L->world, Le = L->local_experts;
   const long long routes = static_cast<long long>(T) * K;
   int ph = 0;
+  // trace level 1: one NVTX range per phase (host-side issue ranges; the kernels inside carry their own names)
+  static const char* const kPhaseNames[] = {"moe.route_quantize", "moe.plan", "moe.pack", "moe.exchange_out", "moe.unpack",
+                                            "moe.experts", "moe.exchange_back", "moe.combine"};
+  const bool nvtx = trace_level() >= 1;
+  int nv = 0;
+  bool nv_open = false;
   auto mark = [&]() -> int {
+    if (nvtx) {
+      if (nv_open) nvtxRangePop();
+      nv_open = nv < 8;
+      if (nv_open) nvtxRangePushA(kPhaseNames[nv++]);
+    }
     if (!phase_ms) return kOk;
     return check_cuda(cudaEventRecord(L->ev_phase[ph++], s), "cudaEventRecord");
   };
+  struct PopAtExit { bool* open; ~PopAtExit() { if (*open) nvtxRangePop(); } } pop_at_exit{&nv_open};
+  TraceRange whole("moe_layer.forward");
   int st = mark();
   if (st != kOk) return st;
   // ---- route + quantise ----

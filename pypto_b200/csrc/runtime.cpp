@@ -2,6 +2,9 @@
 // scratch arena), registered callables, error plumbing, tensor-map encoding.
 // It stands where the reference loads its external device runtime
 // (python/pypto/runtime/device_runner.py:821-842).
+#include <nvtx3/nvToolsExt.h>
+
+#include <atomic>
 #include "runtime.h"
 
 #include <cstdio>
@@ -37,6 +40,28 @@ bool pdl_enabled() {
     return v == nullptr || v[0] != '0';
   }();
   return on;
+}
+
+namespace {
+std::atomic<int> g_trace_level{-1};
+}
+
+int trace_level() {
+  int v = g_trace_level.load(std::memory_order_relaxed);
+  if (v < 0) {   // first use: the environment decides until pto_set_trace is called
+    const char* e = getenv("PTO_TRACE");
+    v = e ? atoi(e) : 0;
+    if (v < 0) v = 0;
+    g_trace_level.store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
+TraceRange::TraceRange(const char* name) : on(trace_level() >= 1) {
+  if (on) nvtxRangePushA(name);
+}
+TraceRange::~TraceRange() {
+  if (on) nvtxRangePop();
 }
 
 bool first_use_on_device(int key) {
@@ -116,6 +141,7 @@ Worker::~Worker() {
     if (kv.second.library) cudaLibraryUnload(kv.second.library);
   }
   kernels.clear();
+  for (cudaEvent_t e : trace_ev) if (e) cudaEventDestroy(e);
   if (moe) pto_moe_layer_destroy(moe);
   if (scratch) cudaFree(scratch);
   if (stream) cudaStreamDestroy(stream);
@@ -292,6 +318,7 @@ int pto_register_callable(pto_worker* h, const char* op_name, int32_t* cid) {
   std::lock_guard<std::mutex> g(w->mu);
   int32_t id = w->next_cid++;
   w->callables[id] = fn;
+  w->callable_names[id] = op_name;
   *cid = id;
   return pto::kOk;
 }
@@ -380,13 +407,46 @@ int pto_run(pto_worker* h, int32_t cid, const pto_task_args* args) {
   PTO_WORKER(h);
   if (args == nullptr) return pto::fail(pto::kInvalidArgument, "run: args is NULL");
   pto::OpFn fn = nullptr;
+  const char* name = "callable";
   {
     std::lock_guard<std::mutex> g(w->mu);
     auto it = w->callables.find(cid);
     if (it == w->callables.end()) return pto::fail(pto::kNotFound, "run: unknown callable id");
     fn = it->second;
+    auto nm = w->callable_names.find(cid);
+    if (nm != w->callable_names.end()) name = nm->second.c_str();   // map nodes are stable while the id is registered
   }
-  return fn(w, args);
+  const int level = pto::trace_level();
+  if (level < 1) return fn(w, args);
+  pto::TraceRange range(name);
+  if (level >= 2) {
+    for (cudaEvent_t& e : w->trace_ev)
+      if (e == nullptr) PTO_CUDA(cudaEventCreate(&e));
+    PTO_CUDA(cudaEventRecord(w->trace_ev[0], w->stream));
+  }
+  const int st = fn(w, args);
+  if (level >= 2 && st == pto::kOk) {
+    PTO_CUDA(cudaEventRecord(w->trace_ev[1], w->stream));
+    w->trace_valid = true;
+  }
+  return st;
+}
+
+int pto_set_trace(int level) {
+  if (level < 0 || level > 2) return pto::fail(pto::kInvalidArgument, "set_trace: level must be 0, 1 or 2");
+  pto::g_trace_level.store(level, std::memory_order_relaxed);
+  return pto::kOk;
+}
+
+int pto_get_trace(void) { return pto::trace_level(); }
+
+int pto_last_run_ms(pto_worker* h, float* ms) {
+  PTO_WORKER(h);
+  if (ms == nullptr) return pto::fail(pto::kInvalidArgument, "last_run_ms: ms is NULL");
+  if (!w->trace_valid) return pto::fail(pto::kNotFound, "last_run_ms: no callable has run with trace level 2 on this worker");
+  PTO_CUDA(cudaEventSynchronize(w->trace_ev[1]));
+  PTO_CUDA(cudaEventElapsedTime(ms, w->trace_ev[0], w->trace_ev[1]));
+  return pto::kOk;
 }
 
 }  // extern "C"

@@ -30,6 +30,9 @@ struct Worker {
   std::mutex mu;
   std::map<uint64_t, size_t> allocs;  // device pointers handed out by pto_malloc
   std::map<int32_t, OpFn> callables;
+  std::map<int32_t, std::string> callable_names;   // for trace ranges
+  cudaEvent_t trace_ev[2] = {nullptr, nullptr};    // device time of the last traced pto_run
+  bool trace_valid = false;
   std::map<int32_t, ExternKernel> kernels;   // share the id space of `callables`
   int32_t next_cid = 1;
   void* scratch = nullptr;
@@ -43,6 +46,15 @@ struct Worker {
 };
 
 OpFn find_op(const char* name);
+
+// Tracing (pto_set_trace): 0 off; 1 = an NVTX range around every registered callable and every phase of the MoE layer;
+// 2 = also CUDA events around every callable, read back with pto_last_run_ms.
+int trace_level();
+struct TraceRange {   // NVTX push / pop when tracing is on
+  explicit TraceRange(const char* name);
+  ~TraceRange();
+  bool on;
+};
 
 // layer_ops.cpp: callables composed of several kernels
 int op_scope3(Worker* w, const pto_task_args* a);

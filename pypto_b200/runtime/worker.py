@@ -6,6 +6,8 @@ from __future__ import annotations
 import contextvars
 import ctypes as C
 import hashlib
+import logging
+import os
 import weakref
 
 import torch
@@ -15,6 +17,15 @@ from .device_tensor import DeviceTensor
 from .run_config import RunConfig
 
 _ACTIVE: contextvars.ContextVar = contextvars.ContextVar("pypto_b200_active_worker", default=None)
+
+# The runtime logger (the reference's PYPTO_RUNTIME_LOG, docs/en/dev/03-logging.md:9-17): one ``logging`` logger for
+# the package; the environment variable sets its level when the application has not configured it.
+log = logging.getLogger("pypto_b200")
+_level = os.environ.get("PYPTO_RUNTIME_LOG", "").strip().upper()
+if _level in ("DEBUG", "INFO", "WARNING", "WARN", "ERROR"):
+    log.setLevel(getattr(logging, "WARNING" if _level == "WARN" else _level))
+    if not log.handlers and not logging.getLogger().handlers:
+        logging.basicConfig(format="%(asctime)s %(name)s %(levelname)s %(message)s")
 
 
 class ChipWorker:
@@ -57,6 +68,12 @@ class ChipWorker:
         h = C.c_void_p()
         _lib.check(lib.pto_worker_create(self._config.device_id, C.byref(h)))
         self._handle, self._initialized = h, True
+        # diagnostics flags of the run configuration (runner.py:344-348): a swimlane level asks for timeline ranges
+        # (NVTX, trace level 1), the PMU flag for per-callable device times (CUDA events, trace level 2)
+        want = 2 if self._config.enable_pmu else (1 if self._config.enable_chip_swimlane else 0)
+        if want > lib.pto_get_trace():
+            _lib.check(lib.pto_set_trace(want))
+        log.info("worker on device %d ready (trace level %d)", self._config.device_id, lib.pto_get_trace())
 
     def close(self) -> None:
         if not self._initialized:
@@ -224,7 +241,17 @@ class ChipWorker:
         python/pypto/backend/pto_backend.py:541-629)."""
         self._require_ready("launch")
         args, _keep = self._task_args(tensors, scalars)
+        if log.isEnabledFor(logging.DEBUG):
+            log.debug("launch %s tensors=%s scalars=%s", op_name, [tuple(t.shape) for t in tensors], list(scalars))
         _lib.check(_lib.load().pto_run(self._handle, self._cid(op_name), C.byref(args)))
+
+    def last_run_ms(self) -> float:
+        """Device time of the last callable this worker ran, measured with CUDA events by the runtime; needs trace
+        level 2 (``RunConfig(enable_pmu=1)``, ``pto_set_trace(2)`` or ``PTO_TRACE=2``).  Waits for that callable."""
+        self._require_ready("last_run_ms")
+        ms = C.c_float()
+        _lib.check(_lib.load().pto_last_run_ms(self._handle, C.byref(ms)))
+        return ms.value
 
     # ---- external kernels (the reference's external_source / jit.extern hook) ----
     def register_kernel_image(self, image: bytes, entry: str = "kernel_entry") -> int:

@@ -196,3 +196,21 @@ def test_reference_llama_mini_example_imports_and_compiles_unchanged():
     spec.loader.exec_module(mod)
     c = ir.compile(mod.build_llama_mini_program(seq_len=16, head_dim=64, vocab_size=64), platform="b200")
     assert c.entry.name == "llama_mini_orch" and len(c.params) == 13 and c.op_names == ("llama_mini",)
+
+
+def test_trace_level_entry_points_and_logger():
+    """Tracing is a process-wide level in the runtime (0 off, 1 NVTX ranges, 2 + CUDA events per callable); the package
+    logs through one ``logging`` logger."""
+    import logging
+
+    from pypto_b200 import _lib
+    from pypto_b200.runtime import worker as worker_mod
+    lib = _lib.load()
+    before = lib.pto_get_trace()
+    try:
+        assert lib.pto_set_trace(2) == 0 and lib.pto_get_trace() == 2
+        assert lib.pto_set_trace(7) != 0 and b"level" in lib.pto_last_error()
+        assert lib.pto_get_trace() == 2
+    finally:
+        lib.pto_set_trace(before)
+    assert worker_mod.log is logging.getLogger("pypto_b200")

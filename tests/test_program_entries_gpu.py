@@ -3,6 +3,7 @@ decode layer (``qwen3_decode``), its third scope against the reference-generated
 program with the reference's physical scale layouts, and the error word surfacing as an exception."""
 
 import math
+import struct
 
 import pytest
 import torch
@@ -156,3 +157,27 @@ def test_llama_mini_program_matches_reference_fixture(golden):
     run(program(48, 128, 320), *[big[n] for n in names], out2, config=RunConfig(platform="b200"))
     exp2 = olm.forward(big)
     assert torch.allclose(out2, exp2, rtol=1e-4, atol=1e-5), (out2 - exp2).abs().max()
+
+
+def test_traced_callable_reports_its_device_time():
+    """Trace level 2 (``RunConfig(enable_pmu=1)``): the runtime brackets every callable with CUDA events and NVTX ranges;
+    the result is unchanged and ``last_run_ms`` returns a plausible device time."""
+    from pypto_b200 import _lib
+    from pypto_b200.runtime import ChipWorker, DeviceTensor, RunConfig
+    lib = _lib.load()
+    before = lib.pto_get_trace()
+    x = torch.randn(64, 4096, device="cuda").bfloat16()
+    gamma = torch.rand(4096, device="cuda") + 0.5
+    out = torch.zeros_like(x)
+    try:
+        with ChipWorker(RunConfig(platform="b200", enable_pmu=1)) as wk:
+            assert lib.pto_get_trace() == 2
+            dt = [DeviceTensor(t.data_ptr(), tuple(t.shape), t.dtype, buffer=t) for t in (x, gamma, out)]
+            torch.cuda.synchronize()
+            wk.launch("rms_norm", dt, [struct.unpack("I", struct.pack("f", 1e-5))[0]])
+            ms = wk.last_run_ms()
+            assert 0.0 < ms < 50.0
+        exp = (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5) * gamma).bfloat16()
+        assert torch.allclose(out.float(), exp.float(), rtol=2e-2, atol=2e-2)
+    finally:
+        lib.pto_set_trace(before)
