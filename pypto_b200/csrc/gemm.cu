@@ -136,22 +136,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                              : static_cast<int>(blockIdx.x);
   const int it_hi = stream_k ? min(p.iters_total, it_lo + p.iters_per_cta) : p.a_tiles * p.b_tiles;
 
+  // The producer and the issuer are one-thread jobs whose instruction streams bound the K loop of small problems:
+  // the whole warp walks the loop and waits (warp-uniform code keeps descriptors and barrier addresses in uniform
+  // registers), one elected lane issues, stages and barrier phases are carried along instead of divided out, and the
+  // operand descriptors advance by additions.
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      int cur = it_lo;
-      Seg sg;
-      while (ok && next_seg(cur, it_hi, p.kblocks_total, stride, sg)) {
-        const int at = sg.tile / p.b_tiles, bt = sg.tile - at * p.b_tiles;
-        for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
-          const uint32_t s = it % p.stages, round = it / p.stages;
-          if (!mbar_wait(&empty[s], (round & 1u) ^ 1u)) {
-            report_error(p.err, kErrBarrierTimeout, 40, static_cast<int>(it));
-            ok = false;
-            break;
-          }
+    uint32_t it = 0, s = 0, ph = 0;   // K blocks issued, stage of the next one, how often that stage was refilled (mod 2)
+    bool ok = true;
+    int cur = it_lo;
+    Seg sg;
+    while (ok && next_seg(cur, it_hi, p.kblocks_total, stride, sg)) {
+      const int at = sg.tile / p.b_tiles, bt = sg.tile - at * p.b_tiles;
+      for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u))) {
+          if (lane == 0) report_error(p.err, kErrBarrierTimeout, 40, static_cast<int>(it));
+          ok = false;
+          break;
+        }
+        if (elect_one()) {
           uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
           mbar_arrive_expect_tx(&full[s], stage_bytes);
           for (int a = 0; a < p.katoms; ++a) {
@@ -161,51 +164,73 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             if (p.dual) tma_load_2d(st + a_bytes + a * b_atom + b_bytes, &tm_b, kx, p.dual_off + bt * p.bn, &full[s]);
           }
         }
+        __syncwarp();
+        if (++s == static_cast<uint32_t>(p.stages)) {
+          s = 0;
+          ph ^= 1u;
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc(kBM, p.bn, 1, 1);
-      const uint32_t idesc2 = umma_idesc(kBM, 2 * p.bn, 1, 1);  // gate and up tiles are adjacent in smem
-      uint32_t it = 0, ui = 0;
-      bool ok = true;
-      int cur = it_lo;
-      Seg sg;
-      for (; ok && next_seg(cur, it_hi, p.kblocks_total, stride, sg); ++ui) {
-        const int kb0 = sg.kb0, kb1 = sg.kb1;
-        const uint32_t ab = ui % p.nbuf;
-        if (!mbar_wait(&tmem_empty[ab], ((ui / p.nbuf) & 1u) ^ 1u)) {
-          report_error(p.err, kErrBarrierTimeout, 41, static_cast<int>(ui));
+    const uint32_t idesc = p.dual ? umma_idesc(kBM, 2 * p.bn, 1, 1)   // gate and up tiles are adjacent in smem
+                                  : umma_idesc(kBM, p.bn, 1, 1);
+    const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);   // stride byte offset, version, 128-byte swizzle
+    const uint32_t lo0 = ((smem_u32(smem) & 0x3FFFFu) >> 4) | (1u << 16);
+    uint32_t it = 0, s = 0, ph = 0;      // K blocks issued, stage, phase of its `full` barrier
+    uint32_t ab = 0, ab_ph = 1;          // accumulator buffer and the phase of `tmem_empty` to wait for (first use: free)
+    bool ok = true;
+    int cur = it_lo;
+    Seg sg;
+    while (ok && next_seg(cur, it_hi, p.kblocks_total, stride, sg)) {
+      const int kb0 = sg.kb0, kb1 = sg.kb1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_empty[ab], ab_ph))) {
+        if (lane == 0) report_error(p.err, kErrBarrierTimeout, 41, static_cast<int>(it));
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t d0 = tmem_base + ab * buf_cols;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&full[s], ph))) {
+          if (lane == 0) report_error(p.err, kErrBarrierTimeout, 42, static_cast<int>(it));
+          ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d0 = tmem_base + ab * buf_cols;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const uint32_t s = it % p.stages, round = it / p.stages;
-          if (!mbar_wait(&full[s], round & 1u)) {
-            report_error(p.err, kErrBarrierTimeout, 42, static_cast<int>(it));
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
-          const uint32_t b_addr = a_addr + a_bytes;
+        if (elect_one()) {
+          const uint32_t a_lo = lo0 + s * (stage_bytes >> 4);
+          const uint32_t b_lo = a_lo + (a_bytes >> 4);
           for (int a = 0; a < p.katoms; ++a) {
 #pragma unroll
-            for (int k = 0; k < kBK / 16; ++k) {
+            for (uint32_t k = 0; k < kBK / 16; ++k) {   // 16 bf16 = 32 bytes of K per step: the address field moves by 2
               const uint32_t acc = (kb > kb0 || a > 0 || k > 0) ? 1u : 0u;
-              const uint64_t bd = umma_desc_sw128(b_addr + a * b_atom + k * 32);
-              for (int mi = 0; mi < p.mt; ++mi)
-                umma_bf16(d0 + mi * acc_cols, umma_desc_sw128(a_addr + a * a_atom + mi * (kBM * 128) + k * 32), bd,
-                          p.dual ? idesc2 : idesc, acc);
+              const uint64_t bd = (static_cast<uint64_t>(desc_hi) << 32) | (b_lo + a * (b_atom >> 4) + 2 * k);
+              for (int mi = 0; mi < p.mt; ++mi) {
+                const uint64_t ad = (static_cast<uint64_t>(desc_hi) << 32) |
+                                    (a_lo + a * (a_atom >> 4) + mi * ((kBM * 128) >> 4) + 2 * k);
+                umma_bf16(d0 + mi * acc_cols, ad, bd, idesc, acc);
+              }
             }
           }
           umma_commit(&empty[s]);
         }
-        if (ok) umma_commit(&tmem_full[ab]);
+        __syncwarp();
+        if (++s == static_cast<uint32_t>(p.stages)) {
+          s = 0;
+          ph ^= 1u;
+        }
       }
-      // TMEM is released only after every MMA has completed, also when a wait gave up
+      if (ok && elect_one()) umma_commit(&tmem_full[ab]);
+      __syncwarp();
+      if (p.nbuf == 2) {
+        ab ^= 1u;
+        if (ab == 0) ab_ph ^= 1u;
+      } else {
+        ab_ph ^= 1u;
+      }
+    }
+    // TMEM is released only after every MMA has completed, also when a wait gave up
+    if (elect_one()) {
       umma_commit(drain);
       if (!mbar_wait(drain, 0)) report_error(p.err, kErrBarrierTimeout, 44, static_cast<int>(it));
     }
