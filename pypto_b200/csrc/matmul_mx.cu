@@ -134,64 +134,88 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   pdl_wait();
   const int tiles = p.m_tiles * p.n_tiles;
 
+  // Producer and issuer are one-thread jobs whose instruction streams sit on the critical path of every K block: the
+  // whole warp walks the loop and waits (warp-uniform code keeps descriptors in uniform registers), one elected lane
+  // issues, and stages and barrier phases are carried along instead of divided out.
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
-        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-          const uint32_t s = it % p.stages, round = it / p.stages;
-          if (!mbar_wait(&empty[s], (round & 1u) ^ 1u)) {
-            report_error(p.err, kErrBarrierTimeout, 70, static_cast<int>(it));
-            ok = false;
-            break;
-          }
+    uint32_t it = 0, s = 0, ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
+      for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u))) {
+          if (lane == 0) report_error(p.err, kErrBarrierTimeout, 70, static_cast<int>(it));
+          ok = false;
+          break;
+        }
+        if (elect_one()) {
           uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
           mbar_arrive_expect_tx(&full[s], a_bytes + b_bytes);
           tma_load_2d(st, &tm_a, kb * kMxBK, mt * 128, &full[s]);          // past m or k the box is zero filled
           for (uint32_t c = 0; c < sfb_chunks; ++c)
             tma_load_2d(st + a_bytes + c * (128 * kMxBK), &tm_b, kb * kMxBK, nt * p.bn + c * 128, &full[s]);
         }
+        __syncwarp();
+        if (++s == static_cast<uint32_t>(p.stages)) {
+          s = 0;
+          ph ^= 1u;
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
-      uint32_t it = 0, ui = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++ui) {
-        const uint32_t ab = ui % p.nbuf;
-        if (!mbar_wait(&tmem_empty[ab], ((ui / p.nbuf) & 1u) ^ 1u)) {
-          report_error(p.err, kErrBarrierTimeout, 71, static_cast<int>(ui));
+    uint32_t it = 0, s = 0, ph = 0;
+    uint32_t ab = 0, ab_ph = 1;          // accumulator buffer and the phase of `tmem_empty` to wait for (first use: free)
+    bool ok = true;
+    const uint32_t idesc0 = mx_idesc(128, static_cast<uint32_t>(p.bn), 0, 0), idesc1 = mx_idesc(128, static_cast<uint32_t>(p.bn), 1, 1);
+    const uint32_t idesc2 = mx_idesc(128, static_cast<uint32_t>(p.bn), 2, 2), idesc3 = mx_idesc(128, static_cast<uint32_t>(p.bn), 3, 3);
+    const uint32_t smem0 = smem_u32(smem);
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_empty[ab], ab_ph))) {
+        if (lane == 0) report_error(p.err, kErrBarrierTimeout, 71, static_cast<int>(it));
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t d0 = tmem_base + ab * p.bn;
+      for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&full[s], ph))) {
+          if (lane == 0) report_error(p.err, kErrBarrierTimeout, 72, static_cast<int>(it));
+          ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d0 = tmem_base + ab * p.bn;
-        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-          const uint32_t s = it % p.stages, round = it / p.stages;
-          if (!mbar_wait(&full[s], round & 1u)) {
-            report_error(p.err, kErrBarrierTimeout, 72, static_cast<int>(it));
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * stage_bytes);
+        if (elect_one()) {
+          const uint32_t a_addr = smem0 + s * stage_bytes;
           const uint32_t b_addr = a_addr + a_bytes;
           const uint32_t sf_addr = b_addr + b_bytes;
           const uint32_t tsfa = tmem_base + sf_col0 + (it & 1u) * sf_set;
           const uint32_t tsfb = tsfa + 4;
           tmem_cp_32x128b_warpx4(tsfa, sf_desc(sf_addr));
           for (uint32_t c = 0; c < sfb_chunks; ++c) tmem_cp_32x128b_warpx4(tsfb + 4 * c, sf_desc(sf_addr + 512 * (1 + c)));
-#pragma unroll
-          for (uint32_t g = 0; g < 4; ++g)
-            umma_mxf8(d0, umma_desc_sw128(a_addr + g * 32), umma_desc_sw128(b_addr + g * 32),
-                      mx_idesc(128, static_cast<uint32_t>(p.bn), g, g), (kb > 0 || g > 0) ? 1u : 0u, tsfa, tsfb);
+          const uint64_t ad = umma_desc_sw128(a_addr), bd = umma_desc_sw128(b_addr);   // + 2 per 32 bytes of K
+          umma_mxf8(d0, ad, bd, idesc0, kb > 0 ? 1u : 0u, tsfa, tsfb);
+          umma_mxf8(d0, ad + 2, bd + 2, idesc1, 1u, tsfa, tsfb);
+          umma_mxf8(d0, ad + 4, bd + 4, idesc2, 1u, tsfa, tsfb);
+          umma_mxf8(d0, ad + 6, bd + 6, idesc3, 1u, tsfa, tsfb);
           umma_commit(&empty[s]);
         }
-        if (ok) umma_commit(&tmem_full[ab]);
+        __syncwarp();
+        if (++s == static_cast<uint32_t>(p.stages)) {
+          s = 0;
+          ph ^= 1u;
+        }
       }
+      if (ok && elect_one()) umma_commit(&tmem_full[ab]);
+      __syncwarp();
+      if (p.nbuf == 2) {
+        ab ^= 1u;
+        if (ab == 0) ab_ph ^= 1u;
+      } else {
+        ab_ph ^= 1u;
+      }
+    }
+    if (elect_one()) {
       umma_commit(drain);   // tensor memory is released only after every MMA has completed
       if (!mbar_wait(drain, 0)) report_error(p.err, kErrBarrierTimeout, 74, static_cast<int>(it));
     }
@@ -245,12 +269,13 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     // turn, so each has four MMA periods for the memory latency of its stage.
     const int lw = warp - 6;   // 0 .. 3
     uint32_t it = 0;
+    uint32_t s = static_cast<uint32_t>(lw) % static_cast<uint32_t>(p.stages);          // stage of this warp's next K block
+    uint32_t round = static_cast<uint32_t>(lw) / static_cast<uint32_t>(p.stages);      // and how often it was refilled
     bool ok = true;
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
       const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
       for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
         if ((it & 3u) != static_cast<uint32_t>(lw)) continue;
-        const uint32_t s = it % p.stages, round = it / p.stages;
         const int g0 = kb * 4;
         // loads first (they do not touch the stage), then the wait for the stage, then the stores
         uint32_t wa[4], wb[8];
@@ -290,6 +315,11 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         fence_proxy_async_smem();   // the chunk is read by tcgen05.cp (async proxy)
         __syncwarp();
         if (lane == 0) mbar_arrive(&full[s]);
+        s += 4;                     // this warp's next K block is four further on
+        while (s >= static_cast<uint32_t>(p.stages)) {
+          s -= static_cast<uint32_t>(p.stages);
+          ++round;
+        }
       }
     }
   }
