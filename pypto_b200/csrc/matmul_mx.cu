@@ -45,19 +45,23 @@ struct MxParams {
   int* err;
 };
 
-// E8M0 code of (row, K group) of the left operand; 127 (= 1.0) outside the matrix.
-__device__ __forceinline__ uint32_t a_scale_code(const MxParams& p, int row, int g) {
-  if (row >= p.m || g >= p.kgroups) return 127u;
+// Address of the E8M0 code of (row, K group) of the left operand.  The loaders read every code with an
+// unconditional load from a clamped position and replace codes outside the matrix by 127 (= 1.0) afterwards:
+// a load behind a bounds branch cannot be issued ahead of the branch, and a K block needs 36 of them per lane.
+__device__ __forceinline__ const uint8_t* a_scale_ptr(const MxParams& p, int row, int g) {
+  row = min(row, p.m - 1);
+  g = min(g, p.kgroups - 1);
   if (p.a_layout == PTO_MX_SCALE_A_ZZ)   // [m/16][kg/2][16][2]
-    return p.a_scale[(static_cast<size_t>(row >> 4) * (p.kgroups >> 1) + (g >> 1)) * 32 + (row & 15) * 2 + (g & 1)];
-  return p.a_scale[static_cast<size_t>(row) * p.kgroups + g];
+    return p.a_scale + (static_cast<size_t>(row >> 4) * (p.kgroups >> 1) + (g >> 1)) * 32 + (row & 15) * 2 + (g & 1);
+  return p.a_scale + static_cast<size_t>(row) * p.kgroups + g;
 }
-// E8M0 code of (K group, column) of the right operand.
-__device__ __forceinline__ uint32_t b_scale_code(const MxParams& p, int col, int g) {
-  if (col >= p.n || g >= p.kgroups) return 127u;
+// Address of the E8M0 code of (K group, column) of the right operand.
+__device__ __forceinline__ const uint8_t* b_scale_ptr(const MxParams& p, int col, int g) {
+  col = min(col, p.n - 1);
+  g = min(g, p.kgroups - 1);
   if (p.b_layout == PTO_MX_SCALE_B_NN)   // [n/16][kg/2][16][2]
-    return p.b_scale[(static_cast<size_t>(col >> 4) * (p.kgroups >> 1) + (g >> 1)) * 32 + (col & 15) * 2 + (g & 1)];
-  return p.b_scale[static_cast<size_t>(g) * p.n + col];
+    return p.b_scale + (static_cast<size_t>(col >> 4) * (p.kgroups >> 1) + (g >> 1)) * 32 + (col & 15) * 2 + (g & 1);
+  return p.b_scale + static_cast<size_t>(g) * p.n + col;
 }
 
 // Shared-memory descriptor of one 512-byte scale chunk for tcgen05.cp: 32 rows of 16 bytes, no swizzle,
@@ -277,27 +281,116 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
         if ((it & 3u) != static_cast<uint32_t>(lw)) continue;
         const int g0 = kb * 4;
-        // loads first (they do not touch the stage), then the wait for the stage, then the stores
+        const int row0 = mt * 128, col0 = nt * p.bn;
+        // Loads first (they do not touch the stage), then the wait for the stage, then the stores.  A lane ends up
+        // with up to four left-operand words (rows ar[i]) and eight right-operand words (columns bc[i]); word =
+        // the four E8M0 codes of the K block, code g in byte g.
+        //
+        // Fast paths: when the tile lies inside the matrix and the scale arrays are aligned, a lane fetches the codes
+        // of several neighbouring rows / columns with a few wide loads and sorts the bytes in registers.  One-byte
+        // loads (the general path below) cost a memory round trip per 32 bytes and were 2.2x the time of the
+        // whole kernel.
         uint32_t wa[4], wb[8];
+        int ar[4], bc[8];
+        int na = 4, nb = 0;
+        const bool k_in = g0 + 4 <= p.kgroups && (p.kgroups & 3) == 0;
+        const bool a_fast_log = p.a_layout == PTO_MX_SCALE_LOGICAL && k_in && (reinterpret_cast<uintptr_t>(p.a_scale) & 3) == 0;
+        const bool a_fast_zz = p.a_layout == PTO_MX_SCALE_A_ZZ && k_in && row0 + 128 <= p.m &&
+                               (reinterpret_cast<uintptr_t>(p.a_scale) & 7) == 0;
+        const bool b_fast_log = p.b_layout == PTO_MX_SCALE_LOGICAL && k_in && col0 + p.bn <= p.n && (p.n & 7) == 0 &&
+                                (reinterpret_cast<uintptr_t>(p.b_scale) & 7) == 0;
+        const bool b_fast_nn = p.b_layout == PTO_MX_SCALE_B_NN && k_in && col0 + p.bn <= p.n &&
+                               (reinterpret_cast<uintptr_t>(p.b_scale) & 15) == 0;
+        // ---- left operand ----
+        if (a_fast_zz) {
+          // [m/16][kg/2][16 rows][2 codes]: a group of 16 rows keeps codes (g0, g0+1) of its rows in 32 contiguous bytes
+          // and (g0+2, g0+3) in the next 32; lane = (group of 16 rows, quarter): four rows, two 8-byte loads
+          const int grp = lane >> 2, qd = lane & 3;
+          const uint8_t* base = p.a_scale + (static_cast<size_t>((row0 >> 4) + grp) * (p.kgroups >> 1) + (g0 >> 1)) * 32 + 8 * qd;
+          const uint2 lo = __ldg(reinterpret_cast<const uint2*>(base)), hi = __ldg(reinterpret_cast<const uint2*>(base + 32));
+          wa[0] = __byte_perm(lo.x, hi.x, 0x5410); wa[1] = __byte_perm(lo.x, hi.x, 0x7632);
+          wa[2] = __byte_perm(lo.y, hi.y, 0x5410); wa[3] = __byte_perm(lo.y, hi.y, 0x7632);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int row = mt * 128 + j * 32 + lane;
-          if (p.a_layout == PTO_MX_SCALE_LOGICAL && row < p.m && g0 + 4 <= p.kgroups && (p.kgroups & 3) == 0) {
-            wa[j] = *reinterpret_cast<const uint32_t*>(p.a_scale + static_cast<size_t>(row) * p.kgroups + g0);
+          for (int i = 0; i < 4; ++i) ar[i] = grp * 16 + qd * 4 + i;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) ar[j] = j * 32 + lane;
+          if (a_fast_log) {   // four codes of a row are one aligned word
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wa[j] = __ldg(reinterpret_cast<const uint32_t*>(a_scale_ptr(p, row0 + ar[j], g0)));
           } else {
-            wa[j] = 0;
+            uint32_t ca[16];
 #pragma unroll
-            for (int g = 0; g < 4; ++g) wa[j] |= a_scale_code(p, row, g0 + g) << (8 * g);
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+              for (int g = 0; g < 4; ++g) ca[j * 4 + g] = __ldg(a_scale_ptr(p, row0 + ar[j], g0 + g));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wa[j] = ca[j * 4] | (ca[j * 4 + 1] << 8) | (ca[j * 4 + 2] << 16) | (ca[j * 4 + 3] << 24);
+          }
+          // codes outside the matrix count as 1.0
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const bool row_in = row0 + ar[j] < p.m;
+            uint32_t w = wa[j];
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              if (!row_in || g0 + g >= p.kgroups) w = (w & ~(0xFFu << (8 * g))) | (127u << (8 * g));
+            wa[j] = w;
           }
         }
-        const int nb_words = static_cast<int>(sfb_chunks) * 4;
+        // ---- right operand ----
+        if (b_fast_log) {
+          // [kg][n]: the codes of one K group are contiguous over the columns; lane = eight neighbouring columns, one
+          // 8-byte load per K group, then a 4 x 8 byte transpose
+          if (8 * lane < p.bn) {
+            nb = 8;
+            const uint8_t* base = p.b_scale + static_cast<size_t>(g0) * p.n + col0 + 8 * lane;
+            const uint2 v0 = __ldg(reinterpret_cast<const uint2*>(base)), v1 = __ldg(reinterpret_cast<const uint2*>(base + p.n));
+            const uint2 v2 = __ldg(reinterpret_cast<const uint2*>(base + 2 * static_cast<size_t>(p.n)));
+            const uint2 v3 = __ldg(reinterpret_cast<const uint2*>(base + 3 * static_cast<size_t>(p.n)));
+            uint32_t t0 = __byte_perm(v0.x, v1.x, 0x5140), t1 = __byte_perm(v2.x, v3.x, 0x5140);
+            uint32_t t2 = __byte_perm(v0.x, v1.x, 0x7362), t3 = __byte_perm(v2.x, v3.x, 0x7362);
+            wb[0] = __byte_perm(t0, t1, 0x5410); wb[1] = __byte_perm(t0, t1, 0x7632);
+            wb[2] = __byte_perm(t2, t3, 0x5410); wb[3] = __byte_perm(t2, t3, 0x7632);
+            t0 = __byte_perm(v0.y, v1.y, 0x5140); t1 = __byte_perm(v2.y, v3.y, 0x5140);
+            t2 = __byte_perm(v0.y, v1.y, 0x7362); t3 = __byte_perm(v2.y, v3.y, 0x7362);
+            wb[4] = __byte_perm(t0, t1, 0x5410); wb[5] = __byte_perm(t0, t1, 0x7632);
+            wb[6] = __byte_perm(t2, t3, 0x5410); wb[7] = __byte_perm(t2, t3, 0x7632);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          wb[j] = 0;
-          if (j < nb_words) {
-            const int col = nt * p.bn + j * 32 + lane;
+            for (int i = 0; i < 8; ++i) bc[i] = 8 * lane + i;
+          }
+        } else if (b_fast_nn) {
+          // [n/16][kg/2][16 columns][2 codes]: as the left operand's physical layout; lane = (group of 16 columns,
+          // half): eight columns, two 16-byte loads
+          const int grp = lane >> 1, hf = lane & 1;
+          if (grp * 16 < p.bn) {
+            nb = 8;
+            const uint8_t* base = p.b_scale + (static_cast<size_t>((col0 >> 4) + grp) * (p.kgroups >> 1) + (g0 >> 1)) * 32 + 16 * hf;
+            const uint4 lo = __ldg(reinterpret_cast<const uint4*>(base)), hi = __ldg(reinterpret_cast<const uint4*>(base + 32));
+            wb[0] = __byte_perm(lo.x, hi.x, 0x5410); wb[1] = __byte_perm(lo.x, hi.x, 0x7632);
+            wb[2] = __byte_perm(lo.y, hi.y, 0x5410); wb[3] = __byte_perm(lo.y, hi.y, 0x7632);
+            wb[4] = __byte_perm(lo.z, hi.z, 0x5410); wb[5] = __byte_perm(lo.z, hi.z, 0x7632);
+            wb[6] = __byte_perm(lo.w, hi.w, 0x5410); wb[7] = __byte_perm(lo.w, hi.w, 0x7632);
 #pragma unroll
-            for (int g = 0; g < 4; ++g) wb[j] |= b_scale_code(p, col, g0 + g) << (8 * g);
+            for (int i = 0; i < 8; ++i) bc[i] = grp * 16 + hf * 8 + i;
+          }
+        } else {
+          nb = static_cast<int>(sfb_chunks) * 4;
+          uint32_t cb[32];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            bc[j] = j * 32 + lane;
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              cb[j * 4 + g] = j < nb ? static_cast<uint32_t>(__ldg(b_scale_ptr(p, col0 + bc[j], g0 + g))) : 127u;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const bool col_in = col0 + bc[j] < p.n;
+            uint32_t w = 0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) w |= ((col_in && g0 + g < p.kgroups) ? cb[j * 4 + g] : 127u) << (8 * g);
+            wb[j] = w;
           }
         }
         if (!mbar_wait_warp(&empty[s], (round & 1u) ^ 1u)) {
@@ -306,12 +399,17 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           break;
         }
         uint8_t* sf = smem + static_cast<size_t>(s) * stage_bytes + a_bytes + b_bytes;
-        // row r = j * 32 + lane of a 128-row chunk sits at byte (r % 32) * 16 + (r / 32) * 4 = lane * 16 + j * 4
+        // row (or column) r of a 128-row chunk sits at byte (r % 32) * 16 + (r / 32) * 4 of the chunk; the left
+        // operand's chunk comes first, the right operand's chunks (128 columns each) follow
 #pragma unroll
-        for (int j = 0; j < 4; ++j) *reinterpret_cast<uint32_t*>(sf + lane * 16 + j * 4) = wa[j];
+        for (int i = 0; i < 4; ++i)
+          if (i < na) *reinterpret_cast<uint32_t*>(sf + (ar[i] & 31) * 16 + (ar[i] >> 5) * 4) = wa[i];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (j < nb_words) *reinterpret_cast<uint32_t*>(sf + 512 * (1 + (j >> 2)) + lane * 16 + (j & 3) * 4) = wb[j];
+        for (int i = 0; i < 8; ++i)
+          if (i < nb) {
+            const int r = bc[i] & 127;
+            *reinterpret_cast<uint32_t*>(sf + 512 * (1 + (bc[i] >> 7)) + (r & 31) * 16 + (r >> 5) * 4) = wb[i];
+          }
         fence_proxy_async_smem();   // the chunk is read by tcgen05.cp (async proxy)
         __syncwarp();
         if (lane == 0) mbar_arrive(&full[s]);

@@ -55,6 +55,27 @@ def test_integer_operands_are_exact_at_ragged_and_large_shapes(m, n, k):
     assert torch.equal(out.cpu(), exp)
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 512, 512), (144, 272, 256), (4096, 2048, 1024)])
+def test_physical_scale_layouts_are_exact_at_larger_shapes(m, n, k):
+    """The reference's packed scale layouts (MX_A_ZZ, MX_B_NN; test_matmul_mx.py:38-117) on tiles that lie inside the
+    matrix (wide scale loads) and on tiles with row and column tails (byte loads), against the same golden."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randint(-2, 3, (m, k), generator=g).to(FP8)
+    b = torch.randint(-2, 3, (k, n), generator=g).to(FP8)
+    sa = torch.randint(125, 131, (m, k // 32), generator=g).to(torch.uint8)
+    sb = torch.randint(125, 131, (k // 32, n), generator=g).to(torch.uint8)
+    exp = omx.matmul_mx(a, sa, b, sb)
+    b_t = ops.transpose_u8(b.cuda().view(torch.uint8)).view(FP8)
+    out = ops.matmul_mx(a.cuda(), omx.pack_a_scale(sa).cuda(), b_t, omx.pack_b_scale(sb).cuda(),
+                        a_scale_layout=ops.MX_SCALE_A_ZZ, b_scale_layout=ops.MX_SCALE_B_NN)
+    mixed = ops.matmul_mx(a.cuda(), sa.cuda(), b_t, omx.pack_b_scale(sb).cuda(), b_scale_layout=ops.MX_SCALE_B_NN)
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    assert torch.equal(out.cpu(), exp)
+    assert torch.equal(mixed.cpu(), exp)
+
+
 def test_quantised_gaussian_operands_match_the_fp64_golden():
     ops = _ops()
     g = torch.Generator().manual_seed(3)
