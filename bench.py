@@ -67,9 +67,9 @@ DEFAULT_STEPS = {"decode": 200, "verify": 20, "ffn": 500, "layer": 200, "moe": 1
 # to capture; None where no capture exists)
 NCU_TRAFFIC = {"decode": 1406460304,            # pa_decode_kernel<1>
                "ffn": 26022144,                 # ffn_fused_kernel at M = 128 (the weights, read once)
-               "layer": 243135232,              # gate/up gemm_bf16_kernel launch of the layer
+               "layer": 240724480 + 6793216,    # gate/up gemm_bf16_kernel launch of the layer
                "moe": (488558848 + 9664768) * 16,   # gate/up moe_gemm_fp8_kernel, 16-expert capture x 16
-               "matmul_mx": 939629056 + 251107584}  # matmul_mx_kernel at 8192^3
+               "matmul_mx": 990629632 + 253626880}  # matmul_mx_kernel at 8192^3
 # pa_decode_kernel<2> on `--workload verify --small` (batch 16): DRAM bytes per byte of K/V that the step reads
 VERIFY_TRAFFIC_PER_KV_BYTE = (1222118000 + 12380416) / 1215746048
 
