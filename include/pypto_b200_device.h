@@ -62,5 +62,43 @@ __device__ __forceinline__ double pto_scalar<double>(const int64_t* args, int i)
 __device__ __forceinline__ int32_t pto_block_idx() { return static_cast<int32_t>(blockIdx.x); }
 __device__ __forceinline__ int32_t pto_block_num() { return static_cast<int32_t>(gridDim.x); }
 
+/* ---- reporting instead of faulting ----
+ * The worker's device error word (four int32: code, site, block, detail) is what pto_device_status /
+ * ChipWorker.device_status() reads and clears after a call.  A kernel that meets a condition it cannot continue
+ * from records it there and returns; it never traps and never spins without a bound.  The first report wins.
+ * Codes: 1 = a bounded wait ran out (PTO_DEVICE_TIMEOUT on the host), 2 = a block id or row outside its pool,
+ * 3 = an index or count outside its array (both PTO_INVALID_ARGUMENT on the host). */
+#define PTO_ERR_WAIT_TIMEOUT 1
+#define PTO_ERR_BAD_BLOCK 2
+#define PTO_ERR_BAD_INDEX 3
+
+__device__ __forceinline__ int32_t* pto_error_word(const int64_t* args) {
+  return reinterpret_cast<int32_t*>(static_cast<uintptr_t>(args[-2]));   /* header slot in front of the arguments */
+}
+
+__device__ __forceinline__ void pto_report_error(const int64_t* args, int32_t code, int32_t site, int32_t detail) {
+  int32_t* w = pto_error_word(args);
+  if (atomicCAS(w, 0, code) == 0) {
+    w[1] = site;
+    w[2] = static_cast<int32_t>(blockIdx.x);
+    w[3] = detail;
+    __threadfence();
+  }
+}
+
+/* Spins until *flag == expected or `timeout_ns` of wall time have passed (%globaltimer).  Returns false on timeout;
+ * the caller reports and returns.  The waiter and whoever sets the flag must be able to run at the same time:
+ * blocks of one cooperative launch, or another device or the host -- never a later launch on the same GPU. */
+__device__ __forceinline__ bool pto_bounded_wait(const volatile int32_t* flag, int32_t expected, uint64_t timeout_ns) {
+  uint64_t t0, t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (*flag == expected) return true;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (t - t0 > timeout_ns) return false;
+  }
+}
+
 #endif /* __CUDACC__ */
 #endif /* PYPTO_B200_DEVICE_H_ */

@@ -372,9 +372,11 @@ int pto_run_kernel(pto_worker* h, int32_t cid, const pto_task_args* args, uint32
     return pto::fail(pto::kInvalidArgument, "run_kernel: block_num >= 1 and 1 <= threads_per_block <= 1024");
   if ((args->n_tensors && !args->tensors) || (args->n_scalars && !args->scalars))
     return pto::fail(pto::kInvalidArgument, "run_kernel: NULL tensor or scalar array");
-  // block layout: int64 args[n_tensors + n_scalars], padded to 16 bytes, then the tensor descriptors
+  // block layout: a 16-byte header {address of the worker's device error word, reserved}, then what the kernel
+  // receives: int64 args[n_tensors + n_scalars], padded to 16 bytes, then the tensor descriptors
+  constexpr size_t kHeader = 16;
   const size_t n = static_cast<size_t>(args->n_tensors) + args->n_scalars;
-  const size_t desc_off = (n * sizeof(int64_t) + 15) & ~static_cast<size_t>(15);
+  const size_t desc_off = kHeader + ((n * sizeof(int64_t) + 15) & ~static_cast<size_t>(15));
   const size_t total = desc_off + args->n_tensors * sizeof(pto_chip_tensor);
   if (total > pto::kExternArgSlotBytes) return pto::fail(pto::kInvalidArgument, "run_kernel: too many arguments");
   cudaKernel_t kernel = nullptr;
@@ -387,8 +389,14 @@ int pto_run_kernel(pto_worker* h, int32_t cid, const pto_task_args* args, uint32
     slot = static_cast<uint8_t*>(it->second.args_dev) +
            (it->second.next_slot++ % pto::kExternArgSlots) * pto::kExternArgSlotBytes;
   }
+  {
+    const int st = w->ensure_scratch(4096);   // the error word lives at the start of the worker's scratch arena
+    if (st != pto::kOk) return st;
+  }
   alignas(16) uint8_t block[pto::kExternArgSlotBytes];
-  int64_t* a = reinterpret_cast<int64_t*>(block);
+  reinterpret_cast<int64_t*>(block)[0] = static_cast<int64_t>(reinterpret_cast<uintptr_t>(w->scratch));
+  reinterpret_cast<int64_t*>(block)[1] = 0;
+  int64_t* a = reinterpret_cast<int64_t*>(block + kHeader);
   for (uint32_t i = 0; i < args->n_tensors; ++i)
     a[i] = static_cast<int64_t>(reinterpret_cast<uintptr_t>(slot + desc_off + i * sizeof(pto_chip_tensor)));
   for (uint32_t i = 0; i < args->n_scalars; ++i) a[args->n_tensors + i] = static_cast<int64_t>(args->scalars[i]);
@@ -396,7 +404,7 @@ int pto_run_kernel(pto_worker* h, int32_t cid, const pto_task_args* args, uint32
   // Pageable source: the runtime stages it before returning, so `block` may go out of scope.  The ring slot is
   // reused only after kExternArgSlots later launches on the same stream, i.e. after this launch has finished.
   PTO_CUDA(cudaMemcpyAsync(slot, block, total, cudaMemcpyHostToDevice, w->stream));
-  void* dev_args = slot;
+  void* dev_args = slot + kHeader;
   void* params[] = {&dev_args};
   PTO_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(kernel), dim3(block_num), dim3(threads_per_block), params, 0,
                             w->stream));

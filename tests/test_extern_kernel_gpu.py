@@ -97,3 +97,26 @@ def test_c_abi_error_paths():
         assert lib.pto_run_kernel(w._handle, good + 1000, C.byref(args), 1, 128) == 6
         assert lib.pto_unregister_callable(w._handle, good) == 0
         assert lib.pto_run_kernel(w._handle, good, C.byref(args), 1, 128) == 6
+
+
+def test_bounded_wait_that_runs_out_is_reported_and_the_worker_stays_usable():
+    """Failure detection on the device without a fault: an external kernel waits 20 ms for a flag nothing sets, records
+    a timeout in the worker's error word and returns; the launch surface raises PTO_DEVICE_TIMEOUT with the site, and
+    the same worker then runs the same kernel with the flag set."""
+    @pl.jit.extern(core_type="aiv", source="extern_kernels/aiv/wait_for_flag.cu")
+    def wait_for_flag(flag: pl.Tensor, out: pl.InOut[pl.Tensor], timeout_us: pl.Scalar[pl.INT64]) -> pl.Tensor: ...
+
+    @pl.jit
+    def entry(flag: pl.Tensor, out: pl.InOut[pl.Tensor], timeout_us: pl.Scalar[pl.INT64]) -> pl.Tensor:
+        out = wait_for_flag(flag, out, timeout_us)
+        return out
+
+    with ChipWorker(RunConfig(platform="b200")) as wk:
+        out = torch.zeros(1)
+        with pytest.raises(_lib.PtoError) as ei:
+            entry(torch.zeros(1, dtype=torch.int32), out, 20000)
+        assert ei.value.status == 4 and "site 900" in str(ei.value)          # PTO_DEVICE_TIMEOUT
+        assert out.item() == 0.0
+        assert wk.device_status() == (0, 0, 0, 0)          # reading the word cleared it
+        entry(torch.ones(1, dtype=torch.int32), out, 20000)
+        assert out.item() == 1.0
