@@ -337,6 +337,9 @@ int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total,
   PTO_REQUIRE(!dual || (bn <= 128 && !swap), "gemm: SwiGLU epilogue needs bn <= 128 and the normal orientation");
   PTO_REQUIRE(epi != kGemmEpiAtomic || !out_bf16, "gemm: atomic epilogue accumulates in fp32");
   (void)k_chunks;
+  // large whole-tile problems run on CTA pairs (256 x 256 tiles, half the B tile per CTA)
+  if (gemm2_eligible(a_rows, b_rows, k, epi, swap, bn, dual))
+    return gemm2_bf16_launch(a, a_rows, b, b_rows_total, b_rows, k, out, ldo, out_bf16, epi, dual_off, err, stream);
 
   GemmParams p;
   p.a_rows = a_rows; p.b_rows = b_rows; p.k = k;

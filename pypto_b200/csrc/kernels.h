@@ -37,6 +37,10 @@ enum GemmEpi : int { kGemmEpiStore = 0, kGemmEpiAtomic = 1, kGemmEpiSwiglu = 2 }
 int gemm_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total, int b_rows, int k, void* out,
                      long long ldo, int out_bf16, int swap, int epi, int dual_off, int bn, int k_chunks,
                      int* err, cudaStream_t stream);
+// gemm2.cu: the same product on CTA pairs (tcgen05.mma.cta_group::2), whole 256 x 256 tiles, store or SwiGLU epilogue
+bool gemm2_eligible(int a_rows, int b_rows, int k, int epi, int swap, int bn, int dual);
+int gemm2_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total, int b_rows, int k, void* out, long long ldo,
+                      int out_bf16, int epi, int dual_off, int* err, cudaStream_t stream);
 
 // linear.cpp
 int linear_launch(const void* x, const void* w_packed, float* out, int m, int n, int k, int accumulate, int* err,

@@ -67,6 +67,20 @@ def test_large_m_256_row_tiles():
     _check(got, offn.ffn_swiglu_bf16(xb, wgb, wub, wdb), 5e-3, "ffn 5000x2048x2048")
 
 
+@pytest.mark.parametrize("m,n,k", [(1300, 3400, 264), (2048, 19200, 64), (4096, 4736, 1024)])
+def test_linear_on_cta_pairs_with_ragged_edges(m, n, k):
+    """Shapes that run on CTA pairs (256 x 256 tiles, tcgen05.mma.cta_group::2): row, column and K tails, a single
+    K block per tile (every hand-off of the pair once per tile), and many tiles per pair."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(k, n, generator=g) * 0.05).bfloat16()
+    got = ops.linear(x.cuda(), ops.pack_weight(w.cuda()))
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    _check(got, x.float() @ w.float(), 2e-3, f"linear on pairs {m}x{n}x{k}")
+
+
 def test_pack_weight_from_fp32_rounds_to_bf16():
     w = torch.randn(96, 40)
     wp = _ops().pack_weight(w.cuda())
