@@ -57,7 +57,9 @@ struct GemmParams {
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
   // sigmoid as recip(1 + exp(-g)), the form of examples/models/01_ffn.py:66-77
-  return g * (1.f / (1.f + __expf(-g))) * u;
+  // (approximate quotient, 2 ulp: an IEEE division costs a dozen instructions per element and made the epilogue of
+  // short-K tiles longer than their MMAs)
+  return __fdividef(g, 1.f + __expf(-g)) * u;
 }
 
 // Segment walk shared by the three roles: iterations [lo, hi) of this CTA, cut at tile

@@ -94,7 +94,10 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 
-__device__ __forceinline__ float silu_mul2(float g, float u) { return g * (1.f / (1.f + __expf(-g))) * u; }
+// silu(g) * u with the sigmoid as recip(1 + exp(-g)) (examples/models/01_ffn.py:66-77); the quotient is the approximate
+// one (2 ulp): an IEEE division costs a dozen instructions per element and the epilogue of a short-K tile is as long as
+// the tile's MMAs
+__device__ __forceinline__ float silu_mul2(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kG2Threads, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Gemm2Params p) {

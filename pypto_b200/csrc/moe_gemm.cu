@@ -519,7 +519,7 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
               float g0, g1, u0, u1;
               unpack_f32x2(acc_a[4 * v + j], g0, g1);
               unpack_f32x2(acc_b[4 * v + j], u0, u1);
-              o[j] = pack_bf16x2(g0 * (1.f / (1.f + __expf(-g0))) * u0, g1 * (1.f / (1.f + __expf(-g1))) * u1);
+              o[j] = pack_bf16x2(__fdividef(g0, 1.f + __expf(-g0)) * u0, __fdividef(g1, 1.f + __expf(-g1)) * u1);
             }
             dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
           }
