@@ -804,16 +804,24 @@ def run_matmul_mx(args, d: Dist):
                    "kind": "port", "sample": f"{cm} of {m} rows, the reference's dequantise + fp64 matmul golden"}
     value = d.world * flops / sec / 1e12
     t_rank = ms / 1e3 / steps
+    # problems of this size run on SM pairs (the launcher's rule): a kernel that packs the scale blocks, then the matmul
+    sms = torch.cuda.get_device_properties(d.dev).multi_processor_count
+    pair = (os.environ.get("PTO_MX_PAIR", "1") != "0" and m >= 512 and n >= 448 and k >= 1024
+            and -(-m // 256) * -(-n // 224) >= sms)
     return line(args, d, metric="matmul_mx_TFLOPs", unit="TFLOP/s", value=value, sec_per_step=sec, scaling="weak",
                 dtype="fp8_e4m3 x E8M0 scale per 32",
                 config={"workload": f"matmul_mx m{m} n{n} k{k} e4m3 operands, E8M0 scale per 32-wide K group, fp32 out",
                         "l2": "operands 2 x 67 MB, output 268 MB: larger than L2", "parallelism": "replicas only",
                         "rounds": rounds},
-                launches=steps, clocks=clocks,
+                launches=steps * (2 if pair else 1), clocks=clocks,
                 roofline={"bound": "tensor", "achieved": flops / t_rank / 1e12, "peak": fp8, "unit": "TFLOP/s",
-                          "frac": flops / t_rank / 1e12 / fp8 if fp8 else None, "traffic": NCU_TRAFFIC["matmul_mx"],
+                          "frac": flops / t_rank / 1e12 / fp8 if fp8 else None,
+                          "traffic": None if pair else NCU_TRAFFIC["matmul_mx"],
+                          "traffic_note": ("the profiler does not list kernels launched as clusters; the one-CTA kernel "
+                                           f"(PTO_MX_PAIR=0) moved {NCU_TRAFFIC['matmul_mx']} bytes at 8192^3") if pair else None,
                           "peak_source": "measured here: torch._scaled_mm e4m3 8192^3, best of 10",
-                          "note": "2*m*n*k / CUDA-event time of matmul_mx_kernel"},
+                          "note": "2*m*n*k / CUDA-event time of the call: mx_pack_scales_kernel + matmul_mx_pair_kernel"
+                                  if pair else "2*m*n*k / CUDA-event time of matmul_mx_kernel"},
                 cpu_baseline=cpu, e2e=e2e)
 
 

@@ -19,24 +19,44 @@
 // test_matmul_mx.py:38-101); the MMA thread moves a chunk to tensor memory with
 // `tcgen05.cp.32x128b.warpx4` and selects the byte with the scale-id field of the instruction.
 //
-// CTA = warp 0 TMA producer, warp 1 MMA issuer (owns tensor memory), warps 2-5 epilogue (one
-// TMEM lane quarter each), warps 6-9 scale loaders (one K block each, in turn).  Tiles of 128 x bn outputs (bn = 128 with two
-// accumulator buffers, or 256 with one) are taken round-robin by persistent CTAs.  Every wait is bounded.
+// One CTA (small and medium problems) = warp 0 TMA producer, warp 1 MMA issuer (owns tensor memory), warps 2-5
+// epilogue (one TMEM lane quarter each), warps 6-13 scale loaders (K blocks in turn, into a ring of scale blocks that
+// runs ahead of the operand stages).  Tiles of 128 x bn outputs (bn = 128 with two accumulator buffers, or 256 with
+// one) are taken by persistent CTAs in groups of tile rows, so that what the CTAs read at one time stays in L2.
+//
+// Large problems run on PAIRS of SMs (matmul_mx_pair_kernel: a cluster of two CTAs, tcgen05 .cta_group::2): a pair
+// shares one 256 x 224 tile, each CTA brings its own 128 rows of a and its own half (112 rows) of the b_t tile, so a
+// CTA's shared memory feeds the tensor core 30 KB per K block instead of 48 KB, and two accumulators (2 x 224
+// columns) plus the scale columns still fit the 512 columns of tensor memory.  The pair has no loader warps: a small
+// kernel first writes all scale blocks in the tensor core's order to scratch memory (1/32 of the operands' bytes) and
+// the producer fetches them by TMA with the operands, each CTA the block of its own 128 rows and the blocks of ALL
+// 224 columns.  (With loader warps in each CTA the pair ran at 1570-1800 TFLOP/s, with the blocks by TMA at 2230-2290:
+// the loaders' global loads take about 2200 cycles under the operand traffic, and their stores and arrivals competed
+// with the overlapped epilogue.)  The leader CTA issues the copies to tensor memory and the MMAs for both.
+// Barriers: full[s] lives in the leader (its producer's expect_tx for both CTAs' bytes); empty[s] and tmem_full[b]
+// are signalled in both CTAs by multicast commits; tmem_empty[b] lives in the leader (eight epilogue warps).
+// No load is multicast.  Every wait is bounded.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
+#include "pair.cuh"
 
 namespace pto {
 namespace {
 
-constexpr int kMxThreads = 320;
-constexpr int kMxScaleWarps = 4;
+constexpr int kMxScaleWarps = 8;                      // a power of two
+constexpr int kMxThreads = 192 + 32 * kMxScaleWarps;
+constexpr int kMxPairThreads = 192;                   // a pair has no loader warps: its scale blocks come by TMA
 constexpr int kMxMaxStages = 8;
 constexpr int kMxBK = 128;           // K bytes per stage = 4 scale groups
+constexpr int kMxSfSlots = 16;       // ring of scale blocks, one per K block; at least kMxScaleWarps
 
 struct MxParams {
   int m, n, k;
   int m_tiles, n_tiles, kblocks, kgroups;
   int bn, nbuf, stages;
+  int group_m;                     // tile rows per raster group
   const uint8_t* a_scale;
   const uint8_t* b_scale;
   int a_layout, b_layout;
@@ -64,6 +84,18 @@ __device__ __forceinline__ const uint8_t* b_scale_ptr(const MxParams& p, int col
   return p.b_scale + static_cast<size_t>(g) * p.n + col;
 }
 
+// Order of the tiles: groups of `group_m` tile rows, and within a group column after column.  The CTAs work on
+// neighbouring tile numbers at the same time, so what they read together is a block of about group_m tile rows by
+// (CTAs / group_m) tile columns: the group's rows of a stay in L2 while b_t streams through once per group, and
+// every line is fetched by many CTAs close together in time.
+__device__ __forceinline__ void tile_coords(int tile, int group_m, int m_tiles, int n_tiles, int& mt, int& nt) {
+  const int per_group = group_m * n_tiles;
+  const int g = tile / per_group, r = tile - g * per_group;
+  const int rows = min(group_m, m_tiles - g * group_m);
+  nt = r / rows;
+  mt = g * group_m + (r - nt * rows);
+}
+
 // Shared-memory descriptor of one 512-byte scale chunk for tcgen05.cp: 32 rows of 16 bytes, no swizzle,
 // 8-row groups 128 bytes apart.
 __device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
@@ -74,8 +106,12 @@ __device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
   return d;
 }
 
+template <bool PAIR>
 __device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t desc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+  if constexpr (PAIR)   // each CTA of the pair copies from its own shared memory to its own tensor memory
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+  else
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
 }
 
 // Block-scaled instruction descriptor: e4m3 x e4m3, K-major, E8M0 scales, M x N, scale byte ids.
@@ -83,32 +119,54 @@ __device__ __forceinline__ uint32_t mx_idesc(uint32_t m, uint32_t n, uint32_t a_
   return (b_sf_id << 4) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (a_sf_id << 29);
 }
 
+template <bool PAIR>
 __device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                           uint32_t accumulate, uint32_t tsfa, uint32_t tsfb) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
-      : "memory");
+  if constexpr (PAIR)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+        : "memory");
 }
 
-__global__ void __launch_bounds__(kMxThreads, 1)
-matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                 const MxParams p) {
+// One CTA's part.  PAIR: the CTA is one of a cluster of two; `rank` 0 is the leader.
+template <bool PAIR>
+__device__ __forceinline__ void matmul_mx_body(const CUtensorMap* tm_a, const CUtensorMap* tm_b, const CUtensorMap* tm_sfa,
+                                               const CUtensorMap* tm_sfb, const MxParams& p) {
   pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  const uint32_t a_bytes = 128 * kMxBK, b_bytes = static_cast<uint32_t>(p.bn) * kMxBK;
-  const uint32_t sfb_chunks = p.bn / 128;
-  const uint32_t sf_bytes = 512 * (1 + sfb_chunks);
-  const uint32_t stage_bytes = a_bytes + b_bytes + 1024 * ((sf_bytes + 1023) / 1024);   // keeps stages 1024-aligned
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
+  uint32_t rank = 0;
+  if constexpr (PAIR) rank = cluster_ctarank();
+  const int unit0 = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);       // first tile of this CTA (pair)
+  const int unit_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  constexpr int kTileM = PAIR ? 256 : 128;
+  const int my_row0 = static_cast<int>(rank) * 128;                  // this CTA's rows within the tile
+  // b_t rows this CTA loads per K block: the whole tile width, or its half of it
+  const uint32_t b_rows = PAIR ? static_cast<uint32_t>(p.bn) / 2 : static_cast<uint32_t>(p.bn);
+  const uint32_t a_bytes = 128 * kMxBK, b_bytes = b_rows * kMxBK;
+  const uint32_t sfb_chunks = (static_cast<uint32_t>(p.bn) + 127) / 128;
+  const uint32_t sf_bytes = 512 * (1 + sfb_chunks);        // one K block's scale chunks
+  // a multiple of 1024, so that stages stay aligned for the swizzle; a pair's stages end with the K block's scale block
+  const uint32_t stage_bytes = a_bytes + b_bytes + (PAIR ? 1024 * ((sf_bytes + 1023) / 1024) : 0);
+  // operand stages, then (one CTA) the ring of scale blocks, then the barriers
+  uint8_t* sf_ring = smem + static_cast<size_t>(p.stages) * stage_bytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sf_ring + (PAIR ? 0 : kMxSfSlots * sf_bytes));
   uint64_t* empty = full + kMxMaxStages;
   uint64_t* tmem_full = empty + kMxMaxStages;
   uint64_t* tmem_empty = tmem_full + 2;
   uint64_t* drain = tmem_empty + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
+  uint64_t* sf_full = drain + 1;
+  uint64_t* sf_empty = sf_full + kMxSfSlots;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_empty + kMxSfSlots);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr uint32_t tmem_cols = 512;
@@ -118,21 +176,29 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < p.stages; ++i) {
-      mbar_init(&full[i], 2);   // the TMA producer's expect_tx arrival and one scale-loader warp
+      mbar_init(&full[i], 1);    // the TMA producer's expect_tx arrival
       mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < kMxSfSlots; ++i) {
+      mbar_init(&sf_full[i], PAIR ? 2 : 1);   // one scale-loader warp (of each CTA)
+      mbar_init(&sf_empty[i], 1);             // the producer warp, once the K block's MMAs have completed
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tmem_full[i], 1);
-      mbar_init(&tmem_empty[i], 4);
+      mbar_init(&tmem_empty[i], PAIR ? 8 : 4);
     }
     mbar_init(drain, 1);
     fence_barrier_init();
-    tma_prefetch_desc(&tm_a);
-    tma_prefetch_desc(&tm_b);
+    tma_prefetch_desc(tm_a);
+    tma_prefetch_desc(tm_b);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
+  if (warp == 1) {
+    if constexpr (PAIR) tmem_alloc_pair(tmem_slot, tmem_cols);   // the same warp in each CTA of the pair, together
+    else tmem_alloc(tmem_slot, tmem_cols);
+  }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // both CTAs' barriers exist before anything is signalled across the pair
+  else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();
@@ -145,8 +211,9 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     // ------------------------------ TMA producer ------------------------------
     uint32_t it = 0, s = 0, ph = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-      const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
+    for (int tile = unit0; tile < tiles && ok; tile += unit_step) {
+      int mt, nt;
+      tile_coords(tile, p.group_m, p.m_tiles, p.n_tiles, mt, nt);
       for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
         if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u))) {
           if (lane == 0) report_error(p.err, kErrBarrierTimeout, 70, static_cast<int>(it));
@@ -154,11 +221,25 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           break;
         }
         if (elect_one()) {
+          // the K block that used this stage before has completed (its copies of the scales to tensor memory too):
+          // its slot of the scale ring is free.  Completions are seen in order, one per K block.
+          if (!PAIR && it >= static_cast<uint32_t>(p.stages)) mbar_arrive(&sf_empty[(it - p.stages) % kMxSfSlots]);
           uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
-          mbar_arrive_expect_tx(&full[s], a_bytes + b_bytes);
-          tma_load_2d(st, &tm_a, kb * kMxBK, mt * 128, &full[s]);          // past m or k the box is zero filled
-          for (uint32_t c = 0; c < sfb_chunks; ++c)
-            tma_load_2d(st + a_bytes + c * (128 * kMxBK), &tm_b, kb * kMxBK, nt * p.bn + c * 128, &full[s]);
+          if constexpr (PAIR) {
+            // both CTAs' bytes are counted by the leader's barrier, which its producer arms for the two of them
+            const uint32_t leader_full = mapa_u32(smem_u32(&full[s]), 0);
+            if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * (a_bytes + b_bytes + sf_bytes));
+            tma_load_2d_pair(st, tm_a, kb * kMxBK, mt * kTileM + my_row0, leader_full);
+            tma_load_2d_pair(st + a_bytes, tm_b, kb * kMxBK, nt * p.bn + static_cast<int>(rank * b_rows), leader_full);
+            // the scale blocks, packed beforehand in the tensor core's order: this CTA's 128 rows, and all columns
+            tma_load_2d_pair(st + a_bytes + b_bytes, tm_sfa, 0, (mt * 2 + static_cast<int>(rank)) * p.kblocks + kb, leader_full);
+            tma_load_2d_pair(st + a_bytes + b_bytes + 512, tm_sfb, 0, nt * p.kblocks + kb, leader_full);
+          } else {
+            mbar_arrive_expect_tx(&full[s], a_bytes + b_bytes);
+            tma_load_2d(st, tm_a, kb * kMxBK, mt * 128, &full[s]);          // past m or k the box is zero filled
+            for (uint32_t c = 0; c < sfb_chunks; ++c)
+              tma_load_2d(st + a_bytes + c * (128 * kMxBK), tm_b, kb * kMxBK, nt * p.bn + c * 128, &full[s]);
+          }
         }
         __syncwarp();
         if (++s == static_cast<uint32_t>(p.stages)) {
@@ -168,14 +249,15 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
+    // ------------------------------- MMA issuer (the leader's, for a pair) -------------------------------
     uint32_t it = 0, s = 0, ph = 0;
     uint32_t ab = 0, ab_ph = 1;          // accumulator buffer and the phase of `tmem_empty` to wait for (first use: free)
     bool ok = true;
-    const uint32_t idesc0 = mx_idesc(128, static_cast<uint32_t>(p.bn), 0, 0), idesc1 = mx_idesc(128, static_cast<uint32_t>(p.bn), 1, 1);
-    const uint32_t idesc2 = mx_idesc(128, static_cast<uint32_t>(p.bn), 2, 2), idesc3 = mx_idesc(128, static_cast<uint32_t>(p.bn), 3, 3);
-    const uint32_t smem0 = smem_u32(smem);
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+    const uint32_t idesc0 = mx_idesc(kTileM, static_cast<uint32_t>(p.bn), 0, 0), idesc1 = mx_idesc(kTileM, static_cast<uint32_t>(p.bn), 1, 1);
+    const uint32_t idesc2 = mx_idesc(kTileM, static_cast<uint32_t>(p.bn), 2, 2), idesc3 = mx_idesc(kTileM, static_cast<uint32_t>(p.bn), 3, 3);
+    const uint32_t smem0 = smem_u32(smem), sf_ring0 = smem_u32(sf_ring);
+    uint32_t slot = 0, sph = 0;          // slot of the scale ring and its phase
+    for (int tile = rank == 0 ? unit0 : tiles; tile < tiles && ok; tile += unit_step) {
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_empty[ab], ab_ph))) {
         if (lane == 0) report_error(p.err, kErrBarrierTimeout, 71, static_cast<int>(it));
         break;
@@ -188,29 +270,42 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           ok = false;
           break;
         }
+        if (!PAIR && !__all_sync(0xffffffffu, mbar_wait(&sf_full[slot], sph))) {
+          if (lane == 0) report_error(p.err, kErrBarrierTimeout, 76, static_cast<int>(it));
+          ok = false;
+          break;
+        }
         tc_fence_after_sync();
         if (elect_one()) {
           const uint32_t a_addr = smem0 + s * stage_bytes;
           const uint32_t b_addr = a_addr + a_bytes;
-          const uint32_t sf_addr = b_addr + b_bytes;
+          const uint32_t sf_addr = PAIR ? b_addr + b_bytes : sf_ring0 + slot * sf_bytes;
           const uint32_t tsfa = tmem_base + sf_col0 + (it & 1u) * sf_set;
           const uint32_t tsfb = tsfa + 4;
-          tmem_cp_32x128b_warpx4(tsfa, sf_desc(sf_addr));
-          for (uint32_t c = 0; c < sfb_chunks; ++c) tmem_cp_32x128b_warpx4(tsfb + 4 * c, sf_desc(sf_addr + 512 * (1 + c)));
+          tmem_cp_32x128b_warpx4<PAIR>(tsfa, sf_desc(sf_addr));
+          for (uint32_t c = 0; c < sfb_chunks; ++c) tmem_cp_32x128b_warpx4<PAIR>(tsfb + 4 * c, sf_desc(sf_addr + 512 * (1 + c)));
           const uint64_t ad = umma_desc_sw128(a_addr), bd = umma_desc_sw128(b_addr);   // + 2 per 32 bytes of K
-          umma_mxf8(d0, ad, bd, idesc0, kb > 0 ? 1u : 0u, tsfa, tsfb);
-          umma_mxf8(d0, ad + 2, bd + 2, idesc1, 1u, tsfa, tsfb);
-          umma_mxf8(d0, ad + 4, bd + 4, idesc2, 1u, tsfa, tsfb);
-          umma_mxf8(d0, ad + 6, bd + 6, idesc3, 1u, tsfa, tsfb);
-          umma_commit(&empty[s]);
+          umma_mxf8<PAIR>(d0, ad, bd, idesc0, kb > 0 ? 1u : 0u, tsfa, tsfb);
+          umma_mxf8<PAIR>(d0, ad + 2, bd + 2, idesc1, 1u, tsfa, tsfb);
+          umma_mxf8<PAIR>(d0, ad + 4, bd + 4, idesc2, 1u, tsfa, tsfb);
+          umma_mxf8<PAIR>(d0, ad + 6, bd + 6, idesc3, 1u, tsfa, tsfb);
+          if constexpr (PAIR) umma_commit_pair(&empty[s]);   // frees the stage in both CTAs
+          else umma_commit(&empty[s]);
         }
         __syncwarp();
         if (++s == static_cast<uint32_t>(p.stages)) {
           s = 0;
           ph ^= 1u;
         }
+        if (++slot == kMxSfSlots) {
+          slot = 0;
+          sph ^= 1u;
+        }
       }
-      if (ok && elect_one()) umma_commit(&tmem_full[ab]);
+      if (ok && elect_one()) {
+        if constexpr (PAIR) umma_commit_pair(&tmem_full[ab]);
+        else umma_commit(&tmem_full[ab]);
+      }
       __syncwarp();
       if (p.nbuf == 2) {
         ab ^= 1u;
@@ -219,8 +314,12 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         ab_ph ^= 1u;
       }
     }
-    if (elect_one()) {
-      umma_commit(drain);   // tensor memory is released only after every MMA has completed
+    if (rank == 0 && elect_one()) {
+      // tensor memory is released only after every MMA has completed
+      if constexpr (PAIR)
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(drain)) : "memory");
+      else
+        umma_commit(drain);
       if (!mbar_wait(drain, 0)) report_error(p.err, kErrBarrierTimeout, 74, static_cast<int>(it));
     }
     __syncwarp();
@@ -228,15 +327,21 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     // -------------------------------- epilogue --------------------------------
     const int q = warp & 3;   // TMEM lane quarter this warp may read
     uint32_t ui = 0;
-    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++ui) {
-      const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
+    uint32_t leader_empty0 = 0, leader_empty1 = 0;
+    if constexpr (PAIR) {
+      leader_empty0 = mapa_u32(smem_u32(&tmem_empty[0]), 0);
+      leader_empty1 = mapa_u32(smem_u32(&tmem_empty[1]), 0);
+    }
+    for (int tile = unit0; tile < tiles; tile += unit_step, ++ui) {
+      int mt, nt;
+      tile_coords(tile, p.group_m, p.m_tiles, p.n_tiles, mt, nt);
       const uint32_t ab = ui % p.nbuf;
       if (!mbar_wait_warp(&tmem_full[ab], (ui / p.nbuf) & 1u)) {
         report_error(p.err, kErrBarrierTimeout, 73, static_cast<int>(ui));
         break;
       }
       tc_fence_after_sync();
-      const int row = mt * 128 + q * 32 + lane;
+      const int row = mt * kTileM + my_row0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * p.bn;
       for (int c0 = 0; c0 < p.bn; c0 += 32) {
         uint32_t v[32];
@@ -264,24 +369,31 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[ab]);
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(ab ? leader_empty1 : leader_empty0);   // the leader's barrier, from either CTA
+        else mbar_arrive(&tmem_empty[ab]);
+      }
     }
-  } else {
-    // ------------------------------ scale loaders ------------------------------
+  } else if constexpr (!PAIR) {
+    // ------------------------------ scale loaders (one CTA) ------------------------------
     // Per stage: 128 left-operand rows and bn right-operand columns, four scale bytes each, packed into one
-    // 32-bit word at its place in the 512-byte chunk of its 128 rows.  The four loader warps take K blocks in
-    // turn, so each has four MMA periods for the memory latency of its stage.
-    const int lw = warp - 6;   // 0 .. 3
+    // 32-bit word at its place in the 512-byte chunk of its 128 rows.  The blocks go to a ring of their own, with more
+    // slots than the operands have stages: the loader warps take K blocks in turn and run up to a ring ahead of the
+    // MMAs, which hides the latency of their loads (about 2000 cycles under the operand traffic).  A warp's K blocks
+    // lie kMxScaleWarps <= kMxSfSlots apart, so it is never more than one refill of a slot ahead and the slot's
+    // phases stay distinguishable.
+    static_assert(kMxScaleWarps <= kMxSfSlots && (kMxScaleWarps & (kMxScaleWarps - 1)) == 0, "loader warps");
+    const uint32_t lw = static_cast<uint32_t>(warp - 6);   // 0 .. kMxScaleWarps - 1
     uint32_t it = 0;
-    uint32_t s = static_cast<uint32_t>(lw) % static_cast<uint32_t>(p.stages);          // stage of this warp's next K block
-    uint32_t round = static_cast<uint32_t>(lw) / static_cast<uint32_t>(p.stages);      // and how often it was refilled
+    uint32_t s = lw, round = 0;          // slot of this warp's next K block, and how often that slot was refilled
     bool ok = true;
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-      const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
+    for (int tile = unit0; tile < tiles && ok; tile += unit_step) {
+      int mt, nt;
+      tile_coords(tile, p.group_m, p.m_tiles, p.n_tiles, mt, nt);
       for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-        if ((it & 3u) != static_cast<uint32_t>(lw)) continue;
+        if ((it & static_cast<uint32_t>(kMxScaleWarps - 1)) != lw) continue;
         const int g0 = kb * 4;
-        const int row0 = mt * 128, col0 = nt * p.bn;
+        const int row0 = mt * kTileM + my_row0, col0 = nt * p.bn;
         // Loads first (they do not touch the stage), then the wait for the stage, then the stores.  A lane ends up
         // with up to four left-operand words (rows ar[i]) and eight right-operand words (columns bc[i]); word =
         // the four E8M0 codes of the K block, code g in byte g.
@@ -393,12 +505,12 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             wb[j] = w;
           }
         }
-        if (!mbar_wait_warp(&empty[s], (round & 1u) ^ 1u)) {
+        if (!mbar_wait_warp(&sf_empty[s], (round & 1u) ^ 1u)) {
           report_error(p.err, kErrBarrierTimeout, 75, static_cast<int>(it));
           ok = false;
           break;
         }
-        uint8_t* sf = smem + static_cast<size_t>(s) * stage_bytes + a_bytes + b_bytes;
+        uint8_t* sf = sf_ring + s * sf_bytes;
         // row (or column) r of a 128-row chunk sits at byte (r % 32) * 16 + (r / 32) * 4 of the chunk; the left
         // operand's chunk comes first, the right operand's chunks (128 columns each) follow
 #pragma unroll
@@ -412,18 +524,84 @@ matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
         fence_proxy_async_smem();   // the chunk is read by tcgen05.cp (async proxy)
         __syncwarp();
-        if (lane == 0) mbar_arrive(&full[s]);
-        s += 4;                     // this warp's next K block is four further on
-        while (s >= static_cast<uint32_t>(p.stages)) {
-          s -= static_cast<uint32_t>(p.stages);
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_peer(mapa_u32(smem_u32(&sf_full[s]), 0));
+          else mbar_arrive(&sf_full[s]);
+        }
+        s += kMxScaleWarps;
+        if (s >= kMxSfSlots) {
+          s -= kMxSfSlots;
           ++round;
         }
       }
     }
   }
   tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+  if constexpr (PAIR) {
+    cluster_sync_all();   // neither CTA leaves, or frees tensor memory, while its partner may still signal or read it
+    if (warp == 1) tmem_dealloc_pair(tmem_base, tmem_cols);
+  } else {
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+__global__ void __launch_bounds__(kMxThreads, 1)
+matmul_mx_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const MxParams p) {
+  matmul_mx_body<false>(&tm_a, &tm_b, nullptr, nullptr, p);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMxPairThreads, 1)
+matmul_mx_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                      const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
+                      const MxParams p) {
+  matmul_mx_body<true>(&tm_a, &tm_b, &tm_sfa, &tm_sfb, p);
+}
+
+// Scale blocks for the pair kernel, in the order the tensor core reads them: word (r % 32) * 4 + r / 32 of a
+// 512-byte chunk holds the four E8M0 codes of one K block for row (or column) r of the chunk's 128.
+//   sfa: one chunk per (group of 128 rows of a, K block);   sfb: ceil(bn / 128) chunks per (tile column, K block),
+// columns counted from the tile's first.  Codes outside the matrix, or past the tile's width, are 127 (= 1.0).
+__global__ void __launch_bounds__(256)
+mx_pack_scales_kernel(const MxParams p, uint32_t* __restrict__ sfa, uint32_t* __restrict__ sfb, int a_groups) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int chunks = (p.bn + 127) / 128;
+  const long long a_words = static_cast<long long>(a_groups) * p.kblocks * 128;
+  const long long b_words = static_cast<long long>(p.n_tiles) * p.kblocks * 128 * chunks;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < a_words + b_words; i += gridDim.x * 256ll) {
+    const bool left = i < a_words;
+    const long long j = left ? i : i - a_words;
+    const int w = static_cast<int>(j & 127);
+    const int r = (w & 3) * 32 + (w >> 2);
+    long long blk = j >> 7;
+    int c = 0;
+    if (!left) {
+      c = static_cast<int>(blk % chunks);
+      blk /= chunks;
+    }
+    const int kb = static_cast<int>(blk % p.kblocks), outer = static_cast<int>(blk / p.kblocks);
+    const int g0 = kb * 4;
+    uint32_t word = 0;
+    if (left) {
+      const int row = outer * 128 + r;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const uint32_t code = __ldg(a_scale_ptr(p, row, g0 + g));
+        word |= ((row < p.m && g0 + g < p.kgroups) ? code : 127u) << (8 * g);
+      }
+      sfa[j] = word;
+    } else {
+      const int cin = c * 128 + r, col = outer * p.bn + cin;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const uint32_t code = __ldg(b_scale_ptr(p, col, g0 + g));
+        word |= ((cin < p.bn && col < p.n && g0 + g < p.kgroups) ? code : 127u) << (8 * g);
+      }
+      sfb[j] = word;
+    }
+  }
 }
 
 // dst[c, r] = src[r, c], bytes; 32 x 32 tiles through shared memory.
@@ -478,20 +656,34 @@ int matmul_mx_launch(const void* a, const void* a_scale, int a_scale_layout, con
   p.kblocks = (k + kMxBK - 1) / kMxBK;
   // 256-column tiles halve the left-operand traffic per FLOP; they pay once the problem has many tiles
   const long long tiles128 = static_cast<long long>((m + 127) / 128) * ((n + 127) / 128);
-  p.bn = (n >= 256 && tiles128 >= 4ll * sm_count()) ? 256 : 128;
-  p.nbuf = p.bn == 128 ? 2 : 1;
-  p.m_tiles = (m + 127) / 128;
+  // SM pairs (256 x 224 tiles, two accumulators) once every pair has at least two tiles and K is long enough for the
+  // kernel that packs the scale blocks to be small beside the matmul
+  static const int pair_enabled = [] { const char* v = getenv("PTO_MX_PAIR"); return v ? atoi(v) : 1; }();
+  const bool pair = pair_enabled && m >= 512 && n >= 448 && k >= 1024 &&
+                    static_cast<long long>((m + 255) / 256) * ((n + 223) / 224) >= sm_count();
+  if (pair) {
+    p.bn = 224;
+    p.nbuf = 2;
+    p.m_tiles = (m + 255) / 256;
+  } else {
+    p.bn = (n >= 256 && tiles128 >= 4ll * sm_count()) ? 256 : 128;
+    p.nbuf = p.bn == 128 ? 2 : 1;
+    p.m_tiles = (m + 127) / 128;
+  }
   p.n_tiles = (n + p.bn - 1) / p.bn;
+  p.group_m = 16;   // 2048 (one CTA) or 4096 (pairs) rows of a per group; measured 4 / 8 / 16 / all rows
   p.a_scale = static_cast<const uint8_t*>(a_scale); p.b_scale = static_cast<const uint8_t*>(b_scale);
   p.a_layout = a_scale_layout; p.b_layout = b_scale_layout;
   p.acc_in = acc_in; p.out = out; p.err = err;
-  const size_t sf_bytes = 512 * (1 + p.bn / 128);
-  const size_t stage_bytes = static_cast<size_t>(128 + p.bn) * kMxBK + 1024 * ((sf_bytes + 1023) / 1024);
-  int stages = static_cast<int>((210 * 1024) / stage_bytes);
+  const size_t sf_bytes = 512 * (1 + (p.bn + 127) / 128);
+  const int b_box_rows = pair ? p.bn / 2 : 128;   // a CTA of a pair loads its half of the b_t tile with one box
+  const size_t stage_bytes = static_cast<size_t>(128 + (pair ? p.bn / 2 : p.bn)) * kMxBK + (pair ? 1024 * ((sf_bytes + 1023) / 1024) : 0);
+  const size_t fixed_bytes = 1024 + (pair ? 0 : kMxSfSlots * sf_bytes) + (2 * kMxMaxStages + 5 + 2 * kMxSfSlots) * 8 + 16;
+  int stages = static_cast<int>((227 * 1024 - fixed_bytes) / stage_bytes);
   if (stages > kMxMaxStages) stages = kMxMaxStages;
   PTO_REQUIRE(stages >= 2, "matmul_mx: shared memory does not fit two pipeline stages");
   p.stages = stages;
-  const size_t smem = 1024 + stages * stage_bytes + (2 * kMxMaxStages + 5) * 8 + 16;
+  const size_t smem = fixed_bytes + stages * stage_bytes;
   const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
   PTO_REQUIRE(tiles < (1ll << 31), "matmul_mx: problem too large");
 
@@ -499,9 +691,50 @@ int matmul_mx_launch(const void* a, const void* a_scale, int a_scale_layout, con
   int st = make_tensor_map_2d(&tm_a, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, m, k, k, kMxBK, 128,
                               CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != kOk) return st;
-  st = make_tensor_map_2d(&tm_b, b_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k, k, kMxBK, 128,
+  st = make_tensor_map_2d(&tm_b, b_t, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, n, k, k, kMxBK, b_box_rows,
                           CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != kOk) return st;
+  if (pair) {
+    // Scale blocks in the tensor core's order, built by a small kernel into stream-ordered scratch memory (1/32 of
+    // the operands' bytes) and fetched by TMA like the operands.
+    const int chunks = (p.bn + 127) / 128, a_groups = 2 * p.m_tiles;
+    const size_t sfa_bytes = static_cast<size_t>(a_groups) * p.kblocks * 512;
+    const size_t sfb_bytes = static_cast<size_t>(p.n_tiles) * p.kblocks * 512 * chunks;
+    void* scratch = nullptr;
+    PTO_CUDA(cudaMallocAsync(&scratch, sfa_bytes + sfb_bytes, stream));
+    uint32_t* sfa = static_cast<uint32_t*>(scratch);
+    uint32_t* sfb = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + sfa_bytes);
+    CUtensorMap tm_sfa, tm_sfb;
+    st = make_tensor_map_2d(&tm_sfa, sfa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, static_cast<uint64_t>(a_groups) * p.kblocks, 128, 512,
+                            128, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (st == kOk)
+      st = make_tensor_map_2d(&tm_sfb, sfb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, static_cast<uint64_t>(p.n_tiles) * p.kblocks,
+                              128 * chunks, 512 * chunks, 128 * chunks, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (st != kOk) {
+      cudaFreeAsync(scratch, stream);
+      return st;
+    }
+    const long long words = static_cast<long long>(sfa_bytes + sfb_bytes) / 4;
+    const long long pack_cap = static_cast<long long>(sm_count()) * 8;
+    const long long pack_blocks = (words + 255) / 256;
+    launch_kernel(mx_pack_scales_kernel, dim3(static_cast<unsigned>(pack_blocks < pack_cap ? pack_blocks : pack_cap)), dim3(256), 0,
+                  stream, p, sfa, sfb, a_groups);
+    if (first_use_on_device(6))
+      PTO_CUDA(cudaFuncSetAttribute(matmul_mx_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    int pairs = sm_count() / 2;
+    if (pairs > tiles) pairs = static_cast<int>(tiles);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(kMxPairThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = nullptr;      // the cluster shape is a compile-time attribute of the kernel
+    cfg.numAttrs = 0;
+    const cudaError_t launched = cudaLaunchKernelEx(&cfg, matmul_mx_pair_kernel, tm_a, tm_b, tm_sfa, tm_sfb, p);
+    cudaFreeAsync(scratch, stream);   // in stream order: after the kernel
+    PTO_CUDA(launched);
+    return check_cuda(cudaGetLastError(), "matmul_mx_pair_kernel launch");
+  }
   if (first_use_on_device(2))
     PTO_CUDA(cudaFuncSetAttribute(matmul_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());

@@ -37,10 +37,12 @@ def test_reference_known_answer_case_is_exact_in_both_scale_layouts(golden):
     assert torch.equal(inplace.cpu(), t["out_acc"])
 
 
-@pytest.mark.parametrize("m,n,k", [(64, 128, 128), (200, 384, 352), (129, 130, 32), (1, 128, 1024), (4096, 4096, 512)])
+@pytest.mark.parametrize("m,n,k", [(64, 128, 128), (200, 384, 352), (129, 130, 32), (1, 128, 1024), (4096, 4096, 512),
+                                   (2100, 4232, 1056)])
 def test_integer_operands_are_exact_at_ragged_and_large_shapes(m, n, k):
     """Same recipe as the reference's case at other shapes: row/column/K tails (TMA zero fill, neutral scale
-    codes outside the matrix), many tiles per CTA, and the 256-column tile of large problems."""
+    codes outside the matrix), many tiles per CTA, and the 256 x 224 tiles that large problems with K >= 1024
+    run on SM pairs (the last shape has tails in all three dimensions there)."""
     ops = _ops()
     g = torch.Generator().manual_seed(m * 7 + n * 3 + k)
     a = torch.randint(-2, 3, (m, k), generator=g).to(FP8)
@@ -55,7 +57,7 @@ def test_integer_operands_are_exact_at_ragged_and_large_shapes(m, n, k):
     assert torch.equal(out.cpu(), exp)
 
 
-@pytest.mark.parametrize("m,n,k", [(256, 512, 512), (144, 272, 256), (4096, 2048, 1024)])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 512), (144, 272, 256), (4096, 2048, 1024), (2064, 4240, 1024)])
 def test_physical_scale_layouts_are_exact_at_larger_shapes(m, n, k):
     """The reference's packed scale layouts (MX_A_ZZ, MX_B_NN; test_matmul_mx.py:38-117) on tiles that lie inside the
     matrix (wide scale loads) and on tiles with row and column tails (byte loads), against the same golden."""
