@@ -84,18 +84,6 @@ __device__ __forceinline__ const uint8_t* b_scale_ptr(const MxParams& p, int col
   return p.b_scale + static_cast<size_t>(g) * p.n + col;
 }
 
-// Order of the tiles: groups of `group_m` tile rows, and within a group column after column.  The CTAs work on
-// neighbouring tile numbers at the same time, so what they read together is a block of about group_m tile rows by
-// (CTAs / group_m) tile columns: the group's rows of a stay in L2 while b_t streams through once per group, and
-// every line is fetched by many CTAs close together in time.
-__device__ __forceinline__ void tile_coords(int tile, int group_m, int m_tiles, int n_tiles, int& mt, int& nt) {
-  const int per_group = group_m * n_tiles;
-  const int g = tile / per_group, r = tile - g * per_group;
-  const int rows = min(group_m, m_tiles - g * group_m);
-  nt = r / rows;
-  mt = g * group_m + (r - nt * rows);
-}
-
 // Shared-memory descriptor of one 512-byte scale chunk for tcgen05.cp: 32 rows of 16 bytes, no swizzle,
 // 8-row groups 128 bytes apart.
 __device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
@@ -213,7 +201,7 @@ __device__ __forceinline__ void matmul_mx_body(const CUtensorMap* tm_a, const CU
     bool ok = true;
     for (int tile = unit0; tile < tiles && ok; tile += unit_step) {
       int mt, nt;
-      tile_coords(tile, p.group_m, p.m_tiles, p.n_tiles, mt, nt);
+      grouped_tile_coords(tile, p.group_m, p.m_tiles, p.n_tiles, mt, nt);
       for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
         if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u))) {
           if (lane == 0) report_error(p.err, kErrBarrierTimeout, 70, static_cast<int>(it));
@@ -334,7 +322,7 @@ __device__ __forceinline__ void matmul_mx_body(const CUtensorMap* tm_a, const CU
     }
     for (int tile = unit0; tile < tiles; tile += unit_step, ++ui) {
       int mt, nt;
-      tile_coords(tile, p.group_m, p.m_tiles, p.n_tiles, mt, nt);
+      grouped_tile_coords(tile, p.group_m, p.m_tiles, p.n_tiles, mt, nt);
       const uint32_t ab = ui % p.nbuf;
       if (!mbar_wait_warp(&tmem_full[ab], (ui / p.nbuf) & 1u)) {
         report_error(p.err, kErrBarrierTimeout, 73, static_cast<int>(ui));
@@ -389,7 +377,7 @@ __device__ __forceinline__ void matmul_mx_body(const CUtensorMap* tm_a, const CU
     bool ok = true;
     for (int tile = unit0; tile < tiles && ok; tile += unit_step) {
       int mt, nt;
-      tile_coords(tile, p.group_m, p.m_tiles, p.n_tiles, mt, nt);
+      grouped_tile_coords(tile, p.group_m, p.m_tiles, p.n_tiles, mt, nt);
       for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
         if ((it & static_cast<uint32_t>(kMxScaleWarps - 1)) != lw) continue;
         const int g0 = kb * 4;

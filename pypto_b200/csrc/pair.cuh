@@ -63,4 +63,16 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 
+// Order of the output tiles of a persistent GEMM: groups of `group` tile rows, and within a group column after
+// column.  The CTAs (or pairs) work on neighbouring tile numbers at the same time, so what they read together is a
+// block of about `group` tile rows by (CTAs / group) tile columns instead of one tile row by all CTAs' columns: each
+// line of either operand is fetched by many CTAs close together in time and far fewer bytes come from DRAM.
+__device__ __forceinline__ void grouped_tile_coords(int tile, int group, int row_tiles, int col_tiles, int& rt, int& ct) {
+  const int per_group = group * col_tiles;
+  const int g = tile / per_group, r = tile - g * per_group;
+  const int rows = min(group, row_tiles - g * group);
+  ct = r / rows;
+  rt = g * group + (r - ct * rows);
+}
+
 }  // namespace pto
