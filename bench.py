@@ -69,7 +69,8 @@ NCU_TRAFFIC = {"decode": 1406460304,            # pa_decode_kernel<1>
                "ffn": 26022144,                 # ffn_fused_kernel at M = 128 (the weights, read once)
                "layer": 240724480 + 6793216,    # gate/up gemm_bf16_kernel launch of the layer
                "moe": (488558848 + 9664768) * 16,   # gate/up moe_gemm_fp8_kernel, 16-expert capture x 16
-               "matmul_mx": 990629632 + 253626880}  # matmul_mx_kernel at 8192^3
+               "matmul_mx": 260926464 + 238253312 + 4204032,    # matmul_mx_pair_kernel + mx_pack_scales_kernel at 8192^3
+               "matmul_mx_one_cta": 359288320 + 232929024}     # matmul_mx_kernel (PTO_MX_PAIR=0) at 8192^3
 # pa_decode_kernel<2> on `--workload verify --small` (batch 16): DRAM bytes per byte of K/V that the step reads
 VERIFY_TRAFFIC_PER_KV_BYTE = (1222118000 + 12380416) / 1215746048
 
@@ -816,9 +817,8 @@ def run_matmul_mx(args, d: Dist):
                 launches=steps * (2 if pair else 1), clocks=clocks,
                 roofline={"bound": "tensor", "achieved": flops / t_rank / 1e12, "peak": fp8, "unit": "TFLOP/s",
                           "frac": flops / t_rank / 1e12 / fp8 if fp8 else None,
-                          "traffic": None if pair else NCU_TRAFFIC["matmul_mx"],
-                          "traffic_note": ("the profiler does not list kernels launched as clusters; the one-CTA kernel "
-                                           f"(PTO_MX_PAIR=0) moved {NCU_TRAFFIC['matmul_mx']} bytes at 8192^3") if pair else None,
+                          "traffic": (NCU_TRAFFIC["matmul_mx"] if pair else NCU_TRAFFIC["matmul_mx_one_cta"])
+                          if (m, n, k) == (MX["m"], MX["n"], MX["k"]) else None,
                           "peak_source": "measured here: torch._scaled_mm e4m3 8192^3, best of 10",
                           "note": "2*m*n*k / CUDA-event time of the call: mx_pack_scales_kernel + matmul_mx_pair_kernel"
                                   if pair else "2*m*n*k / CUDA-event time of matmul_mx_kernel"},

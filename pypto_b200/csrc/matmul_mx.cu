@@ -551,43 +551,44 @@ matmul_mx_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 // 512-byte chunk holds the four E8M0 codes of one K block for row (or column) r of the chunk's 128.
 //   sfa: one chunk per (group of 128 rows of a, K block);   sfb: ceil(bn / 128) chunks per (tile column, K block),
 // columns counted from the tile's first.  Codes outside the matrix, or past the tile's width, are 127 (= 1.0).
+// One 512-byte chunk per group of 128 threads; thread t takes row (or column) t of the chunk, so the loads of the
+// logical right-operand layout are contiguous over the threads.
 __global__ void __launch_bounds__(256)
 mx_pack_scales_kernel(const MxParams p, uint32_t* __restrict__ sfa, uint32_t* __restrict__ sfb, int a_groups) {
   pdl_launch_dependents();
   pdl_wait();
-  const int chunks = (p.bn + 127) / 128;
-  const long long a_words = static_cast<long long>(a_groups) * p.kblocks * 128;
-  const long long b_words = static_cast<long long>(p.n_tiles) * p.kblocks * 128 * chunks;
-  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < a_words + b_words; i += gridDim.x * 256ll) {
-    const bool left = i < a_words;
-    const long long j = left ? i : i - a_words;
-    const int w = static_cast<int>(j & 127);
-    const int r = (w & 3) * 32 + (w >> 2);
-    long long blk = j >> 7;
-    int c = 0;
-    if (!left) {
-      c = static_cast<int>(blk % chunks);
-      blk /= chunks;
-    }
-    const int kb = static_cast<int>(blk % p.kblocks), outer = static_cast<int>(blk / p.kblocks);
-    const int g0 = kb * 4;
+  const unsigned chunks = (p.bn + 127) / 128, kblocks = p.kblocks;
+  const unsigned a_chunks = static_cast<unsigned>(a_groups) * kblocks;
+  const unsigned all_chunks = a_chunks + static_cast<unsigned>(p.n_tiles) * kblocks * chunks;
+  const unsigned r = threadIdx.x & 127;
+  const bool k4 = (p.kgroups & 3) == 0;
+  const bool a_words = p.a_layout == PTO_MX_SCALE_LOGICAL && k4 && (reinterpret_cast<uintptr_t>(p.a_scale) & 3) == 0;
+  for (unsigned ch = blockIdx.x * 2 + (threadIdx.x >> 7); ch < all_chunks; ch += gridDim.x * 2) {
     uint32_t word = 0;
-    if (left) {
-      const int row = outer * 128 + r;
+    if (ch < a_chunks) {
+      const unsigned outer = ch / kblocks, kb = ch - outer * kblocks;
+      const int row = static_cast<int>(outer * 128 + r), g0 = static_cast<int>(kb * 4);
+      if (a_words && row < p.m && g0 + 4 <= p.kgroups) {   // the four codes of a row are one aligned word
+        word = __ldg(reinterpret_cast<const uint32_t*>(p.a_scale + static_cast<size_t>(row) * p.kgroups + g0));
+      } else {
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const uint32_t code = __ldg(a_scale_ptr(p, row, g0 + g));
-        word |= ((row < p.m && g0 + g < p.kgroups) ? code : 127u) << (8 * g);
+        for (int g = 0; g < 4; ++g) {
+          const uint32_t code = __ldg(a_scale_ptr(p, row, g0 + g));
+          word |= ((row < p.m && g0 + g < p.kgroups) ? code : 127u) << (8 * g);
+        }
       }
-      sfa[j] = word;
+      sfa[static_cast<size_t>(ch) * 128 + (r & 31) * 4 + (r >> 5)] = word;
     } else {
-      const int cin = c * 128 + r, col = outer * p.bn + cin;
+      const unsigned j = ch - a_chunks;
+      const unsigned blk = j / chunks, c = j - blk * chunks;
+      const unsigned outer = blk / kblocks, kb = blk - outer * kblocks;
+      const int cin = static_cast<int>(c * 128 + r), col = static_cast<int>(outer) * p.bn + cin, g0 = static_cast<int>(kb * 4);
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         const uint32_t code = __ldg(b_scale_ptr(p, col, g0 + g));
         word |= ((cin < p.bn && col < p.n && g0 + g < p.kgroups) ? code : 127u) << (8 * g);
       }
-      sfb[j] = word;
+      sfb[static_cast<size_t>(j) * 128 + (r & 31) * 4 + (r >> 5)] = word;
     }
   }
 }
@@ -702,9 +703,10 @@ int matmul_mx_launch(const void* a, const void* a_scale, int a_scale_layout, con
       cudaFreeAsync(scratch, stream);
       return st;
     }
-    const long long words = static_cast<long long>(sfa_bytes + sfb_bytes) / 4;
+    const long long pack_chunks = static_cast<long long>(sfa_bytes + sfb_bytes) / 512;
+    PTO_REQUIRE(pack_chunks < (1ll << 31), "matmul_mx: problem too large");
     const long long pack_cap = static_cast<long long>(sm_count()) * 8;
-    const long long pack_blocks = (words + 255) / 256;
+    const long long pack_blocks = (pack_chunks + 1) / 2;
     launch_kernel(mx_pack_scales_kernel, dim3(static_cast<unsigned>(pack_blocks < pack_cap ? pack_blocks : pack_cap)), dim3(256), 0,
                   stream, p, sfa, sfb, a_groups);
     if (first_use_on_device(6))
