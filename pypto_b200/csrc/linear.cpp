@@ -96,6 +96,9 @@ int ffn_swiglu_launch(const void* x, const void* w_gate_up, const void* w_down, 
   int st;
   int bn = 0;
   if (use_swiglu_epilogue(m, inter, &bn)) {
+    // 128 features per tile put the GEMM on SM pairs (256 x 256 tiles of [gate | up]) when the problem is large enough:
+    // a pair moves two thirds of the bytes per FLOP of single CTAs, which outweighs a less even last wave
+    if (inter % 128 == 0 && gemm2_eligible(m, inter, k, kGemmEpiSwiglu, 0, 128, 1)) bn = 128;
     // activations on the TMEM lanes (rows past m are zero filled by TMA), gate and up weight
     // tiles side by side as one MMA N; SiLU(gate) * up in the epilogue, no intermediate in HBM
     st = gemm_bf16_launch(x, m, w_gate_up, 2 * inter, inter, k, act, inter, 1, 0, kGemmEpiSwiglu, inter, bn, 1, err,
