@@ -362,7 +362,12 @@ PTO_API int pto_moe_combine(const void* rows, const int32_t* pos, const void* sh
  *              the physical orders the reference hands its kernel (test_matmul_mx.py:38-101;
  *              these need m, n multiples of 16 and k/32 even)
  *   acc_in     fp32 [m, n] added to the product (matmul_mx_acc), or NULL; may alias out
- *   out        fp32 [m, n] */
+ *   out        fp32 [m, n]
+ * Large problems (m >= 512, n >= 448, k >= 1024, at least two 256 x 224 tiles per pair of SMs) run on SM pairs;
+ * that path first rewrites the scale codes in the tensor core's order into scratch memory of (m + n) * k / 32 bytes
+ * (rounded up to whole tiles) taken from the device's stream-ordered pool (cudaMallocAsync / cudaFreeAsync on
+ * `stream`, no synchronisation; capturable in a graph).  Environment: PTO_MX_PAIR=0 keeps every problem on the
+ * one-CTA kernel, which allocates nothing. */
 enum { PTO_MX_SCALE_LOGICAL = 0, PTO_MX_SCALE_A_ZZ = 1, PTO_MX_SCALE_B_NN = 2 };
 PTO_API int pto_matmul_mx(const void* a, const void* a_scale, int a_scale_layout, const void* b_t,
                           const void* b_scale, int b_scale_layout, const float* acc_in, float* out, int m, int n,
