@@ -18,7 +18,9 @@ namespace {
 
 constexpr int kMaxExpertsPerLane = 32;  // up to 1024 experts per token row
 
-// One warp per token.  scores_in holds logits (is_logits = 1: sigmoid applied here) or scores.
+// One warp per token.  scores_in holds logits (is_logits = 1: sigmoid applied here) or scores.  PER = experts a lane
+// holds (ceil(experts / 32) rounded up to a power of two): the selection loops are unrolled over exactly those.
+template <int PER>
 __global__ void __launch_bounds__(256)
 moe_topk_kernel(const float* __restrict__ scores_in, const float* __restrict__ bias, int is_logits, int tokens,
                 int experts, int topk, int32_t* __restrict__ idx_out, float* __restrict__ w_out) {
@@ -27,20 +29,17 @@ moe_topk_kernel(const float* __restrict__ scores_in, const float* __restrict__ b
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= tokens) return;
-  float s[kMaxExpertsPerLane], sel[kMaxExpertsPerLane];
-  const int per = (experts + 31) / 32;
+  float s[PER], sel[PER];
 #pragma unroll
-  for (int j = 0; j < kMaxExpertsPerLane; ++j) {
+  for (int j = 0; j < PER; ++j) {
     s[j] = 0.f;
     sel[j] = -INFINITY;
-    if (j < per) {
-      const int e = j * 32 + lane;
-      if (e < experts) {
-        float v = scores_in[static_cast<size_t>(t) * experts + e];
-        if (is_logits) v = 1.f / (1.f + expf(-v));
-        s[j] = v;
-        sel[j] = v + (bias ? bias[e] : 0.f);
-      }
+    const int e = j * 32 + lane;
+    if (e < experts) {
+      float v = scores_in[static_cast<size_t>(t) * experts + e];
+      if (is_logits) v = 1.f / (1.f + expf(-v));
+      s[j] = v;
+      sel[j] = v + (bias ? bias[e] : 0.f);
     }
   }
   float picked_sum = 0.f, my_pick = 0.f;
@@ -49,11 +48,9 @@ moe_topk_kernel(const float* __restrict__ scores_in, const float* __restrict__ b
     float best = -INFINITY;
     int best_e = 0x7fffffff;
 #pragma unroll
-    for (int j = 0; j < kMaxExpertsPerLane; ++j) {
-      if (j < per) {
-        const int e = j * 32 + lane;
-        if (sel[j] > best) { best = sel[j]; best_e = e; }  // ascending e per lane: ties keep the lower id
-      }
+    for (int j = 0; j < PER; ++j) {
+      const int e = j * 32 + lane;
+      if (sel[j] > best) { best = sel[j]; best_e = e; }  // ascending e per lane: ties keep the lower id
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -64,7 +61,7 @@ moe_topk_kernel(const float* __restrict__ scores_in, const float* __restrict__ b
     const int owner = best_e & 31, slot = best_e >> 5;
     float sc = 0.f;
 #pragma unroll
-    for (int j = 0; j < kMaxExpertsPerLane; ++j)
+    for (int j = 0; j < PER; ++j)
       if (j == slot && lane == owner) { sc = s[j]; sel[j] = -INFINITY; }
     sc = __shfl_sync(0xffffffffu, sc, owner);
     picked_sum += sc;
@@ -76,38 +73,64 @@ moe_topk_kernel(const float* __restrict__ scores_in, const float* __restrict__ b
   }
 }
 
-// One warp per (row, 128-column group): scale = amax / 448 (1 if the group is all zero),
-// q = e4m3(x / scale), round to nearest even, saturating.
+// scale = amax / 448 over a (row, 128-column group) (1 if the group is all zero), q = e4m3(x / scale), round to
+// nearest even, saturating.  Sixteen lanes per group, eight elements per lane (16-byte loads of bf16), and four
+// pairs of groups in flight per warp: with one group per warp and scalar loads the kernel had 16 KB in flight per
+// SM and ran at a third of the HBM rate.
 template <typename TI>
 __global__ void __launch_bounds__(256)
 quantize_rows_kernel(const TI* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale, long long rows,
                      int cols) {
   pdl_launch_dependents();
   pdl_wait();
-  const int lane = threadIdx.x & 31;
+  constexpr int kU = 4;                                    // group pairs per warp and pass
+  const int lane = threadIdx.x & 31, half = lane >> 4, hl = lane & 15;
   const int groups = cols / 128;
   const long long total = rows * groups;
-  for (long long g = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); g < total;
-       g += static_cast<long long>(gridDim.x) * (blockDim.x >> 5)) {
-    const long long r = g / groups;
-    const int c0 = static_cast<int>(g - r * groups) * 128 + lane * 4;
-    const TI* src = x + r * cols + c0;
-    float v[4];
+  const long long warp_id = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  for (long long base = warp_id * (2 * kU); base < total; base += warps * (2 * kU)) {
+    float v[kU][8];
+    long long off[kU];
+    bool in[kU];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if constexpr (sizeof(TI) == 2) v[i] = __bfloat162float(src[i]); else v[i] = src[i];
+    for (int u = 0; u < kU; ++u) {
+      const long long g = base + 2 * u + half;
+      in[u] = g < total;
+      const long long r = in[u] ? g / groups : 0;
+      off[u] = in[u] ? r * cols + static_cast<long long>(g - r * groups) * 128 + hl * 8 : 0;
+      if constexpr (sizeof(TI) == 2) {
+        const uint4 w = in[u] ? __ldg(reinterpret_cast<const uint4*>(x + off[u])) : make_uint4(0, 0, 0, 0);
+        v[u][0] = bf16_lo_to_float(w.x); v[u][1] = bf16_hi_to_float(w.x);
+        v[u][2] = bf16_lo_to_float(w.y); v[u][3] = bf16_hi_to_float(w.y);
+        v[u][4] = bf16_lo_to_float(w.z); v[u][5] = bf16_hi_to_float(w.z);
+        v[u][6] = bf16_lo_to_float(w.w); v[u][7] = bf16_hi_to_float(w.w);
+      } else {
+        const float4 a = in[u] ? __ldg(reinterpret_cast<const float4*>(x + off[u])) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 b = in[u] ? __ldg(reinterpret_cast<const float4*>(x + off[u]) + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[u][0] = a.x; v[u][1] = a.y; v[u][2] = a.z; v[u][3] = a.w;
+        v[u][4] = b.x; v[u][5] = b.y; v[u][6] = b.z; v[u][7] = b.w;
+      }
     }
-    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-    amax = warp_max(amax);
-    const float sc = amax > 0.f ? amax / 448.f : 1.f;
-    uint32_t packed = 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(v[i] / sc, __NV_SATFINITE, __NV_E4M3);
-      packed |= static_cast<uint32_t>(b) << (8 * i);
+    for (int u = 0; u < kU; ++u) {
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[u][i]));
+#pragma unroll
+      for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // within 16 lanes
+      const float sc = amax > 0.f ? amax / 448.f : 1.f;
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        lo |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[u][i] / sc, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+        hi |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[u][4 + i] / sc, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+      }
+      if (in[u]) {
+        *reinterpret_cast<uint2*>(q + off[u]) = make_uint2(lo, hi);
+        if (hl == 0) scale[base + 2 * u + half] = sc;
+      }
     }
-    *reinterpret_cast<uint32_t*>(q + r * cols + c0) = packed;
-    if (lane == 0) scale[g] = sc;
   }
 }
 
@@ -172,10 +195,15 @@ __global__ void __launch_bounds__(1024) moe_offsets_kernel(int32_t* __restrict__
     const int i = base + threadIdx.x;
     int v = 0;
     if (i < n) {
-      for (int c = 0; c < n_chunks; ++c) {      // consecutive threads read consecutive buckets of a chunk
-        const int h = hist[static_cast<size_t>(c) * n + i];
-        hist[static_cast<size_t>(c) * n + i] = v;
-        v += h;
+      for (int c0 = 0; c0 < n_chunks; c0 += 8) {   // consecutive threads read consecutive buckets of a chunk;
+        int h[8];                                  // eight loads in flight before the stores that follow them
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[j] = c0 + j < n_chunks ? hist[static_cast<size_t>(c0 + j) * n + i] : 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (c0 + j < n_chunks) hist[static_cast<size_t>(c0 + j) * n + i] = v;
+          v += h[j];
+        }
       }
       counts[i] = v;
     }
@@ -331,7 +359,17 @@ moe_gather_rows_kernel(RowArrays a, const int32_t* __restrict__ src_row_of, int 
       if (!ok) {
         for (int c = lane; c < rb; c += 32) dp[c] = 0;
       } else if ((rb & 15) == 0 && ((reinterpret_cast<uintptr_t>(sp) | reinterpret_cast<uintptr_t>(dp)) & 15) == 0) {
-        for (int c = lane; c < rb / 16; c += 32) reinterpret_cast<uint4*>(dp)[c] = reinterpret_cast<const uint4*>(sp)[c];
+        // four loads in flight per lane before the first store: source and destination are plain byte pointers, so
+        // the compiler must keep every load behind the store before it
+        const uint4* s16 = reinterpret_cast<const uint4*>(sp);
+        uint4* d16 = reinterpret_cast<uint4*>(dp);
+        const int n16 = rb / 16;
+        int c = lane;
+        for (; c + 96 < n16; c += 128) {
+          const uint4 v0 = __ldg(s16 + c), v1 = __ldg(s16 + c + 32), v2 = __ldg(s16 + c + 64), v3 = __ldg(s16 + c + 96);
+          d16[c] = v0; d16[c + 32] = v1; d16[c + 64] = v2; d16[c + 96] = v3;
+        }
+        for (; c < n16; c += 32) d16[c] = __ldg(s16 + c);
       } else if ((rb & 3) == 0 && ((reinterpret_cast<uintptr_t>(sp) | reinterpret_cast<uintptr_t>(dp)) & 3) == 0) {
         for (int c = lane; c < rb / 4; c += 32) reinterpret_cast<uint32_t*>(dp)[c] = reinterpret_cast<const uint32_t*>(sp)[c];
       } else {
@@ -432,7 +470,16 @@ int moe_topk_launch(const float* scores, const float* bias, int is_logits, int t
   PTO_REQUIRE(experts > 0 && experts <= 32 * kMaxExpertsPerLane, "moe_topk: at most 1024 experts");
   PTO_REQUIRE(topk > 0 && topk <= 32 && topk <= experts, "moe_topk: 1 <= topk <= min(32, experts)");
   if (tokens <= 0) return kOk;
-  launch_kernel(moe_topk_kernel, dim3((tokens + 7) / 8), dim3(256), 0, stream, scores, bias, is_logits, tokens, experts, topk, idx, weights);
+  const int per = (experts + 31) / 32;
+  const dim3 grid((tokens + 7) / 8), block(256);
+#define PTO_TOPK(P) launch_kernel(moe_topk_kernel<P>, grid, block, 0, stream, scores, bias, is_logits, tokens, experts, topk, idx, weights)
+  if (per <= 1) PTO_TOPK(1);
+  else if (per <= 2) PTO_TOPK(2);
+  else if (per <= 4) PTO_TOPK(4);
+  else if (per <= 8) PTO_TOPK(8);
+  else if (per <= 16) PTO_TOPK(16);
+  else PTO_TOPK(32);
+#undef PTO_TOPK
   return check_cuda(cudaGetLastError(), "moe_topk_kernel launch");
 }
 
@@ -440,8 +487,10 @@ int quantize_rows_launch(const void* x, int x_dtype, void* q, float* scale, long
                          cudaStream_t stream) {
   PTO_REQUIRE(x && q && scale, "quantize_rows: NULL tensor");
   PTO_REQUIRE(cols > 0 && cols % 128 == 0, "quantize_rows: columns must be a multiple of 128");
+  PTO_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0,
+              "quantize_rows: x must be 16-byte aligned, q 8-byte aligned");
   if (rows <= 0) return kOk;
-  const int g = grid_rows(rows * (cols / 128), 8);
+  const int g = grid_rows((rows * (cols / 128) + 7) / 8, 8);     // a warp takes eight groups per pass
   if (x_dtype == PTO_BF16)
     launch_kernel(quantize_rows_kernel<__nv_bfloat16>, dim3(g), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), scale, rows, cols);
   else if (x_dtype == PTO_FP32)
