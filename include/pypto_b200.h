@@ -365,8 +365,8 @@ PTO_API int pto_moe_combine(const void* rows, const int32_t* pos, const void* sh
  *   out        fp32 [m, n]
  * Large problems (m >= 512, n >= 448, k >= 1024, at least two 256 x 224 tiles per pair of SMs) run on SM pairs;
  * that path first rewrites the scale codes in the tensor core's order into scratch memory of (m + n) * k / 32 bytes
- * (rounded up to whole tiles) taken from the device's stream-ordered pool (cudaMallocAsync / cudaFreeAsync on
- * `stream`, no synchronisation; capturable in a graph).  Environment: PTO_MX_PAIR=0 keeps every problem on the
+ * (rounded up to whole tiles) taken in stream order from a memory pool of the library's own (cudaMallocFromPoolAsync /
+ * cudaFreeAsync on `stream`, no synchronisation; capturable in a graph; the pool keeps its memory between calls).  Environment: PTO_MX_PAIR=0 keeps every problem on the
  * one-CTA kernel, which allocates nothing. */
 enum { PTO_MX_SCALE_LOGICAL = 0, PTO_MX_SCALE_A_ZZ = 1, PTO_MX_SCALE_B_NN = 2 };
 PTO_API int pto_matmul_mx(const void* a, const void* a_scale, int a_scale_layout, const void* b_t,

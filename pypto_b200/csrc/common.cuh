@@ -53,6 +53,10 @@ int sm_count();
 // True the first time it is called for (key, current device): function attributes such as the
 // dynamic shared-memory limit are per device and have to be set once on each.
 bool first_use_on_device(int key);
+// Stream-ordered scratch memory for a launcher that needs a work buffer it cannot ask its caller for: taken from a
+// pool of the library's own, handed back in stream order.  No synchronisation; capturable in a graph.
+int scratch_alloc_async(void** out, size_t bytes, cudaStream_t stream);
+int scratch_free_async(void* p, cudaStream_t stream);
 
 // Device error word layout (first 16 ints of every scratch buffer).
 //   [0] error code (0 = none), [1] where (site id), [2] blockIdx.x, [3] extra

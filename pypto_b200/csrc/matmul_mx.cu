@@ -690,7 +690,8 @@ int matmul_mx_launch(const void* a, const void* a_scale, int a_scale_layout, con
     const size_t sfa_bytes = static_cast<size_t>(a_groups) * p.kblocks * 512;
     const size_t sfb_bytes = static_cast<size_t>(p.n_tiles) * p.kblocks * 512 * chunks;
     void* scratch = nullptr;
-    PTO_CUDA(cudaMallocAsync(&scratch, sfa_bytes + sfb_bytes, stream));
+    st = scratch_alloc_async(&scratch, sfa_bytes + sfb_bytes, stream);
+    if (st != kOk) return st;
     uint32_t* sfa = static_cast<uint32_t*>(scratch);
     uint32_t* sfb = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + sfa_bytes);
     CUtensorMap tm_sfa, tm_sfb;
@@ -700,7 +701,7 @@ int matmul_mx_launch(const void* a, const void* a_scale, int a_scale_layout, con
       st = make_tensor_map_2d(&tm_sfb, sfb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, static_cast<uint64_t>(p.n_tiles) * p.kblocks,
                               128 * chunks, 512 * chunks, 128 * chunks, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (st != kOk) {
-      cudaFreeAsync(scratch, stream);
+      scratch_free_async(scratch, stream);
       return st;
     }
     const long long pack_chunks = static_cast<long long>(sfa_bytes + sfb_bytes) / 512;
@@ -721,7 +722,7 @@ int matmul_mx_launch(const void* a, const void* a_scale, int a_scale_layout, con
     cfg.attrs = nullptr;      // the cluster shape is a compile-time attribute of the kernel
     cfg.numAttrs = 0;
     const cudaError_t launched = cudaLaunchKernelEx(&cfg, matmul_mx_pair_kernel, tm_a, tm_b, tm_sfa, tm_sfb, p);
-    cudaFreeAsync(scratch, stream);   // in stream order: after the kernel
+    scratch_free_async(scratch, stream);   // in stream order: after the kernel
     PTO_CUDA(launched);
     return check_cuda(cudaGetLastError(), "matmul_mx_pair_kernel launch");
   }

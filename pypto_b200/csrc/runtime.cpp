@@ -75,6 +75,39 @@ bool first_use_on_device(int key) {
   return first;
 }
 
+// Stream-ordered scratch memory from a pool of the library's own (one per device).  The pool keeps what it has
+// been given (release threshold = everything): with the default threshold a pool hands its memory back to the driver
+// at every synchronisation, and the next call pays for mapping it again.
+int scratch_alloc_async(void** out, size_t bytes, cudaStream_t stream) {
+  static std::mutex mu;
+  static cudaMemPool_t pools[64] = {};
+  int dev = 0;
+  PTO_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(kInvalidArgument, "scratch_alloc_async: device ordinal out of range");
+  cudaMemPool_t pool;
+  {
+    std::lock_guard<std::mutex> g(mu);
+    if (pools[dev] == nullptr) {
+      cudaMemPoolProps props = {};
+      props.allocType = cudaMemAllocationTypePinned;
+      props.handleTypes = cudaMemHandleTypeNone;
+      props.location.type = cudaMemLocationTypeDevice;
+      props.location.id = dev;
+      PTO_CUDA(cudaMemPoolCreate(&pools[dev], &props));
+      unsigned long long keep = ~0ull;
+      PTO_CUDA(cudaMemPoolSetAttribute(pools[dev], cudaMemPoolAttrReleaseThreshold, &keep));
+    }
+    pool = pools[dev];
+  }
+  PTO_CUDA(cudaMallocFromPoolAsync(out, bytes, pool, stream));
+  return kOk;
+}
+
+int scratch_free_async(void* p, cudaStream_t stream) {
+  PTO_CUDA(cudaFreeAsync(p, stream));
+  return kOk;
+}
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
