@@ -177,6 +177,9 @@ def compile(program, *, output_dir=None, strategy=OptimizationStrategy.Default, 
         from ..runtime import extern_kernel
         fused = extern_kernel.match(entry, program if isinstance(program, Program) else None)
         if fused is None:
+            # a program under another name that computes what a fused operator computes
+            fused = fused_programs.from_idiom(entry, program if isinstance(program, Program) else None)
+        if fused is None:
             raise
     return CompiledProgram(entry, fused, platform, bt, program)
 

@@ -140,7 +140,16 @@ class FfnSwigluOp(FusedOp):
     op_names = ("ffn_swiglu",)
     names = ("hidden_states", "gate_proj_weight", "up_proj_weight", "down_proj_weight", "output")
 
+    def __init__(self, entry=None, names=None):
+        # entry + names: a program recognised by what it computes (ir/idioms.py); `names` are ITS parameters in the
+        # order x, gate weight, up weight, down weight, output
+        self.entry = entry
+        if names is not None:
+            self.names = tuple(names)
+
     def matches(self, entry) -> bool:
+        if self.entry is not None:
+            return entry is self.entry
         return entry.name == "ffn_swiglu" and tuple(p.name for p in entry.params) == self.names
 
     def plan(self, compiled, host, worker):
@@ -165,13 +174,30 @@ class RmsNormOp(FusedOp):
     op_names = ("rms_norm",)
     names = ("x", "gamma", "output")
     eps = 1e-5
+    inv_n = None
+
+    def __init__(self, entry=None, names=None, eps=None, inv_n=None):
+        # entry + names (+ constants): a program recognised by what it computes (ir/idioms.py); `names` are ITS
+        # parameters in the order x, gamma, output; inv_n is the constant it multiplies the row sums by
+        self.entry = entry
+        if names is not None:
+            self.names = tuple(names)
+        if eps is not None:
+            self.eps = float(eps)
+        self.inv_n = inv_n
 
     def matches(self, entry) -> bool:
+        if self.entry is not None:
+            return entry is self.entry
         return entry.name == "rms_norm" and tuple(p.name for p in entry.params) == self.names
 
     def plan(self, compiled, host, worker):
-        if host["gamma"].dtype != torch.float32:
+        x, gamma = host[self.names[0]], host[self.names[1]]
+        if gamma.dtype != torch.float32:
             raise TypeError("rms_norm: gamma must be float32")
+        if self.inv_n is not None and abs(self.inv_n * x.shape[-1] - 1.0) > 1e-6:
+            raise ValueError(f"rms_norm: the program scales the row sums by {self.inv_n}, which is not 1 / {x.shape[-1]} "
+                             "(the mean over the row the fused kernel computes)")
         return dict(scalars=[struct.unpack("I", struct.pack("f", self.eps))[0]])
 
     def launch(self, worker, dev, host, plan):
@@ -286,6 +312,21 @@ class LlamaMiniOp(FusedOp):
 
 REGISTRY: list[FusedOp] = [LlamaMiniOp(), PagedAttentionOp(), PagedAttentionSpmdOp(), PagedGatherOp(), FfnSwigluOp(), RmsNormOp(),
                            Qwen3DecodeOp(), Scope3Op(), MatmulMxOp()]
+
+
+def from_idiom(entry, program=None) -> FusedOp | None:
+    """A fused operator for a program that matches none by name but computes what one computes (ir/idioms.py):
+    the operator is bound to the program's own parameter names."""
+    from ..ir import idioms
+    rec = idioms.recognise(entry, program)
+    if rec is None:
+        return None
+    r = rec.roles
+    if rec.idiom == "ffn_swiglu":
+        return FfnSwigluOp(entry, (r["x"], r["w_gate"], r["w_up"], r["w_down"], r["out"]))
+    if rec.idiom == "rms_norm":
+        return RmsNormOp(entry, (r["x"], r["gamma"], r["out"]), eps=rec.constants.get("eps"), inv_n=rec.constants.get("inv_n"))
+    return None
 
 
 def lookup(entry) -> FusedOp:

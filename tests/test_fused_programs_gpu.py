@@ -72,3 +72,25 @@ def test_spmd_paged_attention_signature(golden):
                               torch.clamp(t["context_lens"], max=bs), num_heads=heads, head_dim=hd, block_size=bs,
                               scale=float(t["scale"][0]))
     validate_golden({"out": out2}, {"out": exp.reshape(out2.shape)}, rtol=2e-2, atol=4e-3)
+
+
+def test_programs_recognised_by_what_they_compute_run_on_the_fused_kernels():
+    """A gated MLP and a scaled norm under names, parameter orders and algebraic spellings of their own
+    (tests/dsl_programs/renamed_idioms.py): the idiom recogniser binds the fused operators' roles to their parameters."""
+    from tests.dsl_programs import renamed_idioms as progs
+    x, wg, wu, wd = oracle.inputs.ffn_inputs(128, 1024, 4096, seed=3)
+    y = torch.zeros(128, 1024)
+    progs.gated_mlp(wd, wu, x, wg, y)                     # (w_out, w_lin, tokens, w_act, y)
+    exp = offn.ffn_swiglu(x, wg, wu, wd)
+    assert (y - exp).abs().max() <= 2e-2 * exp.abs().max()
+    swapped = torch.zeros(128, 1024)
+    progs.gated_mlp(wd, wg, x, wu, swapped)               # gate and up exchanged: another function of the inputs
+    assert (swapped - offn.ffn_swiglu(x, wu, wg, wd)).abs().max() <= 2e-2 * exp.abs().max()
+    assert (swapped - exp).abs().max() > 0.1 * exp.abs().max()
+    torch.manual_seed(1)
+    rows, weight = torch.randn(32, 64), torch.randn(1, 64)
+    normed = torch.zeros_like(rows)
+    progs.scaled_norm(weight, rows, normed)
+    validate_golden({"normed": normed}, {"normed": olayer.rms_norm_sqrt_div(rows, weight, progs.EPS)}, rtol=1e-5, atol=1e-5)
+    with pytest.raises(ValueError, match="not 1 / 128"):
+        progs.scaled_norm(torch.randn(1, 128), torch.randn(32, 128), torch.zeros(32, 128))   # the program divides by 64

@@ -1,0 +1,83 @@
+"""CPU: the idiom recogniser (pypto_b200/ir/idioms.py) reads DSL bodies, never runs them, and binds the roles of a
+fused operator to a program's own parameter names by data flow."""
+
+import pytest
+
+from pypto_b200 import ir
+from pypto_b200.ir import idioms
+from pypto_b200.runtime import fused_programs
+from tests.dsl_programs import renamed_idioms as progs
+
+
+def test_swiglu_ffn_is_recognised_under_other_names_orders_and_spellings():
+    rec = idioms.recognise(progs.gated_mlp)
+    assert rec is not None and rec.idiom == "ffn_swiglu"
+    # the weight whose product goes through the sigmoid is the gate, wherever it stands in the signature
+    assert rec.roles == {"x": "tokens", "w_gate": "w_act", "w_up": "w_lin", "w_down": "w_out", "out": "y"}
+    op = fused_programs.from_idiom(progs.gated_mlp)
+    assert op.op_names == ("ffn_swiglu",) and op.names == ("tokens", "w_act", "w_lin", "w_out", "y")
+    assert op.matches(progs.gated_mlp) and not op.matches(progs.relu_mlp)
+
+
+def test_rms_norm_is_recognised_with_its_constants():
+    rec = idioms.recognise(progs.scaled_norm)
+    assert rec is not None and rec.idiom == "rms_norm"
+    assert rec.roles == {"x": "rows", "gamma": "weight", "out": "normed"}
+    assert rec.constants["eps"] == pytest.approx(progs.EPS) and rec.constants["inv_n"] == pytest.approx(1.0 / 64)
+    op = fused_programs.from_idiom(progs.scaled_norm)
+    assert op.eps == pytest.approx(progs.EPS) and op.names == ("rows", "weight", "normed")
+
+
+def test_what_is_not_an_idiom_is_refused():
+    assert idioms.recognise(progs.relu_mlp) is None          # same shape of program, another activation
+    assert idioms.recognise(progs.looped) is None            # a loop is not followed
+    with pytest.raises(NotImplementedError, match="no fused kernel registered"):
+        ir.compile(progs.relu_mlp, platform="b200")
+
+
+def test_compile_routes_a_recognised_program_to_the_fused_operator():
+    compiled = ir.compile(progs.gated_mlp, platform="b200")
+    assert compiled.op_names == ("ffn_swiglu",)
+    compiled = ir.compile(progs.scaled_norm, platform="b200")
+    assert compiled.op_names == ("rms_norm",)
+
+
+def test_algebra_is_canonical():
+    g, u = idioms.P("g"), idioms.P("u")
+    a = idioms.mul(idioms.mul(g, idioms.sigmoid(g)), u)
+    b = idioms.mul(u, idioms.mul(idioms.un("recip", idioms.add(idioms.un("exp", idioms.mul(g, idioms.C(-1))), idioms.C(1))), g))
+    assert a == b
+    assert idioms.add(idioms.C(1), idioms.C(2), g) == idioms.add(g, idioms.C(3))
+    assert idioms.mul(g, idioms.C(0)) == idioms.C(0)
+
+
+def test_the_reference_examples_are_recognised_by_their_bodies():
+    """examples/models/01_ffn.py and examples/intermediate/03_normalization.py, loaded unchanged through the ``pypto``
+    alias: the recogniser reads their kernels and finds the SwiGLU FFN and the RMSNorm without looking at names;
+    their GELU / ReLU FFNs and the layer norm are other computations and are refused."""
+    import importlib.util
+    import os
+
+    import ref_extract
+    if not ref_extract.available():
+        pytest.skip("reference tree not mounted")
+    from pypto_b200 import compat
+    compat.install()
+
+    def load(rel, name):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(ref_extract.REFERENCE_ROOT, rel))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod
+
+    ffn = load("examples/models/01_ffn.py", "ref_example_01_ffn")
+    rec = idioms.recognise(ffn.ffn_swiglu)
+    assert rec is not None and rec.idiom == "ffn_swiglu"
+    assert rec.roles == {"x": "hidden_states", "w_gate": "gate_proj_weight", "w_up": "up_proj_weight",
+                         "w_down": "down_proj_weight", "out": "output"}
+    assert idioms.recognise(ffn.ffn_gelu) is None and idioms.recognise(ffn.ffn_relu) is None
+    norm = load("examples/intermediate/03_normalization.py", "ref_example_03_norm")
+    rec = idioms.recognise(norm.rms_norm)
+    assert rec is not None and rec.idiom == "rms_norm" and rec.roles == {"x": "x", "gamma": "gamma", "out": "output"}
+    assert rec.constants["eps"] == pytest.approx(1e-5) and rec.constants["inv_n"] == pytest.approx(1.0 / 64)
+    assert idioms.recognise(norm.layer_norm) is None
