@@ -72,10 +72,12 @@ def test_physical_scale_layouts_are_exact_at_larger_shapes(m, n, k):
     out = ops.matmul_mx(a.cuda(), omx.pack_a_scale(sa).cuda(), b_t, omx.pack_b_scale(sb).cuda(),
                         a_scale_layout=ops.MX_SCALE_A_ZZ, b_scale_layout=ops.MX_SCALE_B_NN)
     mixed = ops.matmul_mx(a.cuda(), sa.cuda(), b_t, omx.pack_b_scale(sb).cuda(), b_scale_layout=ops.MX_SCALE_B_NN)
+    twice = ops.matmul_mx(a.cuda(), sa.cuda(), b_t, sb.cuda(), acc=out)        # matmul_mx_acc on the same tiles
     torch.cuda.synchronize()
     ops.check_device_status()
     assert torch.equal(out.cpu(), exp)
     assert torch.equal(mixed.cpu(), exp)
+    assert torch.equal(twice.cpu(), exp + exp)
 
 
 def test_quantised_gaussian_operands_match_the_fp64_golden():
