@@ -106,3 +106,38 @@ def test_moe_full_size_token_permutation_equivariance():
     assert rel < 2e-2, rel
     per_row = (got - y_exp).norm(dim=1) / y_exp.norm(dim=1)
     assert per_row.max() < 5e-2, per_row
+
+
+def test_matmul_mx_full_size_scale_shift_row_permutation_and_oracle_slab():
+    """The MXFP8 matmul at the benchmark's 8192^3 (SM pairs, 256 x 224 tiles, scale blocks packed and fetched by TMA):
+    (a) raising every scale code of `a` by one doubles the output exactly (a power of two, in every fp32 partial sum);
+    (b) permuting the rows of `a` and of its scales permutes the output rows bit for bit (every row is accumulated
+    in the same order whatever tile and whichever CTA of a pair it lands in);
+    (c) 128 rows spread over the matrix agree with the reference's golden (dequantise per group, fp64 product,
+    tests/st/runtime/ops/test_matmul_mx.py:119-131) to fp32 accumulation error."""
+    import bench
+    from oracle import matmul_mx as omx
+    from pypto_b200 import ops
+    m, n, k = bench.MX["m"], bench.MX["n"], bench.MX["k"]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev).manual_seed(11)
+    a = (torch.randn(m, k, device=dev, generator=gen) * 2).to(torch.float8_e4m3fn)
+    b_t = (torch.randn(n, k, device=dev, generator=gen) * 2).to(torch.float8_e4m3fn)
+    sa = torch.randint(120, 134, (m, k // 32), device=dev, generator=gen).to(torch.uint8)
+    sb = torch.randint(120, 134, (k // 32, n), device=dev, generator=gen).to(torch.uint8)
+    out = ops.matmul_mx(a, sa, b_t, sb)
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    assert torch.isfinite(out).all()
+    doubled = ops.matmul_mx(a, sa + 1, b_t, sb)
+    assert torch.equal(doubled, out * 2)
+    del doubled
+    perm = torch.randperm(m, device=dev, generator=gen)
+    permuted = ops.matmul_mx(a.view(torch.uint8)[perm].view(torch.float8_e4m3fn), sa[perm], b_t, sb)
+    assert torch.equal(permuted, out[perm])
+    del permuted
+    rows = torch.arange(0, m, m // 128, device=dev)[:128] + 37           # rows of both CTAs of many pairs
+    exp = omx.matmul_mx(a[rows].cpu(), sa[rows].cpu(),
+                        b_t.cpu().view(torch.uint8).t().contiguous().view(torch.float8_e4m3fn), sb.cpu())
+    rel = ((out[rows].cpu() - exp).norm() / exp.norm()).item()
+    assert rel < 1e-5, rel
