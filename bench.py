@@ -530,10 +530,11 @@ def run_ffn(args, d: Dist):
             for ms_ in (128, 512, 2048, 8192):
                 xs = torch.randn(ms_, k, device=d.dev).bfloat16()
                 o = torch.empty(ms_, k, dtype=torch.float32, device=d.dev)
-                j = [0]
+                reps = [graphed(lambda f=f: f(xs, out=o)) for f in ffns]   # graphs: eager launches would be timed
+                j = [0]                                                     # instead of the kernels at small M
 
                 def st():
-                    ffns[j[0] % copies](xs, out=o)
+                    reps[j[0] % copies]()
                     j[0] += 1
                 t = event_time(st, 20)
                 tf = offn.ffn_flops(ms_, k, inter) / t / 1e12

@@ -280,9 +280,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const long long o = static_cast<long long>(a_row) * p.ldo + b_row0;
             const bool full_row = b_row0 + 32 <= p.b_rows;
             if (p.epi == kGemmEpiAtomic) {
+              // a lane owns 32 neighbouring outputs of its row: vector reductions where the row segment is whole and
+              // aligned (scalar ones from 32 lanes hit 32 different lines per instruction)
+              float* dst = static_cast<float*>(p.out) + o;
+              if (full_row && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (b_row0 + j < p.b_rows) red_add_f32(static_cast<float*>(p.out) + o + j, __uint_as_float(v[j]));
+                for (int j = 0; j < 32; j += 4)
+                  red_add_f32x4(dst + j, __uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                __uint_as_float(v[j + 3]));
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (b_row0 + j < p.b_rows) red_add_f32(dst + j, __uint_as_float(v[j]));
+              }
             } else if (p.out_bf16) {
               __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + o;
               if (full_row && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {

@@ -29,10 +29,14 @@ int linear_launch(const void* x, const void* w_packed, float* out, int m, int n,
     if (!accumulate) PTO_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * static_cast<size_t>(m) * n, stream));
     return gemm_bf16_launch(w_packed, n, x, m, m, k, out, n, 0, 1, kGemmEpiAtomic, 0, bn, 1, err, stream);
   }
-  const int bn = n >= 256 ? 256 : 128;
+  int bn = n >= 256 ? 256 : 128;
   const int tiles = ((m + 127) / 128) * ((n + bn - 1) / bn);
   // few tiles: stream-K over (tile, K block) with the atomic epilogue keeps every SM busy
   const int epi = (accumulate || tiles < sm_count()) ? kGemmEpiAtomic : kGemmEpiStore;
+  // every CTA of a stream-K launch reduces one partial tile (or two) into the output: narrower tiles, fewer bytes of
+  // reductions (the tiles are few here, so the operand re-reads they cost stay in L2)
+  // (measured at n = 1024, K = 4096: 16 tiles 37 -> 33 us for the FFN it is part of, 64 tiles 60 -> 63 us)
+  if (epi == kGemmEpiAtomic && 4 * tiles <= sm_count()) bn = 128;
   if (epi == kGemmEpiAtomic && !accumulate)
     PTO_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * static_cast<size_t>(m) * n, stream));
   return gemm_bf16_launch(x, m, w_packed, n, n, k, out, n, 0, 0, epi, 0, bn, 1, err, stream);
