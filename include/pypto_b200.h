@@ -223,6 +223,14 @@ PTO_API size_t pto_ffn_swiglu_workspace_bytes(int m, int inter);
 PTO_API int pto_ffn_swiglu(const void* x, const void* w_gate_up, const void* w_down, void* out, int m, int k,
                            int inter, int n_out, void* workspace, size_t workspace_bytes, int accumulate,
                            int32_t* err, void* stream);
+/* The same with x in fp32 [m, k], the dtype of `ffn_swiglu`'s own inputs (examples/models/01_ffn.py:155-160): x is
+ * rounded to bf16 operands.  With at most 128 rows the one-launch kernel does that cast itself, each CTA its share,
+ * and clears the output when accumulate = 0: ONE launch for the whole operator.  The workspace
+ * (pto_ffn_swiglu_f32_workspace_bytes, 256-byte aligned, same rules as above) also holds the bf16 copy of x. */
+PTO_API size_t pto_ffn_swiglu_f32_workspace_bytes(int m, int k, int inter);
+PTO_API int pto_ffn_swiglu_f32(const float* x, const void* w_gate_up, const void* w_down, void* out, int m, int k,
+                               int inter, int n_out, void* workspace, size_t workspace_bytes, int accumulate,
+                               int32_t* err, void* stream);
 
 /* ---- decoder-layer glue ---- */
 

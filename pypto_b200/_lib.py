@@ -71,6 +71,8 @@ SIGNATURES = {
     "pto_linear": (_i, [_p, _p, _p, _i, _i, _i, _i, _p, _p]),
     "pto_ffn_swiglu_workspace_bytes": (_sz, [_i, _i]),
     "pto_ffn_swiglu": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p, _sz, _i, _p, _p]),
+    "pto_ffn_swiglu_f32_workspace_bytes": (_sz, [_i, _i, _i]),
+    "pto_ffn_swiglu_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p, _sz, _i, _p, _p]),
     "pto_rms_norm": (_i, [_p, _i, _p, _p, _i, _i64, _i, _f, _p]),
     "pto_rms_norm_ex": (_i, [_p, _i, _p, _p, _i, _i64, _i, _f, _p, _p, _sz, _p]),
     "pto_rope_kv_append": (_i, [_p, _p, _p, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i64, _p, _p]),

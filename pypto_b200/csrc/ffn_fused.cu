@@ -34,7 +34,8 @@ constexpr int kFfThreads = 192;          // warp 0 TMA producer, warp 1 MMA issu
 constexpr int kFfMaxStages = 12;
 constexpr int kFfTile1 = 32;             // phase 1: features per tile (gate 32 | up 32 -> MMA N = 64)
 constexpr int kTilesPerSlab = 64 / kFfTile1;   // phase-1 tiles that make one 64-feature slab (= one phase-2 K block)
-constexpr int kFfHeaderInts = 64;        // workspace header: [1] CTAs that have left; slab counters follow
+constexpr int kFfHeaderInts = 64;        // workspace header: [1] CTAs that have left, [8..23] cast counters; slab counters follow
+constexpr int kFfCastCounter0 = 8, kFfCastCounters = 16;   // header[8 .. 23]: CTAs done with their share of the cast
 constexpr size_t kFfHeaderBytes = 8192;  // header + counters; the activation starts here
 
 struct FfnParams {
@@ -48,6 +49,11 @@ struct FfnParams {
   int* header;                           // kFfHeaderInts ints, then inter / 64 slab counters
   float* out;                            // [m, n_out]
   int* err;
+  // fp32 input: the CTAs first cast x to bf16 (into `xb`, which the x tensor map points at) and, if asked, clear the
+  // output, each its share; header[8..23] count the CTAs that are done with it
+  const float* x_f32;                    // [m, k], or NULL when x is given as bf16
+  __nv_bfloat16* xb;                     // [m, k] in the workspace
+  int zero_out;
 };
 
 __device__ __forceinline__ int ld_acquire(const int* p) {
@@ -117,13 +123,46 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   const uint32_t t2_bytes = static_cast<uint32_t>(p.ntok) * 128;         // phase 2: activation tile of a K block
   int n1 = 0;
   for (int tile = b; tile < p.tiles1; tile += gridDim.x) n1 += p.kblocks1;   // phase-1 iterations of this CTA
+  const uint32_t S = static_cast<uint32_t>(p.stages);
+  auto stage_ptr = [&](uint32_t j) { return smem + static_cast<size_t>(j % S) * p.stage_bytes; };
+  auto issue_w1 = [&](uint32_t j, int i1) {      // i1: phase-1 iteration of this CTA
+    const int tile = b + (i1 / p.kblocks1) * static_cast<int>(gridDim.x), kb = i1 % p.kblocks1;
+    uint8_t* st = stage_ptr(j) + lane_bytes;
+    mbar_arrive_expect_tx(&full[j % S], lane_bytes + w1_bytes);
+    tma_load_2d(st, &tm_gu, kb * 64, tile * kFfTile1, &full[j % S]);                               // gate rows
+    tma_load_2d(st + kFfTile1 * 128, &tm_gu, kb * 64, p.inter + tile * kFfTile1, &full[j % S]);    // up rows
+  };
+  // The weights of the first stages do not depend on the kernel before this one: they are requested before the wait
+  // on it (programmatic dependent launch) and before the cast of x, the activations after.
+  const int first = min(n1, p.stages);
+  if (threadIdx.x == 0)
+    for (int i1 = 0; i1 < first; ++i1) issue_w1(static_cast<uint32_t>(i1), i1);
+
+  if (p.x_f32 != nullptr) {
+    // ---- phase 0: this CTA's share of x -> bf16 and of clearing the output ----
+    pdl_wait();   // x and the output belong to the kernels before this one until here; so do the header's counters
+    const long long stride = static_cast<long long>(gridDim.x) * kFfThreads;
+    const long long i0 = static_cast<long long>(b) * kFfThreads + threadIdx.x;
+    const long long n_x4 = static_cast<long long>(p.m) * p.k / 4;
+    for (long long i = i0; i < n_x4; i += stride) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(p.x_f32) + i);
+      reinterpret_cast<uint2*>(p.xb)[i] = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+    }
+    if (p.zero_out) {
+      const long long n_o4 = static_cast<long long>(p.m) * p.n_out / 4;
+      for (long long i = i0; i < n_o4; i += stride) reinterpret_cast<uint4*>(p.out)[i] = make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();                       // cumulative: covers the stores the barrier ordered before it
+      red_release_add(p.header + kFfCastCounter0 + (b % kFfCastCounters), 1);   // spread: increments of one word queue up
+    }
+  }
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     uint32_t it = 0;
     bool ok = true;
-    const uint32_t S = static_cast<uint32_t>(p.stages);
-    auto stage_ptr = [&](uint32_t j) { return smem + static_cast<size_t>(j % S) * p.stage_bytes; };
     auto wait_stage = [&](uint32_t j, int site) {
       if (!mbar_spin_wait(&empty[j % S], ((j / S) & 1u) ^ 1u)) {
         report_error(p.err, kErrBarrierTimeout, site, static_cast<int>(j));
@@ -131,23 +170,33 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       }
       return ok;
     };
-    auto issue_w1 = [&](uint32_t j, int i1) {      // i1: phase-1 iteration of this CTA
-      const int tile = b + (i1 / p.kblocks1) * static_cast<int>(gridDim.x), kb = i1 % p.kblocks1;
-      uint8_t* st = stage_ptr(j) + lane_bytes;
-      mbar_arrive_expect_tx(&full[j % S], lane_bytes + w1_bytes);
-      tma_load_2d(st, &tm_gu, kb * 64, tile * kFfTile1, &full[j % S]);                               // gate rows
-      tma_load_2d(st + kFfTile1 * 128, &tm_gu, kb * 64, p.inter + tile * kFfTile1, &full[j % S]);    // up rows
-    };
     auto issue_x1 = [&](uint32_t j, int i1) {
       tma_load_2d(stage_ptr(j), &tm_x, (i1 % p.kblocks1) * 64, 0, &full[j % S]);                     // rows past m: zeros
     };
+    pdl_wait();
+    if (p.x_f32 != nullptr && n1 > 0) {
+      // every CTA's share of the cast: x is whole once all of them have counted themselves in (lane l watches
+      // counter l, which CTAs l, l + 16, ... increment)
+      bool mine = true;
+      if (lane < kFfCastCounters) {
+        const int want = (static_cast<int>(gridDim.x) - lane + kFfCastCounters - 1) / kFfCastCounters;
+        const unsigned long long t0 = global_timer_ns();
+        while (ld_acquire(p.header + kFfCastCounter0 + lane) < want) {
+          if (global_timer_ns() - t0 > kWaitTimeoutNs) {
+            mine = false;
+            break;
+          }
+        }
+      }
+      if (!__all_sync(0xffffffffu, mine)) {
+        if (lane == 0) report_error(p.err, kErrBarrierTimeout, 88, 0);
+        ok = false;
+      }
+    }
     if (lane == 0) {
-      // The weights of the first stages do not depend on the kernel before this one: they are requested before
-      // the wait on it (programmatic dependent launch), the activations after.
-      const int first = min(n1, p.stages);
-      for (int i1 = 0; i1 < first; ++i1) issue_w1(it + i1, i1);
-      pdl_wait();
-      for (int i1 = 0; i1 < first; ++i1) issue_x1(it + i1, i1);
+      // x was written with ordinary stores by other CTAs: order the bulk (async-proxy) reads after the acquires
+      if (p.x_f32 != nullptr) asm volatile("fence.proxy.async.global;" ::: "memory");
+      for (int i1 = 0; i1 < first && ok; ++i1) issue_x1(it + i1, i1);
       it += first;
       for (int i1 = first; i1 < n1 && ok; ++i1, ++it) {
         if (!wait_stage(it, 80)) break;
@@ -346,6 +395,7 @@ ffn_fused_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   if (*last_to_leave) {
     for (int i = threadIdx.x; i < p.kblocks2; i += kFfThreads) counters[i] = 0;
     if (threadIdx.x == 0) p.header[1] = 0;
+    if (threadIdx.x < kFfCastCounters) p.header[kFfCastCounter0 + threadIdx.x] = 0;
   }
 }
 
@@ -368,9 +418,17 @@ bool ffn_fused_ok(int m, int k, int inter, int n_out) {
 // x bf16 [m, k] (m <= 128), w_gate_up packed [2 * inter, k] (gate rows first), w_down packed [n_out, inter],
 // out fp32 [m, n_out] holding zeros or the residual.  `workspace`: ffn_fused_workspace_bytes(inter) bytes,
 // 256-byte aligned, zeroed once when it is allocated and then owned by this operator (one call at a time).
+// x_f32 (fp32 [m, k], 16-byte aligned) instead of x: the kernel casts it itself into `xb` (bf16 [m, k], 16-byte
+// aligned, not part of the workspace above) and clears `out` first when zero_out is set.
 int ffn_fused_launch(const void* x, const void* w_gate_up, const void* w_down, float* out, int m, int k, int inter,
-                     int n_out, void* workspace, size_t workspace_bytes, int* err, cudaStream_t stream) {
-  PTO_REQUIRE(x && w_gate_up && w_down && out && workspace, "ffn_fused: NULL tensor");
+                     int n_out, void* workspace, size_t workspace_bytes, int* err, cudaStream_t stream,
+                     const float* x_f32, void* xb, int zero_out) {
+  PTO_REQUIRE((x || (x_f32 && xb)) && w_gate_up && w_down && out && workspace, "ffn_fused: NULL tensor");
+  if (x_f32) {
+    PTO_REQUIRE(((reinterpret_cast<uintptr_t>(x_f32) | reinterpret_cast<uintptr_t>(xb) | reinterpret_cast<uintptr_t>(out)) & 15) == 0,
+                "ffn_fused: fp32 x, its bf16 copy and the output must be 16-byte aligned");
+    x = xb;
+  }
   PTO_REQUIRE(ffn_fused_ok(m, k, inter, n_out), "ffn_fused: m <= 128, k % 8 == 0, inter % 64 == 0, n_out % 4 == 0 required");
   PTO_REQUIRE(workspace_bytes >= ffn_fused_workspace_bytes(inter), "ffn_fused: workspace too small");
   PTO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "ffn_fused: workspace must be 256-byte aligned");
@@ -394,6 +452,7 @@ int ffn_fused_launch(const void* x, const void* w_gate_up, const void* w_down, f
   p.header = static_cast<int*>(workspace);
   p.act = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(workspace) + kFfHeaderBytes);
   p.out = out; p.err = err;
+  p.x_f32 = x_f32; p.xb = static_cast<__nv_bfloat16*>(xb); p.zero_out = zero_out;
 
   CUtensorMap tm_x, tm_gu, tm_act, tm_d;
   int st = make_tensor_map_2d(&tm_x, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, m, k, static_cast<uint64_t>(k) * 2, 64,

@@ -46,6 +46,10 @@ int gemm2_bf16_launch(const void* a, int a_rows, const void* b, int b_rows_total
 int linear_launch(const void* x, const void* w_packed, float* out, int m, int n, int k, int accumulate, int* err,
                   cudaStream_t stream);
 size_t ffn_workspace_bytes(int m, int inter);
+size_t ffn_f32_workspace_bytes(int m, int k, int inter);
+int ffn_swiglu_f32_launch(const float* x, const void* w_gate_up, const void* w_down, float* out, int m, int k, int inter,
+                          int n_out, void* workspace, size_t workspace_bytes, int accumulate, int* err,
+                          cudaStream_t stream);
 int ffn_swiglu_launch(const void* x, const void* w_gate_up, const void* w_down, float* out, int m, int k, int inter,
                       int n_out, void* workspace, size_t workspace_bytes, int accumulate, int* err,
                       cudaStream_t stream);
@@ -54,7 +58,8 @@ int ffn_swiglu_launch(const void* x, const void* w_gate_up, const void* w_down, 
 bool ffn_fused_ok(int m, int k, int inter, int n_out);
 size_t ffn_fused_workspace_bytes(int inter);
 int ffn_fused_launch(const void* x, const void* w_gate_up, const void* w_down, float* out, int m, int k, int inter,
-                     int n_out, void* workspace, size_t workspace_bytes, int* err, cudaStream_t stream);
+                     int n_out, void* workspace, size_t workspace_bytes, int* err, cudaStream_t stream,
+                     const float* x_f32 = nullptr, void* xb = nullptr, int zero_out = 0);
 
 // glue.cu
 int rms_norm_launch(const void* x, int x_dtype, const float* gamma, void* out, int out_dtype, long long rows,

@@ -78,6 +78,40 @@ size_t ffn_workspace_bytes(int m, int inter) {
   return chain > fused ? chain : fused;
 }
 
+// The same for fp32 x: the workspace of the bf16 form followed by a bf16 copy of x.
+size_t ffn_f32_workspace_bytes(int m, int k, int inter) {
+  return (ffn_workspace_bytes(m, inter) + 255) / 256 * 256 + (static_cast<size_t>(m) * k * 2 + 255) / 256 * 256;
+}
+
+// fp32 x [m, k]: rounded to bf16 operands as the reference's bf16 kernels do.  With at most 128 rows the one-launch
+// kernel casts x itself and clears the output (accumulate = 0) before its first GEMM: one launch in all.  Otherwise a
+// cast kernel (which also clears the output) goes ahead of the bf16 form.
+int ffn_swiglu_f32_launch(const float* x, const void* w_gate_up, const void* w_down, float* out, int m, int k, int inter,
+                          int n_out, void* workspace, size_t workspace_bytes, int accumulate, int* err,
+                          cudaStream_t stream) {
+  PTO_REQUIRE(x && w_gate_up && w_down && out && workspace, "ffn_swiglu_f32: NULL tensor");
+  PTO_REQUIRE(m > 0 && k > 0 && inter > 0 && n_out > 0 && k % 8 == 0 && inter % 8 == 0,
+              "ffn_swiglu_f32: sizes must be positive, k and inter multiples of 8");
+  PTO_REQUIRE(workspace_bytes >= ffn_f32_workspace_bytes(m, k, inter), "ffn_swiglu_f32: workspace too small");
+  PTO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "ffn_swiglu_f32: workspace must be 256-byte aligned");
+  const size_t base_bytes = (ffn_workspace_bytes(m, inter) + 255) / 256 * 256;
+  void* xb = static_cast<uint8_t*>(workspace) + base_bytes;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  if (ffn_fused_ok(m, k, inter, n_out) && aligned)
+    return ffn_fused_launch(nullptr, w_gate_up, w_down, out, m, k, inter, n_out, workspace, base_bytes, err, stream, x, xb,
+                            accumulate ? 0 : 1);
+  const size_t out_bytes = static_cast<size_t>(m) * n_out * 4;
+  int st;
+  if (!accumulate && aligned && out_bytes % 16 == 0) {
+    st = cast_zero_launch(x, PTO_FP32, xb, PTO_BF16, static_cast<long long>(m) * k, out, out_bytes, stream);
+  } else {
+    st = cast_launch(x, PTO_FP32, xb, PTO_BF16, static_cast<long long>(m) * k, stream);
+    if (st == kOk && !accumulate) st = check_cuda(cudaMemsetAsync(out, 0, out_bytes, stream), "cudaMemsetAsync(out)");
+  }
+  if (st != kOk) return st;
+  return ffn_swiglu_launch(xb, w_gate_up, w_down, out, m, k, inter, n_out, workspace, base_bytes, 1, err, stream);
+}
+
 // out[m, n_out] (+)= (silu(x Wg) * (x Wu)) Wd with bf16 operands, fp32 accumulate, the
 // activation rounded to bf16 before the down projection
 // (tests/st/runtime/framework_and_models/test_qwen3_decode_scope3_mixed.py:282-285).

@@ -263,6 +263,17 @@ int pto_ffn_swiglu(const void* x, const void* w_gate_up, const void* w_down, voi
                                 workspace_bytes, accumulate, err, static_cast<cudaStream_t>(stream));
 }
 
+size_t pto_ffn_swiglu_f32_workspace_bytes(int m, int k, int inter) {
+  if (m <= 0 || k <= 0 || inter <= 0) return 0;
+  return pto::ffn_f32_workspace_bytes(m, k, inter);
+}
+
+int pto_ffn_swiglu_f32(const float* x, const void* w_gate_up, const void* w_down, void* out, int m, int k, int inter,
+                       int n_out, void* workspace, size_t workspace_bytes, int accumulate, int32_t* err, void* stream) {
+  return pto::ffn_swiglu_f32_launch(x, w_gate_up, w_down, static_cast<float*>(out), m, k, inter, n_out, workspace,
+                                    workspace_bytes, accumulate, err, static_cast<cudaStream_t>(stream));
+}
+
 int pto_rms_norm(const void* x, int x_dtype, const float* gamma, void* out, int out_dtype, int64_t rows, int hidden,
                  float eps, void* stream) {
   return pto::rms_norm_launch(x, x_dtype, gamma, out, out_dtype, rows, hidden, eps, nullptr, nullptr, 0,

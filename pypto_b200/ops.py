@@ -232,10 +232,13 @@ _ffn_ws: dict = {}
 def ffn_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, out: torch.Tensor | None = None,
                accumulate: bool = False):
     """fp32 out[m, n_out] (+)= bf16(silu(x Wg) * (x Wu)) Wd; packed weights
-    (w_gate_up [2*inter, k] gate rows first, w_down [n_out, inter])."""
+    (w_gate_up [2*inter, k] gate rows first, w_down [n_out, inter]); x bf16, or fp32 (rounded to bf16 operands by the
+    operator itself: one launch for at most 128 rows)."""
     dev = _need_cuda(x, w_gate_up, w_down)
-    if any(t.dtype != torch.bfloat16 for t in (x, w_gate_up, w_down)):
-        raise TypeError("ffn_swiglu: x and packed weights must be bfloat16")
+    if any(t.dtype != torch.bfloat16 for t in (w_gate_up, w_down)) or x.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("ffn_swiglu: packed weights must be bfloat16, x bfloat16 or float32")
+    if not x.is_contiguous():
+        raise ValueError("ffn_swiglu: x must be contiguous")
     m, k = x.shape
     inter = w_gate_up.shape[0] // 2
     n_out = w_down.shape[0]
@@ -248,16 +251,18 @@ def ffn_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, o
     elif out.dtype != torch.float32 or tuple(out.shape) != (m, n_out) or not out.is_contiguous():
         raise ValueError("ffn_swiglu: out must be a contiguous fp32 [m, n_out] tensor")
     lib = _lib.load()
-    need = lib.pto_ffn_swiglu_workspace_bytes(m, inter)
+    f32 = x.dtype == torch.float32
+    need = lib.pto_ffn_swiglu_f32_workspace_bytes(m, k, inter) if f32 else lib.pto_ffn_swiglu_workspace_bytes(m, inter)
     key = (dev.index, _stream_ptr(dev))
     ws = _ffn_ws.get(key)
     if ws is None or ws.numel() < need:
         # zeroed once: the one-launch kernel for small batches keeps its call counter in the first bytes
         ws = _ffn_ws[key] = torch.zeros(need, dtype=torch.uint8, device=dev)
+    entry = lib.pto_ffn_swiglu_f32 if f32 else lib.pto_ffn_swiglu
     with torch.cuda.device(dev):
-        _lib.check(lib.pto_ffn_swiglu(x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), out.data_ptr(), m, k,
-                                      inter, n_out, ws.data_ptr(), ws.numel(), 1 if accumulate else 0,
-                                      _err_ptr(dev), _stream_ptr(dev)))
+        _lib.check(entry(x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), out.data_ptr(), m, k,
+                         inter, n_out, ws.data_ptr(), ws.numel(), 1 if accumulate else 0,
+                         _err_ptr(dev), _stream_ptr(dev)))
     return out
 
 

@@ -115,6 +115,32 @@ def test_ffn_reference_example_config_fp32_inputs():
     assert rel < 1e-2, rel
 
 
+@pytest.mark.parametrize("m", [128, 57, 300])
+def test_ffn_takes_fp32_x_and_casts_it_itself(m):
+    """pto_ffn_swiglu_f32: x in fp32 as `ffn_swiglu` receives it (01_ffn.py:155-160).  At most 128 rows: ONE launch whose
+    CTAs cast x (each its share) and clear the output before the first GEMM; more rows: a cast kernel ahead of the
+    GEMM chain.  Same numbers as casting first, bit for bit; the accumulate form adds onto a residual."""
+    ops = _ops()
+    from pypto_b200.layers import SwiGLUFFN
+    x, wg, wu, wd = oracle.inputs.ffn_inputs(m, 1024, 4096, seed=m)
+    f = SwiGLUFFN(wg.cuda(), wu.cuda(), wd.cuda())
+    xd = x.cuda()
+    out = torch.full((m, 1024), 7.0, device="cuda")                  # stale contents must be cleared
+    got = ops.ffn_swiglu(xd, f.w_gate_up, f.w_down, out=out)
+    again = ops.ffn_swiglu(xd, f.w_gate_up, f.w_down, out=out)       # counters of the call before are back at zero
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    exp = offn.ffn_swiglu(x, wg, wu, wd)
+    _check(got, exp, 2e-2, f"ffn fp32 x, m = {m}")
+    ref = ops.ffn_swiglu(ops.cast(xd, torch.bfloat16), f.w_gate_up, f.w_down)
+    if m <= 128:                                                      # stream-K partial sums meet in any order
+        assert (got - ref).abs().max() <= 1e-3 * exp.abs().max() and (again - ref).abs().max() <= 1e-3 * exp.abs().max()
+    resid = torch.randn(m, 1024, device="cuda")
+    acc = ops.ffn_swiglu(xd, f.w_gate_up, f.w_down, out=resid.clone(), accumulate=True)
+    torch.cuda.synchronize()
+    _check(acc - resid, exp, 2e-2, f"ffn fp32 x accumulate, m = {m}")
+
+
 def test_ffn_64x64_reference_shape():
     """64x64 fp32, N(0,1) weights, the shapes of 01_ffn.py:157-160 (rtol/atol 3e-3 there is for
     fp32 operands; bf16 operands are held to 2e-2 of the output scale)."""
