@@ -756,6 +756,8 @@ def run_moe(args, d: Dist):
                        "frac_fp8_peak": value / d.world / fp8 if fp8 else None,
                        "exchange": {"bytes_out_per_gpu": int(routes_out * (H + H // 128 * 4 + 16)),
                                     "bytes_back_per_gpu": int(routes_out * H * 2),
+                                    "back_path": "peer memory (own kernel + flags)" if layer.peer_exchange else
+                                                 ("all-to-all-v" if d.world > 1 else "none"),
                                     "all_to_all_GBps_measured": a2a}})
 
 

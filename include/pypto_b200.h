@@ -419,7 +419,13 @@ PTO_API int pto_all_to_all_v(pto_comm* c, const void* send, const int64_t* send_
  *   w_d  e4m3 [local, hidden, inter],   s_d  fp32 [local, hidden/128, inter/128]
  *   sh_* the same for one shared expert, or all NULL
  * pto_moe_layer_create allocates every buffer a step needs, sized for max_tokens tokens per call and the worst
- * case of rows arriving at this rank; with a communicator it and every forward call are collective. */
+ * case of rows arriving at this rank; with a communicator it and every forward call are collective.
+ * Return path through peer memory: when every rank of the communicator can map every other rank's buffers (one
+ * node; CUDA IPC handles go round inside pto_moe_layer_create and all ranks agree on the outcome; the environment
+ * variable PTO_EP_PEER=0 on any rank turns it off for all), the result rows do not travel through a collective:
+ * each rank stores them into their source's buffer with its own kernel and raises a flag there
+ * (pto_moe_layer_peer_exchange tells).  Destroy such layers on all ranks only after all of them have finished their
+ * last forward call (every rank's buffers are mapped by the others until each has destroyed its layer). */
 typedef struct pto_moe_layer_desc {
   int hidden, inter, n_experts, topk, max_tokens;
   const void* gate_packed;
@@ -431,6 +437,7 @@ typedef struct pto_moe_layer_desc {
 typedef struct pto_moe_layer pto_moe_layer;
 PTO_API int pto_moe_layer_create(const pto_moe_layer_desc* desc, pto_moe_layer** out);
 PTO_API int pto_moe_layer_destroy(pto_moe_layer* layer); /* idempotent on NULL */
+PTO_API int pto_moe_layer_peer_exchange(const pto_moe_layer* layer); /* 1: results return through peer memory */
 /* x bf16 [tokens, hidden] -> y bf16 [tokens, hidden].  idx_in / w_in (int32 / fp32 [tokens, topk], both or
  * neither) replace the layer's own routing; idx_out / w_out (may be NULL) receive the routing used.  phase_ms
  * (host float[8] or NULL) receives the device time of route+quantise, plan, pack, exchange out, unpack, experts,

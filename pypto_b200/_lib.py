@@ -117,6 +117,7 @@ SIGNATURES.update({
     "pto_moe_layer_destroy": (_i, [_p]),
     "pto_moe_layer_forward": (_i, [_p, _p, _i, _p, _p, _p, _p, _p, C.POINTER(C.c_float), _p]),
     "pto_moe_layer_status": (_i, [_p, _i32p, _p]),
+    "pto_moe_layer_peer_exchange": (_i, [_p]),
 })
 
 _lock = threading.Lock()

@@ -97,6 +97,17 @@ int scale_rows_launch(const void* x, const float* w, int w_stride, const int32_t
                       long long rows, int cols, void* y, cudaStream_t stream);
 int moe_gather_f32_launch(const float* src, const int32_t* index, long long n, long long n_src, float* dst, int* err,
                           cudaStream_t stream);
+// Peer-memory return path of the expert-parallel layer (moe_route.cu): every rank's sorted result buffer and flag
+// words, as mapped into this process.
+constexpr int kMoeMaxPeers = 32;
+struct MoePeerTable {
+  uint8_t* back[kMoeMaxPeers];
+  int32_t* flags[kMoeMaxPeers];
+};
+int moe_push_rows_launch(const void* rows, int row_bytes, const int32_t* recv_counts, int world, int local_experts,
+                         const int32_t* dst_base, const MoePeerTable& peers, int my_rank, int step, long long dst_rows,
+                         long long rows_hint, int* done_counter, int* err, cudaStream_t stream);
+int moe_wait_flags_launch(const int32_t* flags, int world, int step, int* err, cudaStream_t stream);
 int moe_combine_launch(const void* rows, const int32_t* pos, const void* shared, int tokens, int topk, int hidden,
                        long long n_rows, void* y_bf16, float* y_f32, cudaStream_t stream);
 

@@ -11,11 +11,19 @@
 //   receive plan -> unpack -> gate/up GEMM -> quantise -> down GEMM (rows written in arrival order) ->
 //   ONE all-to-all-v back -> combine
 //
+// When every rank can map every other rank's buffers (one node, CUDA IPC, checked and agreed on when the layer is
+// created; PTO_EP_PEER=0 turns it off), the way back is no collective at all: a kernel stores each source's block
+// of result rows straight into that source's sorted result buffer through peer memory and raises a flag there, and
+// the source's combine waits (bounded) for the flags of all ranks (moe_push_rows_kernel, moe_wait_flags_kernel).
+// The offset of a block in its source's buffer travels with the counts.  The way out stays an all-to-all-v: it is
+// what orders a rank's next step behind the combine of the ranks it writes to.
+//
 // The host waits once per step, for the row counts of the exchange (a pinned buffer and an event); everything
 // before that wait is already queued, so the GPU packs the payload and runs the shared expert meanwhile.
 // All buffers are allocated when the layer is created, sized for `max_tokens` and the worst-case arrival count.
 #include <nvtx3/nvToolsExt.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -57,6 +65,12 @@ struct pto_moe_layer {
   cudaStream_t side = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_counts = nullptr, ev_whole = nullptr;
   cudaEvent_t ev_phase[pto::kPhases + 1] = {};
+  // peer-memory return path
+  bool peer = false;
+  int step = 0;                     // forward calls so far: the value this rank's flags are raised to
+  int32_t *flags = nullptr, *done_counter = nullptr, *base_send = nullptr, *base_recv = nullptr;   // in the arena
+  void* peer_arena[pto::kMoeMaxPeers] = {};   // other ranks' arenas as mapped here (NULL for this rank)
+  pto::MoePeerTable peers = {};
 };
 
 namespace pto {
@@ -73,6 +87,79 @@ int experts_ffn(pto_moe_layer* L, const void* w_gu, const float* s_gu, const voi
   return moe_gemm_fp8_launch(0, w_d, s_d, experts, H, H, I, act_q, act_s, offsets, rows, route_w, out_rows, out, L->err, s);
 }
 
+// Collective over the layer's communicator: every rank exports its arena (CUDA IPC), the handles and the offsets of
+// the result buffer and the flag words go round in an all-to-all, every rank maps the others, and a second
+// all-to-all of one word tells whether ALL of them could.  Only then is the peer path used; any refusal (another
+// node, no peer access, PTO_EP_PEER=0 on some rank) leaves every rank on the collective, all alike.
+struct PeerHello {
+  cudaIpcMemHandle_t handle;
+  unsigned long long arena_bytes, back_off, flags_off;
+  int want;
+  char pad[128 - sizeof(cudaIpcMemHandle_t) - 3 * sizeof(unsigned long long) - sizeof(int)];
+};
+static_assert(sizeof(PeerHello) == 128, "one hello per rank, 128 bytes");
+
+int peer_setup(pto_moe_layer* L, size_t arena_bytes) {
+  const int W = L->world;
+  const char* env = getenv("PTO_EP_PEER");
+  int want = (env == nullptr || atoi(env) != 0) && W <= kMoeMaxPeers ? 1 : 0;
+  PeerHello mine = {};
+  if (want && cudaIpcGetMemHandle(&mine.handle, L->arena) != cudaSuccess) {
+    (void)cudaGetLastError();
+    want = 0;
+  }
+  mine.arena_bytes = arena_bytes;
+  mine.back_off = static_cast<unsigned long long>(L->back - L->arena);
+  mine.flags_off = static_cast<unsigned long long>(reinterpret_cast<uint8_t*>(L->flags) - L->arena);
+  mine.want = want;
+  std::vector<PeerHello> out(W, mine), in(W);
+  uint8_t* dev = nullptr;
+  PTO_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev), 2 * sizeof(PeerHello) * W));
+  struct FreeAtExit { uint8_t* p; ~FreeAtExit() { cudaFree(p); } } free_at_exit{dev};
+  PTO_CUDA(cudaMemcpy(dev, out.data(), sizeof(PeerHello) * W, cudaMemcpyHostToDevice));
+  int st = pto_all_to_all(L->d.comm, dev, dev + sizeof(PeerHello) * W, sizeof(PeerHello), nullptr);
+  if (st != kOk) return st;
+  PTO_CUDA(cudaStreamSynchronize(nullptr));
+  PTO_CUDA(cudaMemcpy(in.data(), dev + sizeof(PeerHello) * W, sizeof(PeerHello) * W, cudaMemcpyDeviceToHost));
+  int ok = want;
+  for (int r = 0; r < W && ok; ++r) {
+    if (!in[r].want || in[r].arena_bytes != arena_bytes || in[r].back_off != mine.back_off || in[r].flags_off != mine.flags_off) {
+      ok = 0;                                   // a rank that refuses, or a layer of another shape
+      break;
+    }
+    if (r == L->rank) continue;
+    void* base = nullptr;
+    if (cudaIpcOpenMemHandle(&base, in[r].handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+      (void)cudaGetLastError();
+      ok = 0;
+      break;
+    }
+    L->peer_arena[r] = base;
+  }
+  // agreement: the peer path only if every rank mapped every other
+  std::vector<int> mine_ok(W * 32, ok), all_ok(W * 32, 0);   // 128 bytes per rank: the all-to-all's granule is not tested below that
+  PTO_CUDA(cudaMemcpy(dev, mine_ok.data(), 128 * W, cudaMemcpyHostToDevice));
+  st = pto_all_to_all(L->d.comm, dev, dev + sizeof(PeerHello) * W, 128, nullptr);
+  if (st != kOk) return st;
+  PTO_CUDA(cudaStreamSynchronize(nullptr));
+  PTO_CUDA(cudaMemcpy(all_ok.data(), dev + sizeof(PeerHello) * W, 128 * W, cudaMemcpyDeviceToHost));
+  for (int r = 0; r < W; ++r) ok = ok && all_ok[r * 32];
+  if (!ok) {
+    for (void*& p : L->peer_arena) {
+      if (p) cudaIpcCloseMemHandle(p);
+      p = nullptr;
+    }
+    return kOk;
+  }
+  for (int r = 0; r < W; ++r) {
+    uint8_t* base = r == L->rank ? L->arena : static_cast<uint8_t*>(L->peer_arena[r]);
+    L->peers.back[r] = base + mine.back_off;
+    L->peers.flags[r] = reinterpret_cast<int32_t*>(base + mine.flags_off);
+  }
+  L->peer = true;
+  return kOk;
+}
+
 }  // namespace
 }  // namespace pto
 
@@ -81,6 +168,8 @@ extern "C" {
 int pto_moe_layer_destroy(pto_moe_layer* L) {
   if (!L) return pto::kOk;
   cudaSetDevice(L->device);
+  cudaDeviceSynchronize();   // nothing of this rank is still writing into a peer's buffers
+  for (void* p : L->peer_arena) if (p) cudaIpcCloseMemHandle(p);
   for (cudaEvent_t e : L->ev_phase) if (e) cudaEventDestroy(e);
   if (L->ev_fork) cudaEventDestroy(L->ev_fork);
   if (L->ev_join) cudaEventDestroy(L->ev_join);
@@ -134,7 +223,9 @@ int pto_moe_layer_create(const pto_moe_layer_desc* desc, pto_moe_layer** out) {
       {(void**)&L->act, (size_t)(C * I * 2)}, {(void**)&L->act_q, (size_t)(C * I)}, {(void**)&L->act_s, (size_t)(C * (I / 128) * 4)},
       {(void**)&L->y_g, (size_t)(C * H * 2)}, {(void**)&L->back, world > 1 ? (size_t)(routes * H * 2) : 0},
       {(void**)&L->sh_act, d.sh_w_gu ? (size_t)(T * I * 2) : 0}, {(void**)&L->sh_act_q, d.sh_w_gu ? (size_t)(T * I) : 0},
-      {(void**)&L->sh_act_s, d.sh_w_gu ? (size_t)(T * (I / 128) * 4) : 0}, {(void**)&L->sh_out, d.sh_w_gu ? (size_t)(T * H * 2) : 0}};
+      {(void**)&L->sh_act_s, d.sh_w_gu ? (size_t)(T * (I / 128) * 4) : 0}, {(void**)&L->sh_out, d.sh_w_gu ? (size_t)(T * H * 2) : 0},
+      {(void**)&L->flags, 256}, {(void**)&L->done_counter, 256}, {(void**)&L->base_send, (size_t)(world * 4)},
+      {(void**)&L->base_recv, (size_t)(world * 4)}};
   size_t total = 0;
   for (auto& s : slots) total += al256(s.bytes ? s.bytes : 1);
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&L->arena), total);
@@ -145,6 +236,7 @@ int pto_moe_layer_create(const pto_moe_layer_desc* desc, pto_moe_layer** out) {
     off += al256(s.bytes ? s.bytes : 1);
   }
   int st = check_cuda(cudaMemset(L->err, 0, 256), "cudaMemset");
+  if (st == kOk) st = check_cuda(cudaMemset(L->flags, 0, 512), "cudaMemset");   // flags and the push kernel's counter
   if (st == kOk) st = check_cuda(cudaMallocHost(reinterpret_cast<void**>(&L->host_counts), (2 * E + 2) * 4), "cudaMallocHost");
   if (st == kOk) st = check_cuda(cudaMallocHost(reinterpret_cast<void**>(&L->host_whole), 16), "cudaMallocHost");
   if (st == kOk) st = check_cuda(cudaStreamCreateWithFlags(&L->side, cudaStreamNonBlocking), "cudaStreamCreate");
@@ -153,10 +245,13 @@ int pto_moe_layer_create(const pto_moe_layer_desc* desc, pto_moe_layer** out) {
   if (st == kOk) st = check_cuda(cudaEventCreateWithFlags(&L->ev_counts, cudaEventDisableTiming), "cudaEventCreate");
   if (st == kOk) st = check_cuda(cudaEventCreateWithFlags(&L->ev_whole, cudaEventDisableTiming), "cudaEventCreate");
   for (int i = 0; st == kOk && i <= kPhases; ++i) st = check_cuda(cudaEventCreate(&L->ev_phase[i]), "cudaEventCreate");
+  if (st == kOk && world > 1) st = peer_setup(L, total);
   if (st != kOk) { pto_moe_layer_destroy(L); return st; }
   *out = L;
   return kOk;
 }
+
+int pto_moe_layer_peer_exchange(const pto_moe_layer* L) { return L && L->peer ? 1 : 0; }
 
 int pto_moe_layer_status(pto_moe_layer* L, int32_t out4[4], void* stream) {
   using namespace pto;
@@ -256,6 +351,12 @@ int pto_moe_layer_forward(pto_moe_layer* L, const void* x, int tokens, const int
     // counts exchange, and their way to the host
     st = pto_all_to_all(d.comm, L->counts, L->recv_counts, static_cast<size_t>(Le) * 4, s);
     if (st != kOk) return st;
+    if (L->peer) {
+      // where, in MY sorted result buffer, the block of each destination rank begins: offsets[r * Le]
+      PTO_CUDA(cudaMemcpy2DAsync(L->base_send, 4, L->offsets, static_cast<size_t>(Le) * 4, 4, W, cudaMemcpyDeviceToDevice, s));
+      st = pto_all_to_all(d.comm, L->base_send, L->base_recv, 4, s);
+      if (st != kOk) return st;
+    }
     PTO_CUDA(cudaMemcpyAsync(L->host_counts, L->offsets, (E + 1) * 4, cudaMemcpyDeviceToHost, s));
     PTO_CUDA(cudaMemcpyAsync(L->host_counts + E + 1, L->recv_counts, E * 4, cudaMemcpyDeviceToHost, s));
     PTO_CUDA(cudaEventRecord(L->ev_counts, s));
@@ -303,8 +404,19 @@ int pto_moe_layer_forward(pto_moe_layer* L, const void* x, int tokens, const int
       if (st != kOk) return st;
     }
     if ((st = mark()) != kOk) return st;   // experts
-    st = pto_all_to_all_v(d.comm, L->y_g, recv_rows.data(), L->back, send_rows.data(), static_cast<size_t>(H) * 2, s);
-    if (st != kOk) return st;
+    if (L->peer) {
+      // every source's block of result rows straight into that source's sorted buffer, then the flags; the combine
+      // below starts once every rank's flag here shows this step
+      ++L->step;
+      st = moe_push_rows_launch(L->y_g, H * 2, L->recv_counts, W, Le, L->base_recv, L->peers, L->rank, L->step,
+                                static_cast<long long>(d.max_tokens) * K, arrived, L->done_counter, L->err, s);
+      if (st != kOk) return st;
+      st = moe_wait_flags_launch(L->flags, W, L->step, L->err, s);
+      if (st != kOk) return st;
+    } else {
+      st = pto_all_to_all_v(d.comm, L->y_g, recv_rows.data(), L->back, send_rows.data(), static_cast<size_t>(H) * 2, s);
+      if (st != kOk) return st;
+    }
     if ((st = mark()) != kOk) return st;   // exchange_back
   }
   if (W == 1) {

@@ -456,6 +456,92 @@ scale_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__
   }
 }
 
+// ---- results on their way home through peer memory (expert parallel, every rank on the same NVSwitch) ----
+//
+// The expert GEMM leaves its result rows in the order the rows arrived: source rank after source rank, and inside a
+// source in the order that rank sorted them.  A source's block therefore belongs, as it stands, at one offset of
+// that source's own sorted result buffer -- the offset the source sent along with its counts.  This kernel copies
+// every block straight into its source's buffer with plain stores to peer memory (one warp per row, 16-byte
+// chunks, four loads in flight) instead of handing the rows to an all-to-all; the block for this rank itself takes the
+// same path.  When the last CTA is done it raises this rank's flag on every peer to the step number: each CTA
+// fences its stores system-wide before it counts itself in, the last one fences again and stores the flags with
+// release semantics, so a peer that has seen the flag sees the rows.  No flag is ever reset: steps only count up.
+__global__ void __launch_bounds__(256)
+moe_push_rows_kernel(const uint8_t* __restrict__ rows, int row_bytes, const int32_t* __restrict__ recv_counts, int world,
+                     int local_experts, const int32_t* __restrict__ dst_base, MoePeerTable peers, int my_rank, int step,
+                     long long dst_rows, int* __restrict__ done_counter, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ long long first[kMoeMaxPeers + 1];   // arrival row at which the block of source s begins
+  __shared__ int n_src[kMoeMaxPeers];
+  if (static_cast<int>(threadIdx.x) < world) {
+    int n = 0;
+    for (int e = 0; e < local_experts; ++e) n += recv_counts[threadIdx.x * local_experts + e];
+    n_src[threadIdx.x] = n;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    long long run = 0;
+    for (int r = 0; r < world; ++r) {
+      first[r] = run;
+      run += n_src[r];
+    }
+    first[world] = run;
+  }
+  __syncthreads();
+  const long long total = first[world];
+  const int lane = threadIdx.x & 31;
+  const int n16 = row_bytes / 16;
+  for (long long a = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); a < total;
+       a += static_cast<long long>(gridDim.x) * (blockDim.x >> 5)) {
+    int src = 0;
+    while (src + 1 < world && a >= first[src + 1]) ++src;
+    const long long slot = static_cast<long long>(dst_base[src]) + (a - first[src]);
+    if (dst_base[src] < 0 || slot >= dst_rows) {          // a base that does not belong to a sorted buffer of this size
+      if (lane == 0) report_error(err, kErrBadIndex, 65, src);
+      continue;
+    }
+    const uint4* s16 = reinterpret_cast<const uint4*>(rows + a * row_bytes);
+    uint4* d16 = reinterpret_cast<uint4*>(peers.back[src] + slot * row_bytes);
+    int c = lane;
+    for (; c + 96 < n16; c += 128) {
+      const uint4 v0 = s16[c], v1 = s16[c + 32], v2 = s16[c + 64], v3 = s16[c + 96];
+      d16[c] = v0; d16[c + 32] = v1; d16[c + 64] = v2; d16[c + 96] = v3;
+    }
+    for (; c < n16; c += 32) d16[c] = s16[c];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();                                // cumulative: the CTA's stores, ordered before it by the barrier
+    if (atomicAdd(done_counter, 1) == static_cast<int>(gridDim.x) - 1) {
+      *done_counter = 0;                                   // for the next launch (stream order)
+      __threadfence_system();
+      for (int r = 0; r < world; ++r)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(peers.flags[r] + my_rank), "r"(step) : "memory");
+    }
+  }
+}
+
+// One warp: lane r waits (bounded) until rank r has raised its flag here to `step`.
+__global__ void __launch_bounds__(32)
+moe_wait_flags_kernel(const int32_t* __restrict__ flags, int world, int step, int* err) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
+    if (v - step >= 0) return;
+    if (global_timer_ns() - t0 > 2 * kWaitTimeoutNs) {
+      report_error(err, kErrBarrierTimeout, 66, r);
+      return;
+    }
+    __nanosleep(200);
+  }
+}
+
 int grid_rows(long long rows, int warps_per_cta) {
   long long g = (rows + warps_per_cta - 1) / warps_per_cta;
   const long long cap = static_cast<long long>(sm_count()) * 8;
@@ -592,6 +678,26 @@ int moe_combine_launch(const void* rows, const int32_t* pos, const void* shared,
                                                  static_cast<const __nv_bfloat16*>(shared), topk, hidden, n_rows,
                                                  static_cast<__nv_bfloat16*>(y_bf16), y_f32);
   return check_cuda(cudaGetLastError(), "moe_combine_kernel launch");
+}
+
+// Result rows (arrival order, `row_bytes` each, a multiple of 16) to the sorted result buffers of their source ranks
+// through peer memory; then this rank's flag on every peer becomes `step`.  recv_counts int32 [world][local_experts]
+// and dst_base int32 [world] (the offset each source asked for) are device arrays; `rows_hint` sizes the grid.
+int moe_push_rows_launch(const void* rows, int row_bytes, const int32_t* recv_counts, int world, int local_experts,
+                         const int32_t* dst_base, const MoePeerTable& peers, int my_rank, int step, long long dst_rows,
+                         long long rows_hint, int* done_counter, int* err, cudaStream_t stream) {
+  PTO_REQUIRE(rows && recv_counts && dst_base && done_counter, "moe_push_rows: NULL argument");
+  PTO_REQUIRE(world >= 1 && world <= kMoeMaxPeers && local_experts >= 1 && row_bytes > 0 && row_bytes % 16 == 0,
+              "moe_push_rows: 1..32 ranks, rows a multiple of 16 bytes");
+  launch_kernel(moe_push_rows_kernel, dim3(grid_rows(rows_hint, 8)), dim3(256), 0, stream, static_cast<const uint8_t*>(rows),
+                row_bytes, recv_counts, world, local_experts, dst_base, peers, my_rank, step, dst_rows, done_counter, err);
+  return check_cuda(cudaGetLastError(), "moe_push_rows_kernel launch");
+}
+
+int moe_wait_flags_launch(const int32_t* flags, int world, int step, int* err, cudaStream_t stream) {
+  PTO_REQUIRE(flags && world >= 1 && world <= kMoeMaxPeers, "moe_wait_flags: 1..32 ranks");
+  launch_kernel(moe_wait_flags_kernel, dim3(1), dim3(32), 0, stream, flags, world, step, err);
+  return check_cuda(cudaGetLastError(), "moe_wait_flags_kernel launch");
 }
 
 }  // namespace pto

@@ -282,6 +282,14 @@ class MoELayer:
         except Exception:
             pass
 
+    @property
+    def peer_exchange(self) -> bool:
+        """True when the experts' results return through peer memory (the library's own kernel and flags) instead of
+        an all-to-all: every rank could map every other rank's buffers when the layer was created."""
+        from . import _lib
+        h = getattr(self, "_handle", None)
+        return bool(h is not None and _lib.load().pto_moe_layer_peer_exchange(h))
+
     def status(self) -> tuple:
         """The layer's device error word (code, site, CTA, detail); reading clears it."""
         import ctypes as C
