@@ -356,6 +356,19 @@ PTO_API int pto_moe_expert_gemm(int swiglu, const void* w, const float* w_scale,
 PTO_API int pto_moe_combine(const void* rows, const int32_t* pos, const void* shared, int tokens, int topk,
                             int hidden, int64_t n_rows, void* y_bf16, float* y_f32, void* stream);
 
+/* The return path of the expert-parallel layer as two calls (pto_moe_layer_forward issues them itself): result
+ * rows in arrival order -- source rank after source rank, recv_counts int32 [world][local_experts] rows from each --
+ * are stored block by block into the sorted result buffers of their sources, back[r] + dst_base[r] * row_bytes
+ * (device pointers of this process; another rank's buffer is one mapped from its CUDA IPC handle), and then
+ * flags[r][my_rank] = step on every rank r.  row_bytes a multiple of 16; dst_rows = rows a result buffer holds
+ * (a block that would not fit is refused through the error word); done_counter: one zeroed int32 on the device,
+ * left at zero; rows_hint sizes the grid.  pto_moe_wait_flags: one warp waits, for at most two seconds, until
+ * flags[r] >= step for every r < world, then the error word says which rank did not show (PTO_DEVICE_TIMEOUT). */
+PTO_API int pto_moe_push_rows(const void* rows, int row_bytes, const int32_t* recv_counts, int world, int local_experts,
+                              const int32_t* dst_base, void* const* back, int32_t* const* flags, int my_rank, int step,
+                              int64_t dst_rows, int64_t rows_hint, int32_t* done_counter, int32_t* err, void* stream);
+PTO_API int pto_moe_wait_flags(const int32_t* flags, int world, int step, int32_t* err, void* stream);
+
 /* ---- MX block-scaled FP8 matmul ---- */
 
 /* out[m, n] = (acc_in[m, n] +) sum_k a[m, k] * 2^(sa[m, k/32] - 127) * b[k, n] * 2^(sb[k/32, n] - 127).

@@ -92,6 +92,8 @@ SIGNATURES = {
     "pto_scale_rows": (_i, [_p, _p, _i, _p, _i, _i64, _i, _p, _p]),
     "pto_moe_expert_gemm": (_i, [_i, _p, _p, _i, _i, _i, _i, _p, _p, _p, _i, _p, _p, _p, _p, _p]),
     "pto_moe_combine": (_i, [_p, _p, _p, _i, _i, _i, _i64, _p, _p, _p]),
+    "pto_moe_push_rows": (_i, [_p, _i, _p, _i, _i, _p, _p, _p, _i, _i, _i64, _i64, _p, _p, _p]),
+    "pto_moe_wait_flags": (_i, [_p, _i, _i, _p, _p]),
     "pto_matmul_mx": (_i, [_p, _p, _i, _p, _p, _i, _p, _p, _i, _i, _i, _p, _p]),
     "pto_transpose_u8": (_i, [_p, _p, _i64, _i64, _p]),
     "pto_comm_unique_id": (_i, [_p]),

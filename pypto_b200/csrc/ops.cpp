@@ -369,6 +369,25 @@ int pto_moe_combine(const void* rows, const int32_t* pos, const void* shared, in
                                  static_cast<cudaStream_t>(stream));
 }
 
+int pto_moe_push_rows(const void* rows, int row_bytes, const int32_t* recv_counts, int world, int local_experts,
+                      const int32_t* dst_base, void* const* back, int32_t* const* flags, int my_rank, int step,
+                      int64_t dst_rows, int64_t rows_hint, int32_t* done_counter, int32_t* err, void* stream) {
+  if (!back || !flags) return pto::fail(pto::kInvalidArgument, "moe_push_rows: NULL pointer table");
+  if (world < 1 || world > pto::kMoeMaxPeers) return pto::fail(pto::kInvalidArgument, "moe_push_rows: 1..32 ranks");
+  pto::MoePeerTable t = {};
+  for (int r = 0; r < world; ++r) {
+    if (!back[r] || !flags[r]) return pto::fail(pto::kInvalidArgument, "moe_push_rows: NULL buffer or flag pointer");
+    t.back[r] = static_cast<uint8_t*>(back[r]);
+    t.flags[r] = flags[r];
+  }
+  return pto::moe_push_rows_launch(rows, row_bytes, recv_counts, world, local_experts, dst_base, t, my_rank, step, dst_rows,
+                                   rows_hint, done_counter, err, static_cast<cudaStream_t>(stream));
+}
+
+int pto_moe_wait_flags(const int32_t* flags, int world, int step, int32_t* err, void* stream) {
+  return pto::moe_wait_flags_launch(flags, world, step, err, static_cast<cudaStream_t>(stream));
+}
+
 int pto_matmul_mx(const void* a, const void* a_scale, int a_scale_layout, const void* b_t, const void* b_scale,
                   int b_scale_layout, const float* acc_in, float* out, int m, int n, int k, int32_t* err,
                   void* stream) {

@@ -522,6 +522,36 @@ def moe_combine(rows: torch.Tensor, pos: torch.Tensor, shared: torch.Tensor | No
     return (y, y32) if want_f32 else y
 
 
+def moe_push_rows(rows: torch.Tensor, recv_counts: torch.Tensor, dst_base: torch.Tensor, back: list, flags: list,
+                  my_rank: int, step: int, done_counter: torch.Tensor) -> None:
+    """The expert-parallel layer's return path as a call of its own: ``rows`` [n, cols] (arrival order, recv_counts
+    int32 [world, local_experts] rows from each source) go block by block to ``back[r][dst_base[r]:]``, then
+    ``flags[r][my_rank] = step``.  ``back`` / ``flags``: one tensor per rank, of this process (tensors of other ranks
+    would be ones mapped from their CUDA IPC handles)."""
+    import ctypes as C
+    dev = _need_cuda(rows, recv_counts, dst_base, done_counter, *back, *flags)
+    world, local_experts = recv_counts.shape
+    if len(back) != world or len(flags) != world:
+        raise ValueError("moe_push_rows: one result buffer and one flag array per rank")
+    row_bytes = rows.shape[1] * rows.element_size()
+    if any(b.shape[1:] != rows.shape[1:] or b.dtype != rows.dtype or not b.is_contiguous() for b in back):
+        raise ValueError("moe_push_rows: result buffers must be contiguous with the rows' width and dtype")
+    bp = (C.c_void_p * world)(*[b.data_ptr() for b in back])
+    fp = (C.c_void_p * world)(*[f.data_ptr() for f in flags])
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_moe_push_rows(rows.data_ptr(), row_bytes, recv_counts.data_ptr(), world, local_experts,
+                                                 dst_base.data_ptr(), bp, fp, my_rank, step, min(b.shape[0] for b in back),
+                                                 rows.shape[0], done_counter.data_ptr(), _err_ptr(dev), _stream_ptr(dev)))
+
+
+def moe_wait_flags(flags: torch.Tensor, world: int, step: int) -> None:
+    """Waits on the device (at most two seconds) until ``flags[r] >= step`` for every rank; a rank that does not show
+    ends up in the device error word (``check_device_status``)."""
+    dev = _need_cuda(flags)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().pto_moe_wait_flags(flags.data_ptr(), world, step, _err_ptr(dev), _stream_ptr(dev)))
+
+
 # ---------------------------------------------------------------------------
 # MX block-scaled FP8 matmul
 # ---------------------------------------------------------------------------
