@@ -198,21 +198,38 @@ int op_decoder_layer(Worker* w, const pto_task_args* a) {
 
 // tensors: x [m, k] bf16, w [k, n] bf16 or fp32 (the `x @ W` layout), out [m, n] fp32; scalars: accumulate
 // (examples/models/qwen3_jit/kernels/projection.py:36-143)
+// tensors: x bf16 or fp32 [m, k] (fp32 is rounded to bf16 operands), w bf16/fp32 [k, n], out fp32 [m, n], and
+// optionally bias fp32 [m, n]: out = x w + bias (examples/intermediate/01_fused_linear.py:60-66).  scalar: accumulate
+// onto what out holds (ignored with a bias).
 int op_linear(Worker* w, const pto_task_args* a) {
-  if (a->n_tensors != 3 || a->n_scalars != 1) return fail(kInvalidArgument, "linear: expects 3 tensors and 1 scalar");
+  if ((a->n_tensors != 3 && a->n_tensors != 4) || a->n_scalars != 1)
+    return fail(kInvalidArgument, "linear: expects 3 or 4 tensors and 1 scalar");
   const pto_chip_tensor* t = a->tensors;
   if (t[0].ndims != 2 || t[1].ndims != 2) return fail(kInvalidArgument, "linear: 2-D tensors expected");
   const int m = t[0].shapes[0], k = t[0].shapes[1], n = t[1].shapes[1];
-  if (t[0].dtype != PTO_BF16 || (t[1].dtype != PTO_BF16 && t[1].dtype != PTO_FP32) || (int)t[1].shapes[0] != k ||
-      !is2d(t[2], m, n, PTO_FP32))
-    return fail(kInvalidArgument, "linear: x bf16 [m, k], w bf16/fp32 [k, n], out fp32 [m, n] expected");
-  int st = w->ensure_scratch(4096 + al256(static_cast<size_t>(n) * k * 2));
+  if ((t[0].dtype != PTO_BF16 && t[0].dtype != PTO_FP32) || (t[1].dtype != PTO_BF16 && t[1].dtype != PTO_FP32) ||
+      (int)t[1].shapes[0] != k || !is2d(t[2], m, n, PTO_FP32) || (a->n_tensors == 4 && !is2d(t[3], m, n, PTO_FP32)))
+    return fail(kInvalidArgument, "linear: x bf16/fp32 [m, k], w bf16/fp32 [k, n], out (and bias) fp32 [m, n] expected");
+  const size_t w_b = al256(static_cast<size_t>(n) * k * 2), x_b = al256(static_cast<size_t>(m) * k * 2);
+  int st = w->ensure_scratch(4096 + w_b + x_b);
   if (st != kOk) return st;
   void* wp = static_cast<uint8_t*>(w->scratch) + 4096;
   st = pack_weight_launch(tptr(t[1], t[1].dtype == PTO_FP32 ? 4 : 2), (int)t[1].dtype, wp, k, n, w->stream);
   if (st != kOk) return st;
-  return linear_launch(tptr(t[0], 2), wp, static_cast<float*>(tptr(t[2], 4)), m, n, k, a->scalars[0] != 0,
-                       static_cast<int*>(w->scratch), w->stream);
+  const void* xb = tptr(t[0], 2);
+  if (t[0].dtype == PTO_FP32) {
+    void* cast_to = static_cast<uint8_t*>(wp) + w_b;
+    st = cast_launch(tptr(t[0], 4), PTO_FP32, cast_to, PTO_BF16, static_cast<long long>(m) * k, w->stream);
+    if (st != kOk) return st;
+    xb = cast_to;
+  }
+  int accumulate = a->scalars[0] != 0;
+  if (a->n_tensors == 4) {
+    PTO_CUDA(cudaMemcpyAsync(tptr(t[2], 4), tptr(t[3], 4), static_cast<size_t>(m) * n * 4, cudaMemcpyDeviceToDevice, w->stream));
+    accumulate = 1;
+  }
+  return linear_launch(xb, wp, static_cast<float*>(tptr(t[2], 4)), m, n, k, accumulate, static_cast<int*>(w->scratch),
+                       w->stream);
 }
 
 // tensors: qkv fp32 [b, (Hq + 2 Hkv) * D], seq_lens int32 [b], rope_cos, rope_sin fp32 [rows, D], block_table int32

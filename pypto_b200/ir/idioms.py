@@ -14,6 +14,11 @@ tensor and unifies that expression with the algebraic form of a fused operator:
 
       out = x / sqrt(c * row_sum(x * x) + eps) * gamma          (or  x * rsqrt(...) * gamma)
 
+* a matrix product, alone or with a full-size bias (examples/beginner/05_matmul.py:29-38,
+  examples/intermediate/01_fused_linear.py:60-66)::
+
+      out = a @ b                    out = a @ b + bias
+
 Products and sums are flattened, constants folded and operands matched in any order, so ``mul(up, swish)`` is the same
 as ``mul(swish, up)`` and ``sub(0, g)`` the same as ``mul(g, -1)``.  The match binds the roles (x, Wg, Wu, Wd, out, ...)
 to the entry's own parameter names and the constants (eps) to their values.  What the evaluator does not follow -- a
@@ -359,4 +364,13 @@ def recognise(entry: Function, program=None) -> Recognised | None:
                 r = finish("rms_norm", b)
                 if r is not None:
                     return r
+        for b in _unify(("matmul", V("a"), V("b")), expr, {}):
+            r = finish("linear", b)
+            if r is not None:
+                return r
+    if n_in == 3:
+        for b in _unify(add(("matmul", V("a"), V("b")), V("bias")), expr, {}):
+            r = finish("linear", b)
+            if r is not None:
+                return r
     return None

@@ -204,6 +204,35 @@ class RmsNormOp(FusedOp):
         worker.launch("rms_norm", [dev[n] for n in self.names], plan["scalars"])
 
 
+class LinearOp(FusedOp):
+    """``out = a @ b`` or ``out = a @ b + bias`` of a program recognised by what it computes (ir/idioms.py;
+    examples/beginner/05_matmul.py:29-38, examples/intermediate/01_fused_linear.py:60-66): the registered ``linear``
+    callable with the program's own parameter names.  fp32 operands are rounded to bf16 for the tensor cores."""
+
+    op_names = ("linear",)
+
+    def __init__(self, entry, a: str, b: str, out: str, bias: str | None = None):
+        self.entry, self.a, self.b, self.out, self.bias = entry, a, b, out, bias
+
+    def matches(self, entry) -> bool:
+        return entry is self.entry
+
+    def plan(self, compiled, host, worker):
+        a, b, out = host[self.a], host[self.b], host[self.out]
+        if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0] or tuple(out.shape) != (a.shape[0], b.shape[1]):
+            raise ValueError("linear: operand shapes do not chain")
+        if out.dtype != torch.float32 or (self.bias is not None and (host[self.bias].dtype != torch.float32 or
+                                                                     host[self.bias].shape != out.shape)):
+            raise TypeError("linear: output and bias must be float32 of the product's shape")
+        if a.shape[1] % 8:
+            raise ValueError("linear: the inner size must be a multiple of 8")
+        return {}
+
+    def launch(self, worker, dev, host, plan):
+        names = [self.a, self.b, self.out] + ([self.bias] if self.bias is not None else [])
+        worker.launch("linear", [dev[n] for n in names], [0])
+
+
 def _f32_bits(v: float) -> int:
     return struct.unpack("I", struct.pack("f", float(v)))[0]
 
@@ -326,6 +355,8 @@ def from_idiom(entry, program=None) -> FusedOp | None:
         return FfnSwigluOp(entry, (r["x"], r["w_gate"], r["w_up"], r["w_down"], r["out"]))
     if rec.idiom == "rms_norm":
         return RmsNormOp(entry, (r["x"], r["gamma"], r["out"]), eps=rec.constants.get("eps"), inv_n=rec.constants.get("inv_n"))
+    if rec.idiom == "linear":
+        return LinearOp(entry, r["a"], r["b"], r["out"], r.get("bias"))
     return None
 
 

@@ -79,3 +79,25 @@ def looped(tokens: pl.Tensor, w: pl.Tensor, y: pl.Out[pl.Tensor]):
     for i in pl.range(4):
         y = product_kernel(tokens, w, y)
     return y
+
+
+@pl.jit
+def product(lhs: pl.Tensor, rhs: pl.Tensor, dst: pl.Out[pl.Tensor]):
+    """dst = lhs @ rhs through the kernel above."""
+    dst = product_kernel(lhs, rhs, dst)
+    return dst
+
+
+@pl.jit.incore
+def shift_kernel(t: pl.Tensor, offset: pl.Tensor, dst: pl.Out[pl.Tensor]):
+    pl.store(pl.add(pl.load(offset, [0, 0], [64, 64]), pl.load(t, [0, 0], [64, 64])), [0, 0], dst)
+    return dst
+
+
+@pl.jit
+def affine(offset: pl.Tensor, lhs: pl.Tensor, rhs: pl.Tensor, dst: pl.Out[pl.Tensor]):
+    """dst = offset + lhs @ rhs: the bias comes first in the signature and first in the sum."""
+    tmp = pl.create_tensor([64, 64], dtype=pl.FP32)
+    tmp = product_kernel(lhs, rhs, tmp)
+    dst = shift_kernel(tmp, offset, dst)
+    return dst

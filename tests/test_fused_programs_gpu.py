@@ -94,3 +94,24 @@ def test_programs_recognised_by_what_they_compute_run_on_the_fused_kernels():
     validate_golden({"normed": normed}, {"normed": olayer.rms_norm_sqrt_div(rows, weight, progs.EPS)}, rtol=1e-5, atol=1e-5)
     with pytest.raises(ValueError, match="not 1 / 128"):
         progs.scaled_norm(torch.randn(1, 128), torch.randn(32, 128), torch.zeros(32, 128))   # the program divides by 64
+
+
+def test_matrix_product_programs_run_on_the_tensor_core_gemm():
+    """`dst = lhs @ rhs` and `dst = offset + lhs @ rhs` under names of their own (the shapes of the reference's
+    05_matmul.py and 01_fused_linear.py examples, fp32 tensors): recognised by their bodies, run by the `linear`
+    callable with bf16 operands and fp32 accumulation, held to 2e-2 of the output scale."""
+    from tests.dsl_programs import renamed_idioms as progs
+    torch.manual_seed(0)
+    a, b, off = torch.randn(64, 64), torch.randn(64, 64), torch.randn(64, 64)
+    dst = torch.zeros(64, 64)
+    progs.product(a, b, dst)
+    exp = a @ b
+    assert (dst - exp).abs().max() <= 2e-2 * exp.abs().max()
+    dst2 = torch.full((64, 64), 9.0)
+    progs.affine(off, a, b, dst2)
+    assert (dst2 - (exp + off)).abs().max() <= 2e-2 * (exp + off).abs().max()
+    a, b = torch.randn(300, 520), torch.randn(520, 384)                # ragged tiles, more than 256 rows
+    dst = torch.zeros(300, 384)
+    progs.product(a, b, dst)
+    exp = a.bfloat16().float() @ b.bfloat16().float()
+    assert (dst - exp).abs().max() <= 2e-3 * exp.abs().max()

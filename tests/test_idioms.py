@@ -28,6 +28,17 @@ def test_rms_norm_is_recognised_with_its_constants():
     assert op.eps == pytest.approx(progs.EPS) and op.names == ("rows", "weight", "normed")
 
 
+def test_matrix_products_are_recognised_with_and_without_a_bias():
+    rec = idioms.recognise(progs.product)
+    assert rec is not None and rec.idiom == "linear" and rec.roles == {"a": "lhs", "b": "rhs", "out": "dst"}
+    rec = idioms.recognise(progs.affine)
+    assert rec is not None and rec.idiom == "linear"
+    assert rec.roles == {"a": "lhs", "b": "rhs", "bias": "offset", "out": "dst"}
+    op = fused_programs.from_idiom(progs.affine)
+    assert op.op_names == ("linear",) and (op.a, op.b, op.out, op.bias) == ("lhs", "rhs", "dst", "offset")
+    assert ir.compile(progs.product, platform="b200").op_names == ("linear",)
+
+
 def test_what_is_not_an_idiom_is_refused():
     assert idioms.recognise(progs.relu_mlp) is None          # same shape of program, another activation
     assert idioms.recognise(progs.looped) is None            # a loop is not followed
@@ -81,3 +92,10 @@ def test_the_reference_examples_are_recognised_by_their_bodies():
     assert rec is not None and rec.idiom == "rms_norm" and rec.roles == {"x": "x", "gamma": "gamma", "out": "output"}
     assert rec.constants["eps"] == pytest.approx(1e-5) and rec.constants["inv_n"] == pytest.approx(1.0 / 64)
     assert idioms.recognise(norm.layer_norm) is None
+    mm = load("examples/beginner/05_matmul.py", "ref_example_05_matmul")
+    rec = idioms.recognise(mm.matmul_64)
+    assert rec is not None and rec.idiom == "linear" and rec.roles == {"a": "a", "b": "b", "out": "c"}
+    fl = load("examples/intermediate/01_fused_linear.py", "ref_example_01_fused_linear")
+    rec = idioms.recognise(fl.fused_matmul_bias)
+    assert rec is not None and rec.idiom == "linear" and rec.roles == {"a": "a", "b": "b", "bias": "bias", "out": "c"}
+    assert idioms.recognise(fl.fused_linear_relu) is None            # relu(a @ b + bias): no fused operator for it
