@@ -405,15 +405,24 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ rows, const int32_t* __rest
   const int t = blockIdx.x;
   for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int k = 0; k < topk; ++k) {
-      const int p = pos[static_cast<size_t>(t) * topk + k];
-      if (p < 0 || p >= n_rows) continue;   // a route that was refused by the plan, or a slot outside `rows`
-      const uint4 v = *reinterpret_cast<const uint4*>(rows + static_cast<size_t>(p) * hidden + c);
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    // eight routes at a time: their positions first, then their rows (all loads in flight together), then the sums in
+    // k order.  A route that was refused by the plan, or a slot outside `rows`, contributes zeros.
+    for (int k0 = 0; k0 < topk; k0 += 8) {
+      uint4 v[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        acc[2 * i] += bf16_lo_to_float(w[i]);
-        acc[2 * i + 1] += bf16_hi_to_float(w[i]);
+      for (int j = 0; j < 8; ++j) {
+        const int p = k0 + j < topk ? pos[static_cast<size_t>(t) * topk + k0 + j] : -1;
+        v[j] = (p >= 0 && p < n_rows) ? __ldg(reinterpret_cast<const uint4*>(rows + static_cast<size_t>(p) * hidden + c))
+                                      : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[2 * i] += bf16_lo_to_float(w[i]);
+          acc[2 * i + 1] += bf16_hi_to_float(w[i]);
+        }
       }
     }
     if (shared) {
