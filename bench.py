@@ -758,6 +758,8 @@ def run_moe(args, d: Dist):
                                     "bytes_back_per_gpu": int(routes_out * H * 2),
                                     "back_path": "peer memory (own kernel + flags)" if layer.peer_exchange else
                                                  ("all-to-all-v" if d.world > 1 else "none"),
+                                    "out_path": "peer memory (own kernel + flags)" if layer.peer_exchange_level >= 2 else
+                                                ("all-to-all-v" if d.world > 1 else "none"),
                                     "all_to_all_GBps_measured": a2a}})
 
 

@@ -450,7 +450,9 @@ typedef struct pto_moe_layer_desc {
 typedef struct pto_moe_layer pto_moe_layer;
 PTO_API int pto_moe_layer_create(const pto_moe_layer_desc* desc, pto_moe_layer** out);
 PTO_API int pto_moe_layer_destroy(pto_moe_layer* layer); /* idempotent on NULL */
-PTO_API int pto_moe_layer_peer_exchange(const pto_moe_layer* layer); /* 1: results return through peer memory */
+PTO_API int pto_moe_layer_peer_exchange(const pto_moe_layer* layer); /* 0: collectives; 1: results return through peer
+                                                                       * memory; 2 (PTO_EP_PEER=2 on every rank): the
+                                                                       * dispatched rows go out through it as well */
 /* x bf16 [tokens, hidden] -> y bf16 [tokens, hidden].  idx_in / w_in (int32 / fp32 [tokens, topk], both or
  * neither) replace the layer's own routing; idx_out / w_out (may be NULL) receive the routing used.  phase_ms
  * (host float[8] or NULL) receives the device time of route+quantise, plan, pack, exchange out, unpack, experts,

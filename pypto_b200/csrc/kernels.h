@@ -108,6 +108,7 @@ int moe_push_rows_launch(const void* rows, int row_bytes, const int32_t* recv_co
                          const int32_t* dst_base, const MoePeerTable& peers, int my_rank, int step, long long dst_rows,
                          long long rows_hint, int* done_counter, int* err, cudaStream_t stream);
 int moe_wait_flags_launch(const int32_t* flags, int world, int step, int* err, cudaStream_t stream);
+int moe_recv_bases_launch(const int32_t* recv_counts, int world, int local_experts, int32_t* base, cudaStream_t stream);
 int moe_combine_launch(const void* rows, const int32_t* pos, const void* shared, int tokens, int topk, int hidden,
                        long long n_rows, void* y_bf16, float* y_f32, cudaStream_t stream);
 

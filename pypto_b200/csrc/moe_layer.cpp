@@ -65,12 +65,15 @@ struct pto_moe_layer {
   cudaStream_t side = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_counts = nullptr, ev_whole = nullptr;
   cudaEvent_t ev_phase[pto::kPhases + 1] = {};
-  // peer-memory return path
+  // peer-memory paths: 1 = the way back, 2 = the way out as well
   bool peer = false;
+  int peer_level = 0;
   int step = 0;                     // forward calls so far: the value this rank's flags are raised to
   int32_t *flags = nullptr, *done_counter = nullptr, *base_send = nullptr, *base_recv = nullptr;   // in the arena
+  int32_t *flags_out = nullptr, *done_counter_out = nullptr, *obase_send = nullptr, *obase_recv = nullptr;
   void* peer_arena[pto::kMoeMaxPeers] = {};   // other ranks' arenas as mapped here (NULL for this rank)
-  pto::MoePeerTable peers = {};
+  pto::MoePeerTable peers = {};       // result buffers and return flags of every rank
+  pto::MoePeerTable peers_out = {};   // receive buffers and arrival flags of every rank
 };
 
 namespace pto {
@@ -93,16 +96,17 @@ int experts_ffn(pto_moe_layer* L, const void* w_gu, const float* s_gu, const voi
 // node, no peer access, PTO_EP_PEER=0 on some rank) leaves every rank on the collective, all alike.
 struct PeerHello {
   cudaIpcMemHandle_t handle;
-  unsigned long long arena_bytes, back_off, flags_off;
-  int want;
-  char pad[128 - sizeof(cudaIpcMemHandle_t) - 3 * sizeof(unsigned long long) - sizeof(int)];
+  unsigned long long arena_bytes, back_off, flags_off, recv_off, flags_out_off;
+  int want;                         // 0: the collectives; 1: results return through peer memory; 2: rows go out that way too
+  char pad[128 - sizeof(cudaIpcMemHandle_t) - 5 * sizeof(unsigned long long) - sizeof(int)];
 };
 static_assert(sizeof(PeerHello) == 128, "one hello per rank, 128 bytes");
 
 int peer_setup(pto_moe_layer* L, size_t arena_bytes) {
   const int W = L->world;
   const char* env = getenv("PTO_EP_PEER");
-  int want = (env == nullptr || atoi(env) != 0) && W <= kMoeMaxPeers ? 1 : 0;
+  int want = env == nullptr ? 1 : atoi(env);
+  want = W > kMoeMaxPeers || want < 0 ? 0 : (want > 2 ? 2 : want);
   PeerHello mine = {};
   if (want && cudaIpcGetMemHandle(&mine.handle, L->arena) != cudaSuccess) {
     (void)cudaGetLastError();
@@ -111,6 +115,8 @@ int peer_setup(pto_moe_layer* L, size_t arena_bytes) {
   mine.arena_bytes = arena_bytes;
   mine.back_off = static_cast<unsigned long long>(L->back - L->arena);
   mine.flags_off = static_cast<unsigned long long>(reinterpret_cast<uint8_t*>(L->flags) - L->arena);
+  mine.recv_off = static_cast<unsigned long long>(L->recv_buf - L->arena);
+  mine.flags_out_off = static_cast<unsigned long long>(reinterpret_cast<uint8_t*>(L->flags_out) - L->arena);
   mine.want = want;
   std::vector<PeerHello> out(W, mine), in(W);
   uint8_t* dev = nullptr;
@@ -121,9 +127,11 @@ int peer_setup(pto_moe_layer* L, size_t arena_bytes) {
   if (st != kOk) return st;
   PTO_CUDA(cudaStreamSynchronize(nullptr));
   PTO_CUDA(cudaMemcpy(in.data(), dev + sizeof(PeerHello) * W, sizeof(PeerHello) * W, cudaMemcpyDeviceToHost));
-  int ok = want;
+  int ok = want > 0, level = want;
   for (int r = 0; r < W && ok; ++r) {
-    if (!in[r].want || in[r].arena_bytes != arena_bytes || in[r].back_off != mine.back_off || in[r].flags_off != mine.flags_off) {
+    if (in[r].want < level) level = in[r].want;   // the most cautious rank decides
+    if (!in[r].want || in[r].arena_bytes != arena_bytes || in[r].back_off != mine.back_off || in[r].flags_off != mine.flags_off ||
+        in[r].recv_off != mine.recv_off || in[r].flags_out_off != mine.flags_out_off) {
       ok = 0;                                   // a rank that refuses, or a layer of another shape
       break;
     }
@@ -155,8 +163,11 @@ int peer_setup(pto_moe_layer* L, size_t arena_bytes) {
     uint8_t* base = r == L->rank ? L->arena : static_cast<uint8_t*>(L->peer_arena[r]);
     L->peers.back[r] = base + mine.back_off;
     L->peers.flags[r] = reinterpret_cast<int32_t*>(base + mine.flags_off);
+    L->peers_out.back[r] = base + mine.recv_off;
+    L->peers_out.flags[r] = reinterpret_cast<int32_t*>(base + mine.flags_out_off);
   }
   L->peer = true;
+  L->peer_level = level;
   return kOk;
 }
 
@@ -224,8 +235,9 @@ int pto_moe_layer_create(const pto_moe_layer_desc* desc, pto_moe_layer** out) {
       {(void**)&L->y_g, (size_t)(C * H * 2)}, {(void**)&L->back, world > 1 ? (size_t)(routes * H * 2) : 0},
       {(void**)&L->sh_act, d.sh_w_gu ? (size_t)(T * I * 2) : 0}, {(void**)&L->sh_act_q, d.sh_w_gu ? (size_t)(T * I) : 0},
       {(void**)&L->sh_act_s, d.sh_w_gu ? (size_t)(T * (I / 128) * 4) : 0}, {(void**)&L->sh_out, d.sh_w_gu ? (size_t)(T * H * 2) : 0},
-      {(void**)&L->flags, 256}, {(void**)&L->done_counter, 256}, {(void**)&L->base_send, (size_t)(world * 4)},
-      {(void**)&L->base_recv, (size_t)(world * 4)}};
+      {(void**)&L->flags, 256}, {(void**)&L->done_counter, 256}, {(void**)&L->flags_out, 256}, {(void**)&L->done_counter_out, 256},
+      {(void**)&L->base_send, (size_t)(world * 4)}, {(void**)&L->base_recv, (size_t)(world * 4)},
+      {(void**)&L->obase_send, (size_t)(world * 4)}, {(void**)&L->obase_recv, (size_t)(world * 4)}};
   size_t total = 0;
   for (auto& s : slots) total += al256(s.bytes ? s.bytes : 1);
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&L->arena), total);
@@ -236,7 +248,7 @@ int pto_moe_layer_create(const pto_moe_layer_desc* desc, pto_moe_layer** out) {
     off += al256(s.bytes ? s.bytes : 1);
   }
   int st = check_cuda(cudaMemset(L->err, 0, 256), "cudaMemset");
-  if (st == kOk) st = check_cuda(cudaMemset(L->flags, 0, 512), "cudaMemset");   // flags and the push kernel's counter
+  if (st == kOk) st = check_cuda(cudaMemset(L->flags, 0, 1024), "cudaMemset");   // both flag arrays and the push kernels' counters
   if (st == kOk) st = check_cuda(cudaMallocHost(reinterpret_cast<void**>(&L->host_counts), (2 * E + 2) * 4), "cudaMallocHost");
   if (st == kOk) st = check_cuda(cudaMallocHost(reinterpret_cast<void**>(&L->host_whole), 16), "cudaMallocHost");
   if (st == kOk) st = check_cuda(cudaStreamCreateWithFlags(&L->side, cudaStreamNonBlocking), "cudaStreamCreate");
@@ -251,7 +263,7 @@ int pto_moe_layer_create(const pto_moe_layer_desc* desc, pto_moe_layer** out) {
   return kOk;
 }
 
-int pto_moe_layer_peer_exchange(const pto_moe_layer* L) { return L && L->peer ? 1 : 0; }
+int pto_moe_layer_peer_exchange(const pto_moe_layer* L) { return L && L->peer ? L->peer_level : 0; }
 
 int pto_moe_layer_status(pto_moe_layer* L, int32_t out4[4], void* stream) {
   using namespace pto;
@@ -352,10 +364,19 @@ int pto_moe_layer_forward(pto_moe_layer* L, const void* x, int tokens, const int
     st = pto_all_to_all(d.comm, L->counts, L->recv_counts, static_cast<size_t>(Le) * 4, s);
     if (st != kOk) return st;
     if (L->peer) {
+      ++L->step;
       // where, in MY sorted result buffer, the block of each destination rank begins: offsets[r * Le]
       PTO_CUDA(cudaMemcpy2DAsync(L->base_send, 4, L->offsets, static_cast<size_t>(Le) * 4, 4, W, cudaMemcpyDeviceToDevice, s));
       st = pto_all_to_all(d.comm, L->base_send, L->base_recv, 4, s);
       if (st != kOk) return st;
+      if (L->peer_level >= 2) {
+        // and where, in each destination's receive buffer, MY block begins: the destination knows (rows of the
+        // ranks before me) and tells
+        st = moe_recv_bases_launch(L->recv_counts, W, Le, L->obase_send, s);
+        if (st != kOk) return st;
+        st = pto_all_to_all(d.comm, L->obase_send, L->obase_recv, 4, s);
+        if (st != kOk) return st;
+      }
     }
     PTO_CUDA(cudaMemcpyAsync(L->host_counts, L->offsets, (E + 1) * 4, cudaMemcpyDeviceToHost, s));
     PTO_CUDA(cudaMemcpyAsync(L->host_counts + E + 1, L->recv_counts, E * 4, cudaMemcpyDeviceToHost, s));
@@ -381,8 +402,18 @@ int pto_moe_layer_forward(pto_moe_layer* L, const void* x, int tokens, const int
       arrived += n;
     }
     if (arrived > L->capacity) return fail(kInvalidArgument, "moe_layer_forward: more rows arrive than the layer was sized for");
-    st = pto_all_to_all_v(d.comm, L->send_buf, send_rows.data(), L->recv_buf, recv_rows.data(), L->payload, s);
-    if (st != kOk) return st;
+    if (L->peer && L->peer_level >= 2) {
+      // the packed rows of every destination straight into that destination's receive buffer, then the flags; the
+      // unpack below starts once every rank's flag here shows this step
+      st = moe_push_rows_launch(L->send_buf, static_cast<int>(L->payload), L->counts, W, Le, L->obase_recv, L->peers_out, L->rank,
+                                L->step, L->capacity, routes, L->done_counter_out, L->err, s);
+      if (st != kOk) return st;
+      st = moe_wait_flags_launch(L->flags_out, W, L->step, L->err, s);
+      if (st != kOk) return st;
+    } else {
+      st = pto_all_to_all_v(d.comm, L->send_buf, send_rows.data(), L->recv_buf, recv_rows.data(), L->payload, s);
+      if (st != kOk) return st;
+    }
     if ((st = mark()) != kOk) return st;   // exchange_out
     st = moe_recv_plan_launch(L->recv_counts, W, Le, 0, static_cast<int>(arrived > 0 ? arrived : 1), L->counts2, L->offsets2,
                               L->arrival_of, L->grouped_of, L->err, s);
@@ -407,7 +438,6 @@ int pto_moe_layer_forward(pto_moe_layer* L, const void* x, int tokens, const int
     if (L->peer) {
       // every source's block of result rows straight into that source's sorted buffer, then the flags; the combine
       // below starts once every rank's flag here shows this step
-      ++L->step;
       st = moe_push_rows_launch(L->y_g, H * 2, L->recv_counts, W, Le, L->base_recv, L->peers, L->rank, L->step,
                                 static_cast<long long>(d.max_tokens) * K, arrived, L->done_counter, L->err, s);
       if (st != kOk) return st;

@@ -531,6 +531,20 @@ moe_push_rows_kernel(const uint8_t* __restrict__ rows, int row_bytes, const int3
   }
 }
 
+// base[s] = rows that arrive here from the ranks before s (recv_counts int32 [world][local_experts]): where the block
+// of source s begins in this rank's receive buffer.
+__global__ void __launch_bounds__(32)
+moe_recv_bases_kernel(const int32_t* __restrict__ recv_counts, int world, int local_experts, int32_t* __restrict__ base) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x != 0) return;
+  int run = 0;
+  for (int s = 0; s < world; ++s) {
+    base[s] = run;
+    for (int e = 0; e < local_experts; ++e) run += recv_counts[s * local_experts + e];
+  }
+}
+
 // One warp: lane r waits (bounded) until rank r has raised its flag here to `step`.
 __global__ void __launch_bounds__(32)
 moe_wait_flags_kernel(const int32_t* __restrict__ flags, int world, int step, int* err) {
@@ -701,6 +715,12 @@ int moe_push_rows_launch(const void* rows, int row_bytes, const int32_t* recv_co
   launch_kernel(moe_push_rows_kernel, dim3(grid_rows(rows_hint, 8)), dim3(256), 0, stream, static_cast<const uint8_t*>(rows),
                 row_bytes, recv_counts, world, local_experts, dst_base, peers, my_rank, step, dst_rows, done_counter, err);
   return check_cuda(cudaGetLastError(), "moe_push_rows_kernel launch");
+}
+
+int moe_recv_bases_launch(const int32_t* recv_counts, int world, int local_experts, int32_t* base, cudaStream_t stream) {
+  PTO_REQUIRE(recv_counts && base && world >= 1 && local_experts >= 1, "moe_recv_bases: bad argument");
+  launch_kernel(moe_recv_bases_kernel, dim3(1), dim3(32), 0, stream, recv_counts, world, local_experts, base);
+  return check_cuda(cudaGetLastError(), "moe_recv_bases_kernel launch");
 }
 
 int moe_wait_flags_launch(const int32_t* flags, int world, int step, int* err, cudaStream_t stream) {

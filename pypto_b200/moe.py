@@ -286,9 +286,15 @@ class MoELayer:
     def peer_exchange(self) -> bool:
         """True when the experts' results return through peer memory (the library's own kernel and flags) instead of
         an all-to-all: every rank could map every other rank's buffers when the layer was created."""
+        return self.peer_exchange_level > 0
+
+    @property
+    def peer_exchange_level(self) -> int:
+        """0: both exchanges are collectives; 1: results return through peer memory; 2: rows go out that way too
+        (``PTO_EP_PEER=2`` on every rank)."""
         from . import _lib
         h = getattr(self, "_handle", None)
-        return bool(h is not None and _lib.load().pto_moe_layer_peer_exchange(h))
+        return int(_lib.load().pto_moe_layer_peer_exchange(h)) if h is not None else 0
 
     def status(self) -> tuple:
         """The layer's device error word (code, site, CTA, detail); reading clears it."""
