@@ -1,6 +1,8 @@
-"""Expert-parallel MoE on 2, 4 and 8 GPUs (one process per GPU; dispatch and combine through the library's
-NCCL communicator): every rank's output must equal the oracle's single-process result for its token slice.
-Each world size is skipped when fewer GPUs are visible."""
+"""Expert-parallel MoE on 2, 4 and 8 GPUs (one process per GPU): every rank's output must equal the oracle's
+single-process result for its token slice.  Rows travel through the library's NCCL communicator, through peer memory
+on the way back (the default on one node), or through peer memory both ways (PTO_EP_PEER = 0 / 1 / 2, set in every
+rank); each case checks that the layer reports the path it was asked for.  Each world size is skipped when fewer GPUs
+are visible."""
 
 import os
 import queue
@@ -18,9 +20,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SHAPE = dict(tokens=256, hidden=7168, inter=256, experts=16, topk=4)
 
 
-def _worker(rank, world, uid, case_path, q):
+def _worker(rank, world, uid, case_path, peer, q):
     try:
         sys.path.insert(0, ROOT)
+        if peer is not None:
+            os.environ["PTO_EP_PEER"] = str(peer)
         from pypto_b200 import ops
         from pypto_b200.comm import Communicator
         from pypto_b200.moe import MoELayer, PhaseTimer
@@ -46,7 +50,8 @@ def _worker(rank, world, uid, case_path, q):
             phases = timer.result()
             same = (idx2.cpu() == idx_exp[sl]).all(dim=1)
             rel2 = ((y2.cpu().float()[same] - y_exp[sl].float()[same]).norm() / y_exp[sl].float()[same].norm()).item()
-            q.put((rank, "ok", rel, rel2, float(same.float().mean()), status[0] or side_status[0], sorted(phases)))
+            q.put((rank, "ok", rel, rel2, float(same.float().mean()), status[0] or side_status[0], sorted(phases),
+                   layer.peer_exchange_level))
         finally:
             comm.close()
     except BaseException:
@@ -101,13 +106,14 @@ def oracle_case(tmp_path_factory):
     return path
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_expert_parallel_layer_matches_oracle(world, oracle_case):
+@pytest.mark.parametrize("world,peer", [(2, None), (4, None), (8, None), (2, 0), (2, 2), (4, 2)])
+def test_expert_parallel_layer_matches_oracle(world, peer, oracle_case):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from pypto_b200 import comm
-    results = run_ranks(_worker, world, args=(comm.unique_id(), oracle_case))
-    for rank, _ok, rel, rel2, frac_same, status, phases in results:
+    results = run_ranks(_worker, world, args=(comm.unique_id(), oracle_case, peer))
+    for rank, _ok, rel, rel2, frac_same, status, phases, level in results:
         assert status == 0
+        assert level == (1 if peer is None else peer), (rank, level)      # one node: every rank maps every other
         assert rel < 2e-2 and rel2 < 2e-2 and frac_same > 0.97, (rank, rel, rel2, frac_same)
         assert {"plan", "pack", "exchange_out", "unpack", "experts", "exchange_back", "combine"} <= set(phases)
