@@ -105,7 +105,7 @@ def sigmoid(x):
 
 _UNARY = {"exp", "recip", "sqrt", "rsqrt", "relu", "abs", "log", "tanh"}
 _PASS_THROUGH = {"move", "reshape", "view", "assemble"}          # change layout or placement, not values
-_FRESH = {"create_tensor", "create_tile", "zeros_like", "empty"}  # scratch to be written later
+_FRESH = {"create_tensor", "create_tile", "create", "zeros_like", "empty"}  # scratch to be written later
 
 
 class _Evaluator:
@@ -142,7 +142,10 @@ class _Evaluator:
         if fn is not None:
             return self.kernel_call(fn, node, env)
         f = node.func
-        if not (isinstance(f, ast.Attribute) and isinstance(f.value, ast.Name) and f.value.id in ("pl", "pld")):
+        root = f.value if isinstance(f, ast.Attribute) else None
+        if isinstance(root, ast.Attribute) and root.attr in ("tile", "tensor") and isinstance(root.value, ast.Name):
+            root = root.value                           # pl.tile.<op> / pl.tensor.<op>: the same operations, namespaced
+        if not (isinstance(root, ast.Name) and root.id in ("pl", "pld")):
             raise _GiveUp(f"call '{ast.unparse(f)}' is not a DSL operation")
         op, a = f.attr, node.args
         if op == "load":

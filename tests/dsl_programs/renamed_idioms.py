@@ -101,3 +101,35 @@ def affine(offset: pl.Tensor, lhs: pl.Tensor, rhs: pl.Tensor, dst: pl.Out[pl.Ten
     tmp = product_kernel(lhs, rhs, tmp)
     dst = shift_kernel(tmp, offset, dst)
     return dst
+
+
+@pl.program
+class GatedMlpProgram:
+    """The gated MLP as a @pl.program class: kernels are methods, the orchestration calls them through `self`."""
+
+    @pl.function(type=pl.FunctionType.InCore)
+    def mm(self, p: pl.Tensor[[64, 64], pl.FP32], q: pl.Tensor[[64, 64], pl.FP32],
+           r: pl.Out[pl.Tensor[[64, 64], pl.FP32]]) -> pl.Tensor[[64, 64], pl.FP32]:
+        acc = pl.matmul(pl.load(p, [0, 0], [64, 64]), pl.load(q, [0, 0], [64, 64]))
+        pl.store(acc, [0, 0], r)
+        return r
+
+    @pl.function(type=pl.FunctionType.InCore)
+    def act(self, g: pl.Tensor[[64, 64], pl.FP32], u: pl.Tensor[[64, 64], pl.FP32],
+            r: pl.Out[pl.Tensor[[64, 64], pl.FP32]]) -> pl.Tensor[[64, 64], pl.FP32]:
+        tg = pl.tile.load(g, [0, 0], [64, 64])
+        sig = pl.recip(pl.add(pl.exp(pl.neg(tg)), 1.0))
+        pl.store(pl.mul(pl.mul(tg, sig), pl.load(u, [0, 0], [64, 64])), [0, 0], r)
+        return r
+
+    @pl.function(type=pl.FunctionType.Orchestration)
+    def run(self, inp: pl.Tensor[[64, 64], pl.FP32], wa: pl.Tensor[[64, 64], pl.FP32], wb: pl.Tensor[[64, 64], pl.FP32],
+            wc: pl.Tensor[[64, 64], pl.FP32], res: pl.Out[pl.Tensor[[64, 64], pl.FP32]]) -> pl.Tensor[[64, 64], pl.FP32]:
+        ga = pl.tensor.create([64, 64], dtype=pl.FP32)
+        ga = self.mm(inp, wa, ga)
+        ub = pl.tensor.create([64, 64], dtype=pl.FP32)
+        ub = self.mm(inp, wb, ub)
+        h = pl.tensor.create([64, 64], dtype=pl.FP32)
+        h = self.act(ga, ub, h)
+        res = self.mm(h, wc, res)
+        return res

@@ -19,6 +19,14 @@ def test_swiglu_ffn_is_recognised_under_other_names_orders_and_spellings():
     assert op.matches(progs.gated_mlp) and not op.matches(progs.relu_mlp)
 
 
+def test_a_program_class_with_kernel_methods_is_followed_through_self():
+    prog = progs.GatedMlpProgram
+    rec = idioms.recognise(prog.entry, prog)
+    assert rec is not None and rec.idiom == "ffn_swiglu"
+    assert rec.roles == {"x": "inp", "w_gate": "wa", "w_up": "wb", "w_down": "wc", "out": "res"}
+    assert ir.compile(prog, platform="b200").op_names == ("ffn_swiglu",)
+
+
 def test_rms_norm_is_recognised_with_its_constants():
     rec = idioms.recognise(progs.scaled_norm)
     assert rec is not None and rec.idiom == "rms_norm"
