@@ -232,6 +232,15 @@ PTO_API int pto_ffn_swiglu_f32(const float* x, const void* w_gate_up, const void
                                int inter, int n_out, void* workspace, size_t workspace_bytes, int accumulate,
                                int32_t* err, void* stream);
 
+/* One-projection FFN with an elementwise activation: out[m, n_out] (+)= bf16(f(x W_in)) W_down, with
+ * kind 1: f(h) = h * sigmoid(alpha h) (alpha = 1.702 is `ffn_gelu`, examples/models/01_ffn.py:51-62, 92-108), or
+ * kind 2: f(h) = max(h, 0) (`ffn_relu`, :80-86, 134-150).  x bf16 [m, k]; w_in packed [inter, k]; w_down packed
+ * [n_out, inter]; out fp32.  Workspace: pto_ffn_act_workspace_bytes(m, inter), 256-byte aligned. */
+PTO_API size_t pto_ffn_act_workspace_bytes(int m, int inter);
+PTO_API int pto_ffn_act(const void* x, const void* w_in, const void* w_down, void* out, int m, int k, int inter,
+                        int n_out, int kind, float alpha, void* workspace, size_t workspace_bytes, int accumulate,
+                        int32_t* err, void* stream);
+
 /* ---- decoder-layer glue ---- */
 
 /* out = x * rsqrt(mean(x^2) + eps) * gamma, fp32 statistics; x and out fp32 or bf16, gamma

@@ -71,6 +71,8 @@ SIGNATURES = {
     "pto_linear": (_i, [_p, _p, _p, _i, _i, _i, _i, _p, _p]),
     "pto_ffn_swiglu_workspace_bytes": (_sz, [_i, _i]),
     "pto_ffn_swiglu": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p, _sz, _i, _p, _p]),
+    "pto_ffn_act_workspace_bytes": (_sz, [_i, _i]),
+    "pto_ffn_act": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, C.c_float, _p, _sz, _i, _p, _p]),
     "pto_ffn_swiglu_f32_workspace_bytes": (_sz, [_i, _i, _i]),
     "pto_ffn_swiglu_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _p, _sz, _i, _p, _p]),
     "pto_rms_norm": (_i, [_p, _i, _p, _p, _i, _i64, _i, _f, _p]),

@@ -152,6 +152,20 @@ __global__ void swiglu_act_kernel(const float* __restrict__ gate_up, __nv_bfloat
   }
 }
 
+// act[i] = bf16(f(h[i])) with f = x * sigmoid(alpha * x) (kind 1: alpha = 1.702 is the GELU of
+// examples/models/01_ffn.py:51-62, alpha = 1 is SiLU; the sigmoid as recip(1 + exp(-alpha x)) like the reference's
+// kernel) or f = max(x, 0) (kind 2, relu_kernel, :80-86).
+__global__ void act_rows_kernel(const float* __restrict__ h, __nv_bfloat16* __restrict__ act, long long n, int kind,
+                                float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float x = h[i];
+    act[i] = __float2bfloat16_rn(kind == 2 ? fmaxf(x, 0.f) : x * (1.f / (1.f + __expf(-alpha * x))));
+  }
+}
+
 // out = cast(in); optional side job of the same launch: `zero` (16-byte aligned, zero_vec uint4 words) is
 // cleared, e.g. the fp32 accumulator of the GEMM that follows.
 template <typename TI, typename TO>
@@ -248,6 +262,13 @@ int swiglu_act_launch(const float* gate_up, void* act, long long rows, int inter
   if (rows == 0) return kOk;
   launch_kernel(swiglu_act_kernel, dim3(grid_for(rows * inter, 256)), dim3(256), 0, stream, gate_up, static_cast<__nv_bfloat16*>(act), rows, inter);
   return check_cuda(cudaGetLastError(), "swiglu_act_kernel launch");
+}
+
+int act_rows_launch(const float* h, void* act, long long n, int kind, float alpha, cudaStream_t stream) {
+  PTO_REQUIRE(h && act && n >= 0 && (kind == 1 || kind == 2), "act_rows: bad arguments (kind 1 = x sigmoid(alpha x), 2 = relu)");
+  if (n == 0) return kOk;
+  launch_kernel(act_rows_kernel, dim3(grid_for(n, 256)), dim3(256), 0, stream, h, static_cast<__nv_bfloat16*>(act), n, kind, alpha);
+  return check_cuda(cudaGetLastError(), "act_rows_kernel launch");
 }
 
 int cast_launch(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream) {

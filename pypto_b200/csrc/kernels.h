@@ -47,6 +47,10 @@ int linear_launch(const void* x, const void* w_packed, float* out, int m, int n,
                   cudaStream_t stream);
 size_t ffn_workspace_bytes(int m, int inter);
 size_t ffn_f32_workspace_bytes(int m, int k, int inter);
+size_t ffn_act_workspace_bytes(int m, int inter);
+int ffn_act_launch(const void* x, const void* w_in, const void* w_down, float* out, int m, int k, int inter, int n_out,
+                   int kind, float alpha, void* workspace, size_t workspace_bytes, int accumulate, int* err,
+                   cudaStream_t stream);
 int ffn_swiglu_f32_launch(const float* x, const void* w_gate_up, const void* w_down, float* out, int m, int k, int inter,
                           int n_out, void* workspace, size_t workspace_bytes, int accumulate, int* err,
                           cudaStream_t stream);
@@ -76,6 +80,7 @@ int llama_mini_launch(const float* hidden, const float* mask, const float* cos_e
                       const float* w_down, const float* w_lm, float* logits, int seq_len, int head_dim, int vocab,
                       cudaStream_t stream);
 int cast_launch(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream);
+int act_rows_launch(const float* h, void* act, long long n, int kind, float alpha, cudaStream_t stream);
 int cast_zero_launch(const void* in, int in_dtype, void* out, int out_dtype, long long n, void* zero,
                      size_t zero_bytes, cudaStream_t stream);
 int pack_weight_launch(const void* src, int src_dtype, void* dst, int k, int n, cudaStream_t stream);

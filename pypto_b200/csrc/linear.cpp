@@ -78,6 +78,33 @@ size_t ffn_workspace_bytes(int m, int inter) {
   return chain > fused ? chain : fused;
 }
 
+// One-projection FFN with an elementwise activation: out (+)= bf16(f(x W_in)) W_down, f = x sigmoid(alpha x)
+// (kind 1; alpha 1.702: `ffn_gelu`, examples/models/01_ffn.py:92-108) or relu (kind 2; `ffn_relu`, :134-150).
+// x bf16 [m, k], w_in packed [inter, k], w_down packed [n_out, inter].  Three launches: GEMM, activation, GEMM.
+// Workspace: fp32 [m, inter] and bf16 [m, inter].
+size_t ffn_act_workspace_bytes(int m, int inter) {
+  const size_t n = static_cast<size_t>(m) * inter;
+  return (n * 4 + 255) / 256 * 256 + (n * 2 + 255) / 256 * 256;
+}
+
+int ffn_act_launch(const void* x, const void* w_in, const void* w_down, float* out, int m, int k, int inter, int n_out,
+                   int kind, float alpha, void* workspace, size_t workspace_bytes, int accumulate, int* err,
+                   cudaStream_t stream) {
+  PTO_REQUIRE(x && w_in && w_down && out && workspace, "ffn_act: NULL tensor");
+  PTO_REQUIRE(m > 0 && k > 0 && inter > 0 && n_out > 0 && k % 8 == 0 && inter % 8 == 0,
+              "ffn_act: sizes must be positive, k and inter multiples of 8");
+  PTO_REQUIRE(workspace_bytes >= ffn_act_workspace_bytes(m, inter), "ffn_act: workspace too small");
+  PTO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "ffn_act: workspace must be 256-byte aligned");
+  const size_t n = static_cast<size_t>(m) * inter;
+  float* h = static_cast<float*>(workspace);
+  void* act = static_cast<uint8_t*>(workspace) + (n * 4 + 255) / 256 * 256;
+  int st = linear_launch(x, w_in, h, m, inter, k, 0, err, stream);
+  if (st != kOk) return st;
+  st = act_rows_launch(h, act, static_cast<long long>(n), kind, alpha, stream);
+  if (st != kOk) return st;
+  return linear_launch(act, w_down, out, m, n_out, inter, accumulate, err, stream);
+}
+
 // The same for fp32 x: the workspace of the bf16 form followed by a bf16 copy of x.
 size_t ffn_f32_workspace_bytes(int m, int k, int inter) {
   return (ffn_workspace_bytes(m, inter) + 255) / 256 * 256 + (static_cast<size_t>(m) * k * 2 + 255) / 256 * 256;

@@ -153,11 +153,46 @@ struct OpEntry {
   OpFn fn;
 };
 
+// The reference's ffn_gelu / ffn_relu signatures (examples/models/01_ffn.py:92-108, 134-150): fp32 (or bf16 x),
+// weights in the x @ W layout.  tensors: x [m, k], w_in [k, i], w_down [i, n], out [m, n];
+// scalars: kind (1: x * sigmoid(alpha x), 2: relu), alpha as fp32 bits.  Operands are cast / packed per call.
+int op_ffn_act(Worker* w, const pto_task_args* a) {
+  if (a->n_tensors != 4 || a->n_scalars != 2) return fail(kInvalidArgument, "ffn_act: expects 4 tensors and 2 scalars");
+  const pto_chip_tensor* t = a->tensors;
+  for (int i = 0; i < 4; ++i)
+    if (t[i].ndims != 2 || (t[i].dtype != PTO_FP32 && !(i < 3 && t[i].dtype == PTO_BF16)))
+      return fail(kInvalidArgument, "ffn_act: 2-D fp32 (or bf16 input) tensors expected, fp32 output");
+  const int m = t[0].shapes[0], k = t[0].shapes[1], inter = t[1].shapes[1], n = t[2].shapes[1];
+  if ((int)t[1].shapes[0] != k || (int)t[2].shapes[0] != inter || (int)t[3].shapes[0] != m || (int)t[3].shapes[1] != n)
+    return fail(kInvalidArgument, "ffn_act: operand shapes do not chain");
+  const int kind = static_cast<int>(a->scalars[0]);
+  const uint32_t bits = static_cast<uint32_t>(a->scalars[1]);
+  float alpha;
+  memcpy(&alpha, &bits, 4);
+  auto al = [](size_t v) { return (v + 255) / 256 * 256; };
+  const size_t x_b = al((size_t)m * k * 2), in_b = al((size_t)inter * k * 2), d_b = al((size_t)n * inter * 2);
+  const size_t ws_b = ffn_act_workspace_bytes(m, inter);
+  int st = w->ensure_scratch(4096 + x_b + in_b + d_b + ws_b);
+  if (st != kOk) return st;
+  uint8_t* base = static_cast<uint8_t*>(w->scratch) + 4096;
+  void* xb = base; void* wi = base + x_b; void* wd = base + x_b + in_b; void* ws = base + x_b + in_b + d_b;
+  if (t[0].dtype == PTO_FP32) st = cast_launch(tptr(t[0], 4), PTO_FP32, xb, PTO_BF16, (long long)m * k, w->stream);
+  else st = check_cuda(cudaMemcpyAsync(xb, tptr(t[0], 2), (size_t)m * k * 2, cudaMemcpyDeviceToDevice, w->stream), "copy x");
+  if (st != kOk) return st;
+  st = pack_weight_launch(tptr(t[1], dtype_bytes(t[1].dtype)), (int)t[1].dtype, wi, k, inter, w->stream);
+  if (st != kOk) return st;
+  st = pack_weight_launch(tptr(t[2], dtype_bytes(t[2].dtype)), (int)t[2].dtype, wd, inter, n, w->stream);
+  if (st != kOk) return st;
+  return ffn_act_launch(xb, wi, wd, static_cast<float*>(tptr(t[3], 4)), m, k, inter, n, kind, alpha, ws, ws_b, 0,
+                        static_cast<int*>(w->scratch), w->stream);
+}
+
 const OpEntry kOps[] = {
     {"paged_attention", op_paged_attention},
     {"paged_gather", op_paged_gather},
     {"rms_norm", op_rms_norm},
     {"ffn_swiglu", op_ffn_swiglu},
+    {"ffn_act", op_ffn_act},
     {"linear", op_linear},
     {"rope_kv_append", op_rope_kv_append},
     {"scope3", op_scope3},
@@ -261,6 +296,17 @@ int pto_ffn_swiglu(const void* x, const void* w_gate_up, const void* w_down, voi
                    int n_out, void* workspace, size_t workspace_bytes, int accumulate, int32_t* err, void* stream) {
   return pto::ffn_swiglu_launch(x, w_gate_up, w_down, static_cast<float*>(out), m, k, inter, n_out, workspace,
                                 workspace_bytes, accumulate, err, static_cast<cudaStream_t>(stream));
+}
+
+size_t pto_ffn_act_workspace_bytes(int m, int inter) {
+  if (m <= 0 || inter <= 0) return 0;
+  return pto::ffn_act_workspace_bytes(m, inter);
+}
+
+int pto_ffn_act(const void* x, const void* w_in, const void* w_down, void* out, int m, int k, int inter, int n_out, int kind,
+                float alpha, void* workspace, size_t workspace_bytes, int accumulate, int32_t* err, void* stream) {
+  return pto::ffn_act_launch(x, w_in, w_down, static_cast<float*>(out), m, k, inter, n_out, kind, alpha, workspace,
+                             workspace_bytes, accumulate, err, static_cast<cudaStream_t>(stream));
 }
 
 size_t pto_ffn_swiglu_f32_workspace_bytes(int m, int k, int inter) {

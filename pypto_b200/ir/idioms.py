@@ -14,6 +14,10 @@ tensor and unifies that expression with the algebraic form of a fused operator:
 
       out = x / sqrt(c * row_sum(x * x) + eps) * gamma          (or  x * rsqrt(...) * gamma)
 
+* the one-projection FFNs of the same file (examples/models/01_ffn.py:51-62, 80-108, 134-150)::
+
+      out = f(x @ W_in) @ W_down,    f(h) = h * recip(1 + exp(-alpha h))  (GELU: alpha = 1.702)   or   f = relu
+
 * a matrix product, alone or with a full-size bias (examples/beginner/05_matmul.py:29-38,
   examples/intermediate/01_fused_linear.py:60-66)::
 
@@ -372,6 +376,17 @@ def recognise(entry: Function, program=None) -> Recognised | None:
             if r is not None:
                 return r
     if n_in == 3:
+        h = ("matmul", V("x"), V("w_in"))
+        for b in _unify(("matmul", mul(h, un("recip", add(C(1.0), un("exp", mul(V("#neg_alpha"), h))))), V("w_down")), expr, {}):
+            r = finish("ffn_act", b)
+            if r is not None and r.constants["neg_alpha"] < 0:
+                r.constants = {"kind": 1, "alpha": -r.constants["neg_alpha"]}
+                return r
+        for b in _unify(("matmul", un("relu", h), V("w_down")), expr, {}):
+            r = finish("ffn_act", b)
+            if r is not None:
+                r.constants = {"kind": 2}
+                return r
         for b in _unify(add(("matmul", V("a"), V("b")), V("bias")), expr, {}):
             r = finish("linear", b)
             if r is not None:

@@ -167,6 +167,44 @@ class FfnSwigluOp(FusedOp):
         worker.launch("ffn_swiglu", [dev[n] for n in self.names], [])
 
 
+class FfnActOp(FusedOp):
+    """``ffn_gelu`` / ``ffn_relu(hidden_states, gate_proj_weight, down_proj_weight, output)``
+    (examples/models/01_ffn.py:92-108, 134-150): one projection, an elementwise activation, the down projection --
+    by those names, or any program recognised as computing ``f(x @ W_in) @ W_down`` with f = h * sigmoid(alpha h) or
+    relu (ir/idioms.py), bound to its own parameter names."""
+
+    op_names = ("ffn_act",)
+    names = ("hidden_states", "gate_proj_weight", "down_proj_weight", "output")
+    KINDS = {"ffn_gelu": (1, 1.702), "ffn_relu": (2, 0.0)}
+
+    def __init__(self, entry=None, names=None, kind=None, alpha=0.0):
+        self.entry, self.kind, self.alpha = entry, kind, float(alpha)
+        if names is not None:
+            self.names = tuple(names)
+
+    def _kind(self, entry):
+        return (self.kind, self.alpha) if self.entry is not None else self.KINDS[entry.name]
+
+    def matches(self, entry) -> bool:
+        if self.entry is not None:
+            return entry is self.entry
+        return entry.name in self.KINDS and tuple(p.name for p in entry.params) == self.names
+
+    def plan(self, compiled, host, worker):
+        x, wi, wd, out = (host[n] for n in self.names)
+        if x.shape[1] != wi.shape[0] or wd.shape[0] != wi.shape[1] or tuple(out.shape) != (x.shape[0], wd.shape[1]):
+            raise ValueError("ffn_act: operand shapes do not chain")
+        if out.dtype != torch.float32:
+            raise TypeError("ffn_act: output must be float32")
+        if x.shape[1] % 8 or wi.shape[1] % 8:
+            raise ValueError("ffn_act: hidden and intermediate sizes must be multiples of 8")
+        kind, alpha = self._kind(compiled.entry)
+        return dict(scalars=[kind, _f32_bits(alpha)])
+
+    def launch(self, worker, dev, host, plan):
+        worker.launch("ffn_act", [dev[n] for n in self.names], plan["scalars"])
+
+
 class RmsNormOp(FusedOp):
     """``rms_norm(x, gamma, output)`` (examples/intermediate/03_normalization.py:34-65), eps 1e-5
     (tests/st/examples/02_intermediate/test_rms_norm.py:35)."""
@@ -339,7 +377,7 @@ class LlamaMiniOp(FusedOp):
         worker.launch("llama_mini", [dev[n] for n in self.names], [])
 
 
-REGISTRY: list[FusedOp] = [LlamaMiniOp(), PagedAttentionOp(), PagedAttentionSpmdOp(), PagedGatherOp(), FfnSwigluOp(), RmsNormOp(),
+REGISTRY: list[FusedOp] = [LlamaMiniOp(), PagedAttentionOp(), PagedAttentionSpmdOp(), PagedGatherOp(), FfnSwigluOp(), FfnActOp(), RmsNormOp(),
                            Qwen3DecodeOp(), Scope3Op(), MatmulMxOp()]
 
 
@@ -357,6 +395,9 @@ def from_idiom(entry, program=None) -> FusedOp | None:
         return RmsNormOp(entry, (r["x"], r["gamma"], r["out"]), eps=rec.constants.get("eps"), inv_n=rec.constants.get("inv_n"))
     if rec.idiom == "linear":
         return LinearOp(entry, r["a"], r["b"], r["out"], r.get("bias"))
+    if rec.idiom == "ffn_act":
+        return FfnActOp(entry, (r["x"], r["w_in"], r["w_down"], r["out"]), kind=int(rec.constants["kind"]),
+                        alpha=rec.constants.get("alpha", 0.0))
     return None
 
 

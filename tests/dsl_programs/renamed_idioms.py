@@ -133,3 +133,21 @@ class GatedMlpProgram:
         h = self.act(ga, ub, h)
         res = self.mm(h, wc, res)
         return res
+
+
+@pl.jit.incore
+def swish_kernel(t: pl.Tensor, dst: pl.Out[pl.Tensor]):
+    v = pl.load(t, [0, 0], [64, 64])
+    pl.store(pl.div(v, pl.add(pl.exp(pl.neg(v)), 1.0)), [0, 0], dst)
+    return dst
+
+
+@pl.jit
+def swish_mlp(w_b: pl.Tensor, tokens: pl.Tensor, w_a: pl.Tensor, y: pl.Out[pl.Tensor]):
+    """y = silu(tokens @ w_a) @ w_b: one projection and an activation, the shape of the reference's ffn_gelu."""
+    h = pl.create_tensor([64, 64], dtype=pl.FP32)
+    h = product_kernel(tokens, w_a, h)
+    a = pl.create_tensor([64, 64], dtype=pl.FP32)
+    a = swish_kernel(h, a)
+    y = product_kernel(a, w_b, y)
+    return y

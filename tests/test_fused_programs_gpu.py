@@ -115,3 +115,31 @@ def test_matrix_product_programs_run_on_the_tensor_core_gemm():
     progs.product(a, b, dst)
     exp = a.bfloat16().float() @ b.bfloat16().float()
     assert (dst - exp).abs().max() <= 2e-3 * exp.abs().max()
+
+
+def test_gelu_and_relu_ffns_by_name_and_by_body():
+    """`ffn_gelu` / `ffn_relu` with the reference's signature (examples/models/01_ffn.py:92-108, 134-150; 64 x 64 fp32,
+    N(0,1) weights as in :155-160) and a SiLU MLP under names of its own: the one-projection FFN (GEMM, activation,
+    GEMM) against the fp32 expressions, bf16 operands held to 2e-2 of the output scale."""
+    from tests.dsl_programs import renamed_idioms as progs
+
+    @pl.jit
+    def ffn_gelu(hidden_states: pl.Tensor, gate_proj_weight: pl.Tensor, down_proj_weight: pl.Tensor,
+                 output: pl.Out[pl.Tensor]):
+        ...
+
+    @pl.jit
+    def ffn_relu(hidden_states: pl.Tensor, gate_proj_weight: pl.Tensor, down_proj_weight: pl.Tensor,
+                 output: pl.Out[pl.Tensor]):
+        ...
+    torch.manual_seed(0)
+    x, wg, wd = torch.randn(64, 64), torch.randn(64, 64), torch.randn(64, 64)
+    for fn, exp in ((ffn_gelu, offn.ffn_gelu(x, wg, wd)), (ffn_relu, offn.ffn_relu(x, wg, wd))):
+        out = torch.zeros(64, 64)
+        fn(x, wg, wd, out)
+        assert (out - exp).abs().max() <= 2e-2 * exp.abs().max(), fn.name
+    x, wa, wb = torch.randn(200, 512) , torch.randn(512, 1024) * 0.05, torch.randn(1024, 256) * 0.05
+    y = torch.zeros(200, 256)
+    progs.swish_mlp(wb, x, wa, y)
+    exp = offn.ffn_gelu(x, wa, wb, alpha=1.0)
+    assert (y - exp).abs().max() <= 2e-2 * exp.abs().max()

@@ -47,6 +47,15 @@ def test_matrix_products_are_recognised_with_and_without_a_bias():
     assert ir.compile(progs.product, platform="b200").op_names == ("linear",)
 
 
+def test_one_projection_ffns_are_recognised_with_their_activation():
+    rec = idioms.recognise(progs.swish_mlp)
+    assert rec is not None and rec.idiom == "ffn_act" and rec.constants["kind"] == 1
+    assert rec.constants["alpha"] == pytest.approx(1.0)                      # plain SiLU
+    assert rec.roles == {"x": "tokens", "w_in": "w_a", "w_down": "w_b", "out": "y"}
+    op = fused_programs.from_idiom(progs.swish_mlp)
+    assert op.op_names == ("ffn_act",) and op.names == ("tokens", "w_a", "w_b", "y")
+
+
 def test_what_is_not_an_idiom_is_refused():
     assert idioms.recognise(progs.relu_mlp) is None          # same shape of program, another activation
     assert idioms.recognise(progs.looped) is None            # a loop is not followed
@@ -73,7 +82,8 @@ def test_algebra_is_canonical():
 def test_the_reference_examples_are_recognised_by_their_bodies():
     """examples/models/01_ffn.py and examples/intermediate/03_normalization.py, loaded unchanged through the ``pypto``
     alias: the recogniser reads their kernels and finds the SwiGLU FFN and the RMSNorm without looking at names;
-    their GELU / ReLU FFNs and the layer norm are other computations and are refused."""
+    the GELU and ReLU FFNs of the same file go to the one-projection FFN; the layer norm has no fused operator and is
+    refused."""
     import importlib.util
     import os
 
@@ -94,7 +104,12 @@ def test_the_reference_examples_are_recognised_by_their_bodies():
     assert rec is not None and rec.idiom == "ffn_swiglu"
     assert rec.roles == {"x": "hidden_states", "w_gate": "gate_proj_weight", "w_up": "up_proj_weight",
                          "w_down": "down_proj_weight", "out": "output"}
-    assert idioms.recognise(ffn.ffn_gelu) is None and idioms.recognise(ffn.ffn_relu) is None
+    rec = idioms.recognise(ffn.ffn_gelu)
+    assert rec is not None and rec.idiom == "ffn_act" and rec.constants["kind"] == 1
+    assert rec.constants["alpha"] == pytest.approx(1.702)
+    assert rec.roles == {"x": "hidden_states", "w_in": "gate_proj_weight", "w_down": "down_proj_weight", "out": "output"}
+    rec = idioms.recognise(ffn.ffn_relu)
+    assert rec is not None and rec.idiom == "ffn_act" and rec.constants == {"kind": 2}
     norm = load("examples/intermediate/03_normalization.py", "ref_example_03_norm")
     rec = idioms.recognise(norm.rms_norm)
     assert rec is not None and rec.idiom == "rms_norm" and rec.roles == {"x": "x", "gamma": "gamma", "out": "output"}
