@@ -15,8 +15,11 @@
 // created; PTO_EP_PEER=0 turns it off), the way back is no collective at all: a kernel stores each source's block
 // of result rows straight into that source's sorted result buffer through peer memory and raises a flag there, and
 // the source's combine waits (bounded) for the flags of all ranks (moe_push_rows_kernel, moe_wait_flags_kernel).
-// The offset of a block in its source's buffer travels with the counts.  The way out stays an all-to-all-v: it is
-// what orders a rank's next step behind the combine of the ranks it writes to.
+// The offset of a block in its source's buffer travels with the counts.  With PTO_EP_PEER=2 on every rank the way
+// out works the same way (each destination tells its sources where their blocks begin in its receive buffer, the
+// same kernel stores the packed rows there, a second set of flags); by default it stays an all-to-all-v.  What orders
+// a rank's next step behind the combine of the ranks it writes to are the small all-to-alls of every step (counts,
+// offsets): every pair of ranks exchanges a word in them, and a rank enqueues them after its previous combine.
 //
 // The host waits once per step, for the row counts of the exchange (a pinned buffer and an event); everything
 // before that wait is already queued, so the GPU packs the payload and runs the shared expert meanwhile.
