@@ -252,11 +252,14 @@ def event_time(fn, n, warm=3):
 _measured: dict = {}
 
 
-def fp8_peak_tflops(dev):
+def fp8_peak_tflops(dev, refresh=False):
     """Dense FP8 tensor throughput of this GPU, measured the way the bf16 peak is: a library GEMM
-    (``torch._scaled_mm`` e4m3 x e4m3 -> bf16, 8192^3), best of 10.  None if that call is unavailable."""
-    if "fp8" in _measured:
+    (``torch._scaled_mm`` e4m3 x e4m3 -> bf16, 8192^3), best of 10.  None if that call is unavailable.
+    ``refresh`` measures again and keeps the LARGER figure: a burst measured right after seconds of power-capped work
+    reads hundreds of TFLOP/s low, and a peak that is too low flatters every fraction taken of it."""
+    if "fp8" in _measured and (not refresh or _measured["fp8"] is None):
         return _measured["fp8"]
+    before = _measured.get("fp8")
     try:
         n = 8192
         a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
@@ -268,9 +271,9 @@ def fp8_peak_tflops(dev):
         for _ in range(3):
             mm()
         best = min(event_time(mm, 1, warm=0) for _ in range(10))
-        _measured["fp8"] = 2 * n ** 3 / best / 1e12
+        _measured["fp8"] = max(2 * n ** 3 / best / 1e12, before or 0.0)
     except Exception:
-        _measured["fp8"] = None
+        _measured["fp8"] = before
     return _measured["fp8"]
 
 
@@ -778,12 +781,13 @@ def run_matmul_mx(args, d: Dist):
     sa = torch.randint(120, 134, (m, k // 32), device=d.dev, generator=gen).to(torch.uint8)
     sb = torch.randint(120, 134, (k // 32, n), device=d.dev, generator=gen).to(torch.uint8)
     out = torch.empty(m, n, dtype=torch.float32, device=d.dev)
+    fp8_peak_tflops(d.dev, refresh=True)        # the denominator: the largest of the figures taken before and after
     ms, clocks, rounds = timed(lambda: ops.matmul_mx(a, sa, b_t, sb, out=out), d, steps, args.warmup)
     ops.check_device_status()
     ms_max, = d.reduce([ms], "MAX")
     sec = ms_max / 1e3 / steps
     flops = 2.0 * m * n * k
-    fp8 = fp8_peak_tflops(d.dev)
+    fp8 = fp8_peak_tflops(d.dev, refresh=True)
     cpu = e2e = None
     if not args.kernel_only:
         ah, bh = a.cpu().pin_memory(), b_t.cpu().pin_memory()
@@ -824,7 +828,7 @@ def run_matmul_mx(args, d: Dist):
                           "frac": flops / t_rank / 1e12 / fp8 if fp8 else None,
                           "traffic": (NCU_TRAFFIC["matmul_mx"] if pair else NCU_TRAFFIC["matmul_mx_one_cta"])
                           if (m, n, k) == (MX["m"], MX["n"], MX["k"]) else None,
-                          "peak_source": "measured here: torch._scaled_mm e4m3 8192^3, best of 10",
+                          "peak_source": "measured here: torch._scaled_mm e4m3 8192^3, best of 10, largest of the run's measurements",
                           "note": "2*m*n*k / CUDA-event time of the call: mx_pack_scales_kernel + matmul_mx_pair_kernel"
                                   if pair else "2*m*n*k / CUDA-event time of matmul_mx_kernel"},
                 cpu_baseline=cpu, e2e=e2e)
