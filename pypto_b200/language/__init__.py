@@ -320,7 +320,12 @@ def _install_distributed():
 
     mod.NotifyOp, mod.WaitCmp = NotifyOp, WaitCmp
     mod.tensor, mod.system = _OpNamespace(), _OpNamespace()
-    mod.__getattr__ = lambda n: _unexecuted(n)  # type: ignore[assignment]
+    def _other(name):
+        if name.startswith("__"):          # __file__, __path__, ...: tools that walk sys.modules ask for these
+            raise AttributeError(name)
+        return _unexecuted(name)
+
+    mod.__getattr__ = _other  # type: ignore[assignment]
     sys.modules[mod.__name__] = mod
     return mod
 

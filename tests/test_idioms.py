@@ -122,3 +122,42 @@ def test_the_reference_examples_are_recognised_by_their_bodies():
     rec = idioms.recognise(fl.fused_matmul_bias)
     assert rec is not None and rec.idiom == "linear" and rec.roles == {"a": "a", "b": "b", "bias": "bias", "out": "c"}
     assert idioms.recognise(fl.fused_linear_relu) is None            # relu(a @ b + bias): no fused operator for it
+
+
+def test_canonical_forms_do_not_depend_on_operand_order_or_grouping():
+    """Property (hypothesis): any way of writing the same product / sum of the same operands gives one canonical
+    expression, and a template built one way unifies with an expression built another."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    leaves = [idioms.P(n) for n in "abcd"] + [idioms.un("exp", idioms.P("a")), ("matmul", idioms.P("a"), idioms.P("b"))]
+
+    def build(op, items, splits):
+        """Combine `items` with the binary `op` in the grouping that `splits` dictates."""
+        items = list(items)
+        for sp in splits:
+            if len(items) < 2:
+                break
+            i = sp % (len(items) - 1)
+            items[i:i + 2] = [op(items[i], items[i + 1])]
+        while len(items) > 1:
+            items[0:2] = [op(items[0], items[1])]
+        return items[0]
+
+    @settings(max_examples=200, deadline=None)
+    @given(st.lists(st.sampled_from(leaves), min_size=2, max_size=5), st.randoms(use_true_random=False),
+           st.lists(st.integers(0, 7), max_size=4), st.lists(st.integers(0, 7), max_size=4),
+           st.sampled_from(["mul", "add"]))
+    def check(items, rnd, s1, s2, op_name):
+        op = getattr(idioms, op_name)
+        shuffled = list(items)
+        rnd.shuffle(shuffled)
+        assert build(op, items, s1) == build(op, shuffled, s2)
+
+    check()
+    # unification across orderings: a template with roles against the same shape written the other way round
+    x, w, u = idioms.V("x"), idioms.V("w"), idioms.V("u")
+    t = idioms.mul(("matmul", x, w), idioms.sigmoid(("matmul", x, w)), u)
+    e = idioms.mul(idioms.P("q"), idioms.mul(idioms.sigmoid(("matmul", idioms.P("p"), idioms.P("r"))), ("matmul", idioms.P("p"), idioms.P("r"))))
+    bindings = list(idioms._unify(t, e, {}))
+    assert bindings and all(b == {"x": idioms.P("p"), "w": idioms.P("r"), "u": idioms.P("q")} for b in bindings)

@@ -214,3 +214,17 @@ def test_trace_level_entry_points_and_logger():
     finally:
         lib.pto_set_trace(before)
     assert worker_mod.log is logging.getLogger("pypto_b200")
+
+
+def test_placeholder_modules_answer_dunder_lookups_like_modules():
+    """``pypto.language.distributed`` answers any operation name with a placeholder, but not ``__file__`` and the
+    like: tools that walk ``sys.modules`` (hypothesis, inspect) ask for those and expect strings or AttributeError."""
+    import sys
+
+    from pypto_b200 import compat
+    compat.install()
+    for name in ("pypto_b200.language.distributed", "pypto.language.distributed", "pypto_b200.language", "pypto.language"):
+        mod = sys.modules[name]
+        assert isinstance(getattr(mod, "__file__", None), (str, type(None))), name
+        assert not hasattr(mod, "__wrapped__"), name
+    assert callable(sys.modules["pypto.language.distributed"].notify)        # an operation name still resolves
