@@ -283,7 +283,7 @@ def _unexecuted(name):
 
 class _OpNamespace(types.SimpleNamespace):
     def __getattr__(self, name):
-        if name.startswith("__"):
+        if name.startswith("_"):     # dunder and protocol probes (_repr_html_, ...): no operation is named so
             raise AttributeError(name)
         return _unexecuted(name)
 
@@ -297,7 +297,7 @@ system = _OpNamespace()
 def __getattr__(name):
     """Any other ``pl.<op>`` (load, store, matmul, row_max, range, ...) resolves to a
     placeholder: DSL bodies are never executed here."""
-    if name.startswith("__"):
+    if name.startswith("_"):         # dunder and protocol probes (_repr_html_, ...): no operation is named so
         raise AttributeError(name)
     if name == "jit":
         from ..jit import jit as _jit
@@ -321,7 +321,7 @@ def _install_distributed():
     mod.NotifyOp, mod.WaitCmp = NotifyOp, WaitCmp
     mod.tensor, mod.system = _OpNamespace(), _OpNamespace()
     def _other(name):
-        if name.startswith("__"):          # __file__, __path__, ...: tools that walk sys.modules ask for these
+        if name.startswith("_"):           # __file__, _repr_html_, ...: tools and notebooks ask for these; no operation is named so
             raise AttributeError(name)
         return _unexecuted(name)
 

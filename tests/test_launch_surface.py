@@ -228,3 +228,7 @@ def test_placeholder_modules_answer_dunder_lookups_like_modules():
         assert isinstance(getattr(mod, "__file__", None), (str, type(None))), name
         assert not hasattr(mod, "__wrapped__"), name
     assert callable(sys.modules["pypto.language.distributed"].notify)        # an operation name still resolves
+    import pypto_b200.language as pl_
+    for ns in (pl_, pl_.tensor, pl_.tile, pl_.distributed):
+        assert not hasattr(ns, "_repr_html_") and not hasattr(ns, "_ipython_canary_method_should_not_exist_")
+        assert callable(ns.load)
